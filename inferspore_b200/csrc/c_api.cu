@@ -1,0 +1,78 @@
+// Library-level entry points of the C ABI: error text, the thread-local stream
+// used by the C++ launch templates, and the per-device status word that kernels
+// set instead of trapping on bad data.
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ispore {
+namespace {
+
+thread_local char g_error[512] = "";
+thread_local cudaStream_t g_stream = nullptr;
+
+// One status word per device, in that device's memory.
+__device__ unsigned g_device_status = 0;
+
+constexpr int kMaxDevices = 64;
+unsigned* g_status_addr[kMaxDevices] = {};
+std::mutex g_status_mutex;
+
+}  // namespace
+
+int fail(int code, const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_error, sizeof(g_error), fmt, ap);
+    va_end(ap);
+    return code;
+}
+
+int check_launch(const char* what) {
+    const cudaError_t e = cudaPeekAtLastError();
+    if (e == cudaSuccess) return ISPORE_OK;
+    (void)cudaGetLastError();  // clear a (non-sticky) launch-configuration error
+    return fail(ISPORE_ELAUNCH, "%s: %s", what, cudaGetErrorString(e));
+}
+
+unsigned* device_status_ptr() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return nullptr;
+    std::lock_guard<std::mutex> lock(g_status_mutex);
+    if (g_status_addr[dev] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        g_status_addr[dev] = static_cast<unsigned*>(p);
+    }
+    return g_status_addr[dev];
+}
+
+}  // namespace ispore
+
+extern "C" {
+
+int ispore_version(void) { return 100; /* 0.1.0 */ }
+
+const char* ispore_last_error_string(void) { return ispore::g_error; }
+
+void ispore_set_stream(ispore_stream_t stream) { ispore::g_stream = static_cast<cudaStream_t>(stream); }
+
+ispore_stream_t ispore_get_stream(void) { return ispore::g_stream; }
+
+int ispore_device_status(unsigned* flags_out, int clear) {
+    if (flags_out == nullptr) return ispore::fail(ISPORE_ENULL, "device_status: flags_out is NULL");
+    unsigned* p = ispore::device_status_ptr();
+    if (p == nullptr) return ispore::fail(ISPORE_ELAUNCH, "device_status: no CUDA device");
+    cudaError_t e = cudaMemcpy(flags_out, p, sizeof(unsigned), cudaMemcpyDeviceToHost);
+    if (e == cudaSuccess && clear) e = cudaMemset(p, 0, sizeof(unsigned));
+    if (e != cudaSuccess) return ispore::fail(ISPORE_ELAUNCH, "device_status: %s", cudaGetErrorString(e));
+    return ISPORE_OK;
+}
+
+}  // extern "C"

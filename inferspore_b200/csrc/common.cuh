@@ -1,0 +1,132 @@
+// Shared device/host helpers for the sm_100a layer kernels.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ispore_kernels.h"
+
+namespace ispore {
+
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+
+// ---- host-side status plumbing (c_api.cu owns the storage) -------------------
+int fail(int code, const char* fmt, ...);
+int check_launch(const char* what);
+unsigned* device_status_ptr();  // address of the per-device status word (device memory)
+
+// ---- storage-type traits ------------------------------------------------------
+// One 128-bit vector holds 4 floats or 8 halves.
+template <typename T>
+struct VecTraits;
+template <>
+struct VecTraits<float> {
+    static constexpr int kElems = 4;
+};
+template <>
+struct VecTraits<__half> {
+    static constexpr int kElems = 8;
+};
+
+template <typename T>
+__device__ __forceinline__ float to_float(T v);
+template <>
+__device__ __forceinline__ float to_float<float>(float v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ float to_float<__half>(__half v) {
+    return __half2float(v);
+}
+template <typename T>
+__device__ __forceinline__ T from_float(float v);
+template <>
+__device__ __forceinline__ float from_float<float>(float v) {
+    return v;
+}
+template <>
+__device__ __forceinline__ __half from_float<__half>(float v) {
+    return __float2half_rn(v);
+}
+
+// ---- 128-bit global accesses with cache policy ---------------------------------
+// Activations are touched once: stream them (evict-first) so that small reused
+// operands (gamma, bias, masks, frequency tables) keep their L2 lines.
+__device__ __forceinline__ uint4 ld_stream(const uint4* p) { return __ldcs(p); }
+__device__ __forceinline__ uint4 ld_keep(const uint4* p) { return __ldg(p); }
+__device__ __forceinline__ void st_stream(uint4* p, uint4 v) { __stcs(p, v); }
+
+// A 128-bit vector viewed as N fp32 lanes after widening (4 for float, 8 for half).
+template <typename T>
+struct Unpacked;
+template <>
+struct Unpacked<float> {
+    float v[4];
+};
+template <>
+struct Unpacked<__half> {
+    float v[8];
+};
+
+__device__ __forceinline__ void unpack(const uint4& raw, Unpacked<float>& out) {
+    out.v[0] = __uint_as_float(raw.x);
+    out.v[1] = __uint_as_float(raw.y);
+    out.v[2] = __uint_as_float(raw.z);
+    out.v[3] = __uint_as_float(raw.w);
+}
+__device__ __forceinline__ void unpack(const uint4& raw, Unpacked<__half>& out) {
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 h = *reinterpret_cast<const __half2*>(&w[i]);
+        float2 f = __half22float2(h);
+        out.v[2 * i] = f.x;
+        out.v[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 pack(const Unpacked<float>& in) {
+    return make_uint4(__float_as_uint(in.v[0]), __float_as_uint(in.v[1]), __float_as_uint(in.v[2]),
+                      __float_as_uint(in.v[3]));
+}
+__device__ __forceinline__ uint4 pack(const Unpacked<__half>& in) {
+    uint32_t w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        __half2 h = __floats2half2_rn(in.v[2 * i], in.v[2 * i + 1]);
+        w[i] = *reinterpret_cast<uint32_t*>(&h);
+    }
+    return make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+// Rounds every lane to the storage type and back (identity for float).  Used
+// where the reference stores an intermediate in the activation type.
+__device__ __forceinline__ void round_to_storage(Unpacked<float>&) {}
+__device__ __forceinline__ void round_to_storage(Unpacked<__half>& x) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) x.v[i] = __half2float(__float2half_rn(x.v[i]));
+}
+
+// ---- reductions -------------------------------------------------------------------
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// 2^x through the SFU (ex2.approx, ~2^-22 relative error, denormals flushed).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
+
+}  // namespace ispore

@@ -1,0 +1,106 @@
+// Input-embedding gather for sm_100a.
+//
+// Semantics: src/kernels/input_embedding.cu:5-23 of the reference —
+// output[t, :] = table[input_ids[t], :], a bit-exact row copy.  The reference
+// moves one element per thread-iteration with a div/mod per element; here one
+// warp owns a row and moves it as 128-bit vectors, four independent loads in
+// flight per lane, rows taken grid-stride.
+#include "common.cuh"
+
+namespace ispore {
+namespace {
+
+template <int THREADS, int UNROLL>
+__global__ void __launch_bounds__(THREADS)
+embedding_gather_vec_kernel(const int32_t* __restrict__ ids, uint4* __restrict__ out,
+                            const uint4* __restrict__ table, int64_t num_tokens, int row_vecs,
+                            int64_t vocab, unsigned* __restrict__ status) {
+    constexpr int kWarps = THREADS / 32;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
+    const int64_t warp_stride = static_cast<int64_t>(gridDim.x) * kWarps;
+    for (int64_t t = warp_global; t < num_tokens; t += warp_stride) {
+        const int64_t id = __ldg(ids + t);
+        uint4* dst = out + t * row_vecs;
+        if (vocab > 0 && (id < 0 || id >= vocab)) {
+            if (lane == 0) atomicOr(status, ISPORE_DEV_BAD_TOKEN_ID);
+            for (int v = lane; v < row_vecs; v += 32) st_stream(dst + v, make_uint4(0, 0, 0, 0));
+            continue;
+        }
+        const uint4* src = table + id * row_vecs;
+        for (int v0 = lane; v0 < row_vecs; v0 += 32 * UNROLL) {
+            uint4 buf[UNROLL];
+#pragma unroll
+            for (int k = 0; k < UNROLL; ++k) {
+                const int v = v0 + 32 * k;
+                if (v < row_vecs) buf[k] = ld_stream(src + v);
+            }
+#pragma unroll
+            for (int k = 0; k < UNROLL; ++k) {
+                const int v = v0 + 32 * k;
+                if (v < row_vecs) st_stream(dst + v, buf[k]);
+            }
+        }
+    }
+}
+
+template <typename T>
+__global__ void embedding_gather_scalar_kernel(const int32_t* __restrict__ ids, T* __restrict__ out,
+                                               const T* __restrict__ table, int64_t num_tokens,
+                                               int64_t hidden, int64_t vocab,
+                                               unsigned* __restrict__ status) {
+    for (int64_t t = blockIdx.x; t < num_tokens; t += gridDim.x) {
+        const int64_t id = ids[t];
+        const bool bad = vocab > 0 && (id < 0 || id >= vocab);
+        if (bad && threadIdx.x == 0) atomicOr(status, ISPORE_DEV_BAD_TOKEN_ID);
+        for (int64_t j = threadIdx.x; j < hidden; j += blockDim.x)
+            out[t * hidden + j] = bad ? from_float<T>(0.f) : table[id * hidden + j];
+    }
+}
+
+template <typename T>
+int embedding_dispatch(const int32_t* ids, T* out, const T* table, int64_t tokens, int64_t hidden,
+                       int64_t vocab, cudaStream_t st) {
+    if (ids == nullptr || out == nullptr || table == nullptr)
+        return fail(ISPORE_ENULL, "input_embedding: NULL buffer");
+    if (tokens < 0 || hidden <= 0 || vocab < 0)
+        return fail(ISPORE_ESHAPE, "input_embedding: bad shape tokens=%lld hidden=%lld vocab=%lld",
+                    (long long)tokens, (long long)hidden, (long long)vocab);
+    if (tokens == 0) return ISPORE_OK;
+    unsigned* status = device_status_ptr();
+    if (status == nullptr) return fail(ISPORE_ELAUNCH, "input_embedding: no device status word");
+    constexpr int E = VecTraits<T>::kElems;
+    if (hidden % E == 0 && hidden / E <= INT32_MAX && aligned16(out) && aligned16(table)) {
+        constexpr int THREADS = 256, UNROLL = 4;
+        const int64_t blocks = ceil_div(tokens, THREADS / 32);
+        const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
+        embedding_gather_vec_kernel<THREADS, UNROLL>
+            <<<static_cast<int>(blocks < max_ctas ? blocks : max_ctas), THREADS, 0, st>>>(
+                ids, reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(table), tokens,
+                static_cast<int>(hidden / E), vocab, status);
+        return check_launch("embedding_gather_vec_kernel");
+    }
+    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
+    embedding_gather_scalar_kernel<T><<<static_cast<int>(tokens < max_ctas ? tokens : max_ctas), 256, 0, st>>>(
+        ids, out, table, tokens, hidden, vocab, status);
+    return check_launch("embedding_gather_scalar_kernel");
+}
+
+}  // namespace
+}  // namespace ispore
+
+extern "C" {
+int ispore_input_embedding_f32(const int32_t* input_ids, float* output, const float* table,
+                               int64_t num_tokens, int64_t hidden, int64_t vocab_size,
+                               ispore_stream_t stream) {
+    return ispore::embedding_dispatch<float>(input_ids, output, table, num_tokens, hidden, vocab_size,
+                                             static_cast<cudaStream_t>(stream));
+}
+int ispore_input_embedding_f16(const int32_t* input_ids, void* output, const void* table,
+                               int64_t num_tokens, int64_t hidden, int64_t vocab_size,
+                               ispore_stream_t stream) {
+    return ispore::embedding_dispatch<__half>(input_ids, static_cast<__half*>(output),
+                                              static_cast<const __half*>(table), num_tokens, hidden,
+                                              vocab_size, static_cast<cudaStream_t>(stream));
+}
+}

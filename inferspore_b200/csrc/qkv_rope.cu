@@ -1,0 +1,340 @@
+// QKV bias + RoPE + un-pad + head transpose (prefill) and in-place decode RoPE
+// for sm_100a.
+//
+// Semantics: the reference's fp32 kernel, src/kernels/qkv_bias_and_RoPE.cu:110-192,
+// with the bias add its fp16 draft describes (:236-252) applied before the
+// rotation; rotation pairs are (j, j + head_size/2) (:47-53, :182-190);
+// theta_j = m / powf(base, 2j/rot_dim) (:38-45).
+//
+// The reference launches one CTA per (token, head) and recomputes
+// powf+cos+sin for every head.  Here one CTA owns a token: cos/sin for the
+// token's position are computed once into shared memory (rot_dim/2 sincosf
+// calls) and reused by all q and k heads; every thread moves 128-bit vectors —
+// the low-half vector and its partner in the high half — so a warp reads 1 KB
+// of contiguous QKV and writes whole 256-byte head rows of the transposed
+// outputs.  The powf denominators are evaluated on the host and travel as a
+// kernel argument.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace ispore {
+namespace {
+
+constexpr int kMaxRotHalf = 256;
+struct RopeDenominators {
+    float d[kMaxRotHalf];  // powf(base, 2j / rot_dim)
+};
+
+int fill_denominators(RopeDenominators* out, int rot_dim, float base) {
+    if (rot_dim < 0 || rot_dim / 2 > kMaxRotHalf) return -1;
+    for (int j = 0; j < rot_dim / 2; ++j)
+        out->d[j] = powf(base, static_cast<float>(2 * j) / static_cast<float>(rot_dim));
+    return 0;
+}
+
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* __restrict__ v_buf,
+                              const T* __restrict__ QKV, const T* __restrict__ bias,
+                              const int32_t* __restrict__ padding_offset,
+                              const int32_t* __restrict__ history_length, int64_t batch_size,
+                              int64_t seq_len, int64_t token_num, int head_num, int kv_head_num,
+                              int head_size, int rot_half, const RopeDenominators freq,
+                              unsigned* __restrict__ status) {
+    constexpr int E = VecTraits<T>::kElems;
+    __shared__ float2 cos_sin[kMaxRotHalf];
+    const int tid = threadIdx.x;
+    const int head_vecs = head_size / E;
+    const int half_vecs = head_vecs / 2;
+    const int qkv_heads = head_num + 2 * kv_head_num;
+    const int rope_tasks = (head_num + kv_head_num) * half_vecs;
+    const int v_tasks = kv_head_num * head_vecs;
+    const uint4* bias_v = reinterpret_cast<const uint4*>(bias);
+
+    for (int64_t token = blockIdx.x; token < token_num; token += gridDim.x) {
+        const int64_t dst_token = token + __ldg(padding_offset + token);
+        if (dst_token < 0 || dst_token >= batch_size * seq_len) {
+            if (tid == 0) atomicOr(status, ISPORE_DEV_BAD_PADDING);
+            continue;  // uniform over the CTA
+        }
+        const int64_t b = dst_token / seq_len;
+        const int64_t s = dst_token - b * seq_len;
+        const float m = static_cast<float>(__ldg(history_length + b) + static_cast<int>(s));
+
+        __syncthreads();  // previous token's readers are done with cos_sin
+        for (int j = tid; j < rot_half; j += THREADS) {
+            float sn, cs;
+            sincosf(m / freq.d[j], &sn, &cs);
+            cos_sin[j] = make_float2(cs, sn);
+        }
+        __syncthreads();
+
+        const uint4* src = reinterpret_cast<const uint4*>(QKV) + token * qkv_heads * head_vecs;
+
+        // q and k heads: rotate (low-half vector, high-half vector) pairs.
+#pragma unroll 2
+        for (int task = tid; task < rope_tasks; task += THREADS) {
+            const int hh = task / half_vecs;  // head index inside [q heads | k heads]
+            const int c = task - hh * half_vecs;
+            const uint4 lo_raw = ld_stream(src + hh * head_vecs + c);
+            const uint4 hi_raw = ld_stream(src + hh * head_vecs + half_vecs + c);
+            Unpacked<T> lo, hi;
+            unpack(lo_raw, lo);
+            unpack(hi_raw, hi);
+            if (bias != nullptr) {
+                Unpacked<T> blo, bhi;
+                unpack(ld_keep(bias_v + hh * head_vecs + c), blo);
+                unpack(ld_keep(bias_v + hh * head_vecs + half_vecs + c), bhi);
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    lo.v[e] += blo.v[e];
+                    hi.v[e] += bhi.v[e];
+                }
+            }
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                const int j = c * E + e;
+                if (j < rot_half) {
+                    const float2 cs = cos_sin[j];
+                    const float x0 = lo.v[e], x1 = hi.v[e];
+                    lo.v[e] = cs.x * x0 - cs.y * x1;
+                    hi.v[e] = cs.x * x1 + cs.y * x0;
+                }
+            }
+            const bool is_q = hh < head_num;
+            const int h = is_q ? hh : hh - head_num;
+            T* base = is_q ? q_buf : k_buf;
+            const int64_t heads = is_q ? head_num : kv_head_num;
+            uint4* dst = reinterpret_cast<uint4*>(base) + ((b * heads + h) * seq_len + s) * head_vecs;
+            st_stream(dst + c, pack(lo));
+            st_stream(dst + half_vecs + c, pack(hi));
+        }
+
+        // v heads: bias add and transposed copy.
+        const uint4* vsrc = src + (head_num + kv_head_num) * head_vecs;
+#pragma unroll 2
+        for (int task = tid; task < v_tasks; task += THREADS) {
+            const int h = task / head_vecs;
+            const int c = task - h * head_vecs;
+            uint4 raw = ld_stream(vsrc + task);
+            if (bias != nullptr) {
+                Unpacked<T> x, bb;
+                unpack(raw, x);
+                unpack(ld_keep(bias_v + (head_num + kv_head_num) * head_vecs + task), bb);
+#pragma unroll
+                for (int e = 0; e < E; ++e) x.v[e] += bb.v[e];
+                raw = pack(x);
+            }
+            uint4* dst = reinterpret_cast<uint4*>(v_buf) +
+                         ((b * kv_head_num + h) * seq_len + s) * head_vecs;
+            st_stream(dst + c, raw);
+        }
+    }
+}
+
+// Any head size / alignment (head_size even): one thread per rotation pair.
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+qkv_rope_transpose_scalar_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* __restrict__ v_buf,
+                                 const T* __restrict__ QKV, const T* __restrict__ bias,
+                                 const int32_t* __restrict__ padding_offset,
+                                 const int32_t* __restrict__ history_length, int64_t batch_size,
+                                 int64_t seq_len, int64_t token_num, int head_num, int kv_head_num,
+                                 int head_size, int rot_half, const RopeDenominators freq,
+                                 unsigned* __restrict__ status) {
+    const int tid = threadIdx.x;
+    const int half = head_size / 2;
+    const int qkv_heads = head_num + 2 * kv_head_num;
+    for (int64_t token = blockIdx.x; token < token_num; token += gridDim.x) {
+        const int64_t dst_token = token + padding_offset[token];
+        if (dst_token < 0 || dst_token >= batch_size * seq_len) {
+            if (tid == 0) atomicOr(status, ISPORE_DEV_BAD_PADDING);
+            continue;
+        }
+        const int64_t b = dst_token / seq_len;
+        const int64_t s = dst_token - b * seq_len;
+        const float m = static_cast<float>(history_length[b] + static_cast<int>(s));
+        const T* src = QKV + token * qkv_heads * head_size;
+        for (int task = tid; task < (head_num + kv_head_num) * half; task += THREADS) {
+            const int hh = task / half, j = task - hh * half;
+            float x0 = to_float<T>(src[hh * head_size + j]);
+            float x1 = to_float<T>(src[hh * head_size + half + j]);
+            if (bias != nullptr) {
+                x0 += to_float<T>(bias[hh * head_size + j]);
+                x1 += to_float<T>(bias[hh * head_size + half + j]);
+            }
+            float o0 = x0, o1 = x1;
+            if (j < rot_half) {
+                float sn, cs;
+                sincosf(m / freq.d[j], &sn, &cs);
+                o0 = cs * x0 - sn * x1;
+                o1 = cs * x1 + sn * x0;
+            }
+            const bool is_q = hh < head_num;
+            const int h = is_q ? hh : hh - head_num;
+            T* base = is_q ? q_buf : k_buf;
+            const int64_t heads = is_q ? head_num : kv_head_num;
+            T* dst = base + ((b * heads + h) * seq_len + s) * head_size;
+            dst[j] = from_float<T>(o0);
+            dst[half + j] = from_float<T>(o1);
+        }
+        const int v_at = (head_num + kv_head_num) * head_size;
+        for (int task = tid; task < kv_head_num * head_size; task += THREADS) {
+            const int h = task / head_size, j = task - h * head_size;
+            float x = to_float<T>(src[v_at + task]);
+            if (bias != nullptr) x += to_float<T>(bias[v_at + task]);
+            v_buf[((b * kv_head_num + h) * seq_len + s) * head_size + j] = from_float<T>(x);
+        }
+    }
+}
+
+// Decode step: rotate q and k heads of qkv_buf[batch, heads, head_size] in place
+// at position step-1 (reference: src/kernels/qkv_bias_and_RoPE.cu:352-390).
+template <typename T, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rope_decode_kernel(T* __restrict__ qkv, int head_num, int kv_head_num, int head_size, int rot_half,
+                   float position, const RopeDenominators freq) {
+    __shared__ float2 cos_sin[kMaxRotHalf];
+    const int tid = threadIdx.x;
+    for (int j = tid; j < rot_half; j += THREADS) {
+        float sn, cs;
+        sincosf(position / freq.d[j], &sn, &cs);
+        cos_sin[j] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    const int half = head_size / 2;
+    T* row = qkv + static_cast<int64_t>(blockIdx.x) * (head_num + 2 * kv_head_num) * head_size;
+    for (int task = tid; task < (head_num + kv_head_num) * rot_half; task += THREADS) {
+        const int hh = task / rot_half, j = task - hh * rot_half;
+        T* p = row + hh * head_size;
+        const float x0 = to_float<T>(p[j]), x1 = to_float<T>(p[half + j]);
+        const float2 cs = cos_sin[j];
+        p[j] = from_float<T>(cs.x * x0 - cs.y * x1);
+        p[half + j] = from_float<T>(cs.x * x1 + cs.y * x0);
+    }
+}
+
+template <typename T>
+int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
+                 const int32_t* padding_offset, const int32_t* history_length, int64_t batch_size,
+                 int64_t seq_len, int64_t token_num, int64_t head_num, int64_t kv_head_num,
+                 int64_t head_size, int32_t rot_dim, float base, cudaStream_t st) {
+    if (!q_buf || !k_buf || !v_buf || !QKV || !padding_offset || !history_length)
+        return fail(ISPORE_ENULL, "qkv_bias_rope_transpose: NULL buffer");
+    if (batch_size <= 0 || seq_len <= 0 || token_num < 0 || head_num <= 0 || kv_head_num <= 0 ||
+        head_size <= 0 || head_size % 2 != 0 || head_num > 65535 || kv_head_num > 65535 ||
+        head_size > 65536)
+        return fail(ISPORE_ESHAPE,
+                    "qkv_bias_rope_transpose: bad shape bs=%lld seq=%lld tokens=%lld heads=%lld/%lld d=%lld",
+                    (long long)batch_size, (long long)seq_len, (long long)token_num,
+                    (long long)head_num, (long long)kv_head_num, (long long)head_size);
+    if (token_num > batch_size * seq_len)
+        return fail(ISPORE_ESHAPE, "qkv_bias_rope_transpose: %lld packed tokens exceed bs*seq=%lld",
+                    (long long)token_num, (long long)(batch_size * seq_len));
+    if (rot_dim < 0 || rot_dim % 2 != 0 || rot_dim > head_size)
+        return fail(ISPORE_ESHAPE, "qkv_bias_rope_transpose: rotary dim %d vs head size %lld", rot_dim,
+                    (long long)head_size);
+    RopeDenominators freq;
+    if (fill_denominators(&freq, rot_dim, base) != 0)
+        return fail(ISPORE_ELIMIT, "qkv_bias_rope_transpose: rotary dim %d > %d", rot_dim, 2 * kMaxRotHalf);
+    if (token_num == 0) return ISPORE_OK;
+    unsigned* status = device_status_ptr();
+    if (status == nullptr) return fail(ISPORE_ELAUNCH, "qkv_bias_rope_transpose: no device status word");
+
+    constexpr int THREADS = 256;
+    constexpr int E = VecTraits<T>::kElems;
+    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
+    const int grid = static_cast<int>(token_num < max_ctas ? token_num : max_ctas);
+    const bool vec_ok = head_size % (2 * E) == 0 && aligned16(q_buf) && aligned16(k_buf) &&
+                        aligned16(v_buf) && aligned16(QKV) && (bias == nullptr || aligned16(bias));
+    if (vec_ok) {
+        qkv_rope_transpose_vec_kernel<T, THREADS><<<grid, THREADS, 0, st>>>(
+            q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
+            token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
+        return check_launch("qkv_rope_transpose_vec_kernel");
+    }
+    qkv_rope_transpose_scalar_kernel<T, THREADS><<<grid, THREADS, 0, st>>>(
+        q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len, token_num,
+        (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
+    return check_launch("qkv_rope_transpose_scalar_kernel");
+}
+
+template <typename T>
+int rope_decode_dispatch(T* qkv, int64_t batch, int64_t head_num, int64_t kv_head_num,
+                         int64_t head_size, int32_t step, int32_t rot_dim, float base, cudaStream_t st) {
+    if (!qkv) return fail(ISPORE_ENULL, "rope_decode: NULL buffer");
+    if (batch < 0 || head_num <= 0 || kv_head_num <= 0 || head_size <= 0 || head_size % 2 != 0 ||
+        head_num > 65535 || kv_head_num > 65535 || head_size > 65536 || batch > INT32_MAX)
+        return fail(ISPORE_ESHAPE, "rope_decode: bad shape");
+    if (rot_dim < 0 || rot_dim % 2 != 0 || rot_dim > head_size)
+        return fail(ISPORE_ESHAPE, "rope_decode: rotary dim %d vs head size %lld", rot_dim, (long long)head_size);
+    RopeDenominators freq;
+    if (fill_denominators(&freq, rot_dim, base) != 0)
+        return fail(ISPORE_ELIMIT, "rope_decode: rotary dim %d > %d", rot_dim, 2 * kMaxRotHalf);
+    if (batch == 0) return ISPORE_OK;
+    constexpr int THREADS = 256;
+    rope_decode_kernel<T, THREADS><<<static_cast<int>(batch), THREADS, 0, st>>>(
+        qkv, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2,
+        static_cast<float>(step - 1), freq);
+    return check_launch("rope_decode_kernel");
+}
+
+}  // namespace
+}  // namespace ispore
+
+extern "C" {
+
+int ispore_qkv_bias_rope_transpose_f32(float* q_buf, float* k_buf, float* v_buf, const float* QKV,
+                                       const float* bias, const int32_t* padding_offset,
+                                       const int32_t* history_length, const int32_t* input_length,
+                                       int64_t batch_size, int64_t seq_len, int64_t token_num,
+                                       int64_t head_num, int64_t kv_head_num, int64_t head_size,
+                                       int32_t rotary_embedding_dim, float rotary_embedding_base,
+                                       int32_t max_position_embeddings, int32_t use_dynamic_ntk,
+                                       ispore_stream_t stream) {
+    (void)input_length;
+    (void)max_position_embeddings;
+    (void)use_dynamic_ntk;
+    return ispore::qkv_dispatch<float>(q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length,
+                                       batch_size, seq_len, token_num, head_num, kv_head_num, head_size,
+                                       rotary_embedding_dim, rotary_embedding_base,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+int ispore_qkv_bias_rope_transpose_f16(void* q_buf, void* k_buf, void* v_buf, const void* QKV,
+                                       const void* bias, const int32_t* padding_offset,
+                                       const int32_t* history_length, const int32_t* input_length,
+                                       int64_t batch_size, int64_t seq_len, int64_t token_num,
+                                       int64_t head_num, int64_t kv_head_num, int64_t head_size,
+                                       int32_t rotary_embedding_dim, float rotary_embedding_base,
+                                       int32_t max_position_embeddings, int32_t use_dynamic_ntk,
+                                       ispore_stream_t stream) {
+    (void)input_length;
+    (void)max_position_embeddings;
+    (void)use_dynamic_ntk;
+    return ispore::qkv_dispatch<__half>(
+        static_cast<__half*>(q_buf), static_cast<__half*>(k_buf), static_cast<__half*>(v_buf),
+        static_cast<const __half*>(QKV), static_cast<const __half*>(bias), padding_offset,
+        history_length, batch_size, seq_len, token_num, head_num, kv_head_num, head_size,
+        rotary_embedding_dim, rotary_embedding_base, static_cast<cudaStream_t>(stream));
+}
+
+int ispore_rope_decode_f32(float* qkv_buf, int64_t batch_size, int64_t head_num, int64_t kv_head_num,
+                           int64_t head_size, int32_t step, int32_t rotary_embedding_dim,
+                           float rotary_embedding_base, ispore_stream_t stream) {
+    return ispore::rope_decode_dispatch<float>(qkv_buf, batch_size, head_num, kv_head_num, head_size,
+                                               step, rotary_embedding_dim, rotary_embedding_base,
+                                               static_cast<cudaStream_t>(stream));
+}
+
+int ispore_rope_decode_f16(void* qkv_buf, int64_t batch_size, int64_t head_num, int64_t kv_head_num,
+                           int64_t head_size, int32_t step, int32_t rotary_embedding_dim,
+                           float rotary_embedding_base, ispore_stream_t stream) {
+    return ispore::rope_decode_dispatch<__half>(static_cast<__half*>(qkv_buf), batch_size, head_num,
+                                                kv_head_num, head_size, step, rotary_embedding_dim,
+                                                rotary_embedding_base,
+                                                static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,479 @@
+"""CUDA kernels vs the oracle, through the C ABI.  Marked gpu.
+
+Bit-exact where the op is a copy or an index selection (embedding, KV concat,
+top-K ids and values); 1e-5 relative for fp32 outputs; 2e-3 absolute against
+the oracle's fp32-accumulated value for fp16 outputs (tests/_util.py).
+"""
+import numpy as np
+import pytest
+import torch
+
+from _util import assert_close_f16, assert_close_f32, dev, host, randn16
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(cuda):
+    from inferspore_b200 import ops as _ops
+
+    return _ops
+
+
+@pytest.fixture(autouse=True)
+def _clean_status(cuda):
+    from inferspore_b200 import capi
+
+    capi.device_status(clear=True)
+    yield
+    torch.cuda.synchronize()
+
+
+# ---- residual add + RMSNorm ---------------------------------------------------------------------
+
+NORM_SHAPES = [(64, 4096), (2, 32), (5, 8), (3, 1000), (300, 4096), (7, 5120), (4, 8192), (3, 11008), (2, 16384),
+               (3, 100), (2, 4100), (1, 1), (1200, 256), (2, 20000)]
+
+
+@pytest.mark.parametrize("tokens,hidden", NORM_SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_add_residual_rmsnorm_f32(ops, orc, rng, tokens, hidden, with_bias):
+    x = rng.standard_normal((tokens, hidden), dtype=np.float32)
+    r = rng.standard_normal((tokens, hidden), dtype=np.float32)
+    g = rng.uniform(0.5, 1.5, hidden).astype(np.float32)
+    b = (rng.standard_normal(hidden) * 0.1).astype(np.float32) if with_bias else None
+    dx, dr, dg = dev(x), dev(r), dev(g)
+    ops.launchFusedAddBiasResidualRMSNorm(dr, dx, None if b is None else dev(b), dg, 1e-6)
+    want_x, want_r, _ = orc.add_residual_rmsnorm(x, r, b, g, 1e-6)
+    assert np.array_equal(host(dr), want_r)  # one IEEE add: exact
+    assert_close_f32(host(dx), want_x, what="rmsnorm f32")
+
+
+@pytest.mark.parametrize("tokens,hidden", NORM_SHAPES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_add_residual_rmsnorm_f16(ops, orc, rng, tokens, hidden, with_bias):
+    x, r = randn16(rng, (tokens, hidden)), randn16(rng, (tokens, hidden))
+    g = rng.uniform(0.5, 1.5, hidden).astype(np.float16)
+    b = randn16(rng, hidden, 0.1) if with_bias else None
+    dx, dr = dev(x), dev(r)
+    ops.launchFusedAddBiasResidualRMSNorm(dr, dx, None if b is None else dev(b), dev(g), 1e-6)
+    want_x, want_r, want32 = orc.add_residual_rmsnorm(x, r, b, g, 1e-6)
+    assert np.array_equal(host(dr).view(np.uint16), want_r.view(np.uint16))
+    _, _, same = assert_close_f16(host(dx), want32, want_x, "rmsnorm f16")
+    assert same > 0.99
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("tokens,hidden", [(64, 4096), (9, 40), (3, 12288)])
+def test_plain_rmsnorm_and_null_residual(ops, orc, rng, dtype, tokens, hidden):
+    x = rng.standard_normal((tokens, hidden), dtype=np.float32).astype(dtype)
+    g = rng.uniform(0.5, 1.5, hidden).astype(dtype)
+    want, want_copy, want32 = orc.rmsnorm(x, g, 1e-6, want_copy=True)
+    # (1) launchRMSNorm with a residual copy
+    dx, dc = dev(x), torch.empty_like(dev(x))
+    ops.launchRMSNorm(dx, dc, dev(g), 1e-6)
+    assert np.array_equal(host(dc).view(np.uint8), x.view(np.uint8))
+    # (2) launchRMSNorm without, (3) the reference's route: fused launcher with a NULL residual
+    dx2, dx3 = dev(x), dev(x)
+    ops.launchRMSNorm(dx2, None, dev(g), 1e-6)
+    ops.launchFusedAddBiasResidualRMSNorm(None, dx3, None, dev(g), 1e-6)
+    for d in (dx, dx2, dx3):
+        if dtype == np.float32:
+            assert_close_f32(host(d), want, what="plain rmsnorm")
+        else:
+            assert_close_f16(host(d), want32, want, "plain rmsnorm f16")
+    assert np.array_equal(host(dx).view(np.uint8), host(dx2).view(np.uint8))
+    assert np.array_equal(host(dx).view(np.uint8), host(dx3).view(np.uint8))
+
+
+def test_rmsnorm_unaligned_views_take_the_scalar_path(ops, orc, rng):
+    big = rng.standard_normal(3 * 64 + 1, dtype=np.float32)
+    d = dev(big)
+    x = d[1:].view(3, 64)  # 4-byte aligned only
+    g = rng.uniform(0.5, 1.5, 64).astype(np.float32)
+    ops.launchFusedAddBiasResidualRMSNorm(None, x, None, dev(g), 1e-6)
+    want, _, _ = orc.add_residual_rmsnorm(big[1:].reshape(3, 64), None, None, g, 1e-6)
+    assert_close_f32(host(x), want, what="unaligned rmsnorm")
+    assert host(d)[0] == big[0]
+
+
+def test_rmsnorm_empty(ops, cuda):
+    x = torch.empty((0, 128), device=cuda)
+    ops.launchFusedAddBiasResidualRMSNorm(torch.empty_like(x), x, None, torch.ones(128, device=cuda), 1e-6)
+
+
+# ---- embedding -----------------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("tokens,hidden,vocab", [(4096, 4096, 32000), (64, 4096, 32000), (33, 100, 50), (1, 8, 3),
+                                                 (257, 1000, 777), (19, 7, 11)])
+def test_input_embedding_bit_exact(ops, orc, rng, dtype, tokens, hidden, vocab):
+    table = (rng.standard_normal((vocab, hidden), dtype=np.float32) * 0.02).astype(dtype)
+    ids = rng.integers(0, vocab, tokens).astype(np.int32)
+    ids[0], ids[-1] = vocab - 1, 0
+    out = torch.empty((tokens, hidden), dtype=dev(table[:1]).dtype, device="cuda:0")
+    ops.launchInputEmbedding(dev(ids), out, dev(table))
+    assert np.array_equal(host(out).view(np.uint8), orc.input_embedding(ids, table).view(np.uint8))
+
+
+def test_input_embedding_bad_id_is_flagged_not_faulted(ops, orc, rng):
+    from inferspore_b200 import capi
+
+    table = rng.standard_normal((10, 64), dtype=np.float32)
+    ids = np.array([1, 10, -1, 9], np.int32)
+    out = torch.full((4, 64), 5.0, device="cuda:0")
+    ops.launchInputEmbedding(dev(ids), out, dev(table))
+    torch.cuda.synchronize()
+    assert capi.device_status(clear=True) & capi.DEV_BAD_TOKEN_ID
+    assert np.array_equal(host(out), orc.input_embedding(ids, table))
+    assert capi.device_status() == 0
+
+
+# ---- QKV bias + RoPE + transpose --------------------------------------------------------------------------
+
+def _rope_inputs(rng, dtype, batch, seq, heads, kv_heads, d, lens, hist):
+    lens = np.asarray(lens)
+    token_num = int(lens.sum())
+    padding_offset = np.concatenate([np.full(n, b * seq - lens[:b].sum(), np.int32) for b, n in enumerate(lens)])
+    QKV = rng.standard_normal((token_num, heads + 2 * kv_heads, d), dtype=np.float32).astype(dtype)
+    bias = (rng.standard_normal((heads + 2 * kv_heads) * d) * 0.02).astype(dtype)
+    return QKV, bias, padding_offset.astype(np.int32), np.asarray(hist, np.int32), lens.astype(np.int32)
+
+
+def _pair_magnitude(QKV, bias, padding_offset, batch, seq, heads, kv_heads):
+    """|x0| + |x1| of every rotation pair, scattered like the outputs: the scale the fp32
+    rounding error of c*x0 - s*x1 is proportional to when the two terms cancel."""
+    x = QKV.astype(np.float32)
+    if bias is not None:
+        x = x + bias.astype(np.float32).reshape(1, -1, x.shape[2])
+    half = x.shape[2] // 2
+    mag = np.abs(x[..., :half]) + np.abs(x[..., half:])
+    mag = np.concatenate([mag, mag], -1)
+    dst = np.arange(x.shape[0]) + padding_offset
+    out_q = np.zeros((batch, heads, seq, x.shape[2]), np.float32)
+    out_k = np.zeros((batch, kv_heads, seq, x.shape[2]), np.float32)
+    out_q[dst // seq, :, dst % seq] = mag[:, :heads]
+    out_k[dst // seq, :, dst % seq] = mag[:, heads:heads + kv_heads]
+    return out_q, out_k
+
+
+ROPE_CASES = [
+    # batch, seq, heads, kv_heads, d, rot, lens, hist
+    (1, 32, 32, 32, 128, 128, [32], [0]),
+    (3, 5, 2, 2, 8, 8, [3, 3, 3], [0, 0, 0]),
+    (2, 16, 8, 2, 128, 128, [16, 9], [7, 4000]),      # GQA, history, ragged
+    (2, 7, 4, 4, 64, 32, [7, 1], [0, 5]),             # partial rotary dim
+    (4, 33, 5, 1, 128, 128, [33, 1, 17, 2], [1, 2, 3, 4095]),
+    (2, 6, 3, 3, 20, 20, [6, 5], [0, 1]),             # head size not a multiple of the vector width
+]
+
+
+@pytest.mark.parametrize("case", ROPE_CASES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_qkv_rope_transpose_f32(ops, orc, rng, case, with_bias):
+    batch, seq, heads, kv_heads, d, rot, lens, hist = case
+    QKV, bias, po, hl, il = _rope_inputs(rng, np.float32, batch, seq, heads, kv_heads, d, lens, hist)
+    bias = bias if with_bias else None
+    sentinel = 777.0
+    q = torch.full((batch, heads, seq, d), sentinel, device="cuda:0")
+    k = torch.full((batch, kv_heads, seq, d), sentinel, device="cuda:0")
+    v = torch.full((batch, kv_heads, seq, d), sentinel, device="cuda:0")
+    ops.launchAddFusedQKVBiasTransposeAndRoPE(q, k, v, dev(QKV), None if bias is None else dev(bias), dev(po), dev(hl),
+                                              dev(il), rot, 10000.0)
+    wq, wk, wv, _, _ = orc.qkv_bias_rope_transpose(QKV, bias, po, hl, batch, seq, heads, kv_heads, rot, 10000.0,
+                                                   fill=sentinel)
+    mq, mk = _pair_magnitude(QKV, bias, po, batch, seq, heads, kv_heads)
+    # c*x0 - s*x1 can cancel: the error is relative to |x0| + |x1| (an fma on one side and two
+    # roundings on the other already differ by an ulp of the larger term), hence the floor.
+    assert_close_f32(host(q), wq, floor=0.1 * mq, what="q")
+    assert_close_f32(host(k), wk, floor=0.1 * mk, what="k")
+    assert np.array_equal(host(v), wv)  # copy, or one IEEE add with the bias
+
+
+@pytest.mark.parametrize("case", ROPE_CASES)
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_qkv_rope_transpose_f16(ops, orc, rng, case, with_bias):
+    batch, seq, heads, kv_heads, d, rot, lens, hist = case
+    QKV, bias, po, hl, il = _rope_inputs(rng, np.float16, batch, seq, heads, kv_heads, d, lens, hist)
+    bias = bias if with_bias else None
+    mk16 = lambda *s: torch.full(s, 777.0, dtype=torch.float16, device="cuda:0")
+    q, k, v = mk16(batch, heads, seq, d), mk16(batch, kv_heads, seq, d), mk16(batch, kv_heads, seq, d)
+    ops.launchAddFusedQKVBiasTransposeAndRoPE(q, k, v, dev(QKV), None if bias is None else dev(bias), dev(po), dev(hl),
+                                              dev(il), rot, 10000.0)
+    wq, wk, wv, q32, k32 = orc.qkv_bias_rope_transpose(QKV, bias, po, hl, batch, seq, heads, kv_heads, rot, 10000.0,
+                                                       fill=777.0)
+    assert_close_f16(host(q), q32, wq, "q f16")
+    assert_close_f16(host(k), k32, wk, "k f16")
+    assert np.array_equal(host(v).view(np.uint16), wv.view(np.uint16))
+
+
+def test_qkv_rope_norm_preserved_and_llama_shape(ops, orc, rng):
+    """Llama-2-7B prefill shape (one sequence of 512): rotation preserves every pair's norm."""
+    batch, seq, H, d = 1, 512, 32, 128
+    QKV, _, po, hl, il = _rope_inputs(rng, np.float32, batch, seq, H, H, d, [seq], [0])
+    q = torch.empty((batch, H, seq, d), device="cuda:0")
+    k, v = torch.empty_like(q), torch.empty_like(q)
+    ops.launchAddFusedQKVBiasTransposeAndRoPE(q, k, v, dev(QKV), None, dev(po), dev(hl), dev(il), 128, 10000.0)
+    qh = host(q).astype(np.float64)
+    got = qh[..., :64] ** 2 + qh[..., 64:] ** 2
+    x = QKV[:, :H].astype(np.float64).reshape(seq, H, d).transpose(1, 0, 2)[None]
+    want = x[..., :64] ** 2 + x[..., 64:] ** 2
+    assert np.allclose(got, want, rtol=1e-5, atol=1e-9)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("batch,heads,kv_heads,d,rot,step", [(1, 32, 32, 128, 128, 17), (5, 8, 2, 64, 32, 4096),
+                                                             (2, 3, 3, 10, 10, 1)])
+def test_rope_decode(ops, orc, rng, dtype, batch, heads, kv_heads, d, rot, step):
+    qkv = rng.standard_normal((batch, heads + 2 * kv_heads, d), dtype=np.float32).astype(dtype)
+    dq = dev(qkv)
+    ops.launchRoPE(dq, step, heads, kv_heads, rot, 10000.0)
+    want, unr = orc.rope_decode(qkv, heads, kv_heads, step, rot, 10000.0)
+    if dtype == np.float32:
+        half = d // 2
+        x = qkv.astype(np.float32)
+        mag = np.abs(x[..., :half]) + np.abs(x[..., half:])
+        assert_close_f32(host(dq), want, floor=0.1 * np.concatenate([mag, mag], -1), what="decode rope")
+    else:
+        assert_close_f16(host(dq), unr, want, "decode rope f16")
+    # v heads untouched
+    assert np.array_equal(host(dq)[:, heads + kv_heads:].view(np.uint8), qkv[:, heads + kv_heads:].view(np.uint8))
+
+
+# ---- SiLU * up ---------------------------------------------------------------------------------------------------
+
+ACT_SHAPES = [(16, 11008), (1, 8), (3, 7), (5, 1001), (64, 4096), (1, 27648), (130, 344)]
+
+
+@pytest.mark.parametrize("rows,inter", ACT_SHAPES)
+def test_silu_mul_f32(ops, orc, rng, rows, inter):
+    inp = (rng.standard_normal((rows, 2, inter), dtype=np.float32) * 3)
+    inp.flat[:6] = [0.0, -0.0, 30.0, -30.0, 80.0, -80.0][: min(6, inp.size)]
+    out = torch.empty((rows, inter), device="cuda:0")
+    ops.launchAct(dev(inp), out)
+    want, _ = orc.silu_mul(inp)
+    assert_close_f32(host(out), want, floor=1e-30, what="silu*up f32")
+
+
+@pytest.mark.parametrize("rows,inter", ACT_SHAPES)
+def test_silu_mul_f16(ops, orc, rng, rows, inter):
+    inp = randn16(rng, (rows, 2, inter), 2.0)
+    out = torch.empty((rows, inter), dtype=torch.float16, device="cuda:0")
+    ops.launchAct(dev(inp), out)
+    want, want32 = orc.silu_mul(inp)
+    _, _, same = assert_close_f16(host(out), want32, want, "silu*up f16")
+    assert same > 0.99
+
+
+# ---- KV concat ------------------------------------------------------------------------------------------------------
+
+CONCAT_CASES = [
+    # layers, batch, heads, max_q, max_seq, d, layer
+    (1, 1, 2, 16, 32, 8, 0),
+    (3, 4, 2, 5, 40, 128, 2),
+    (2, 64, 32, 1, 64, 128, 1),       # decode shape (short cache)
+    (2, 3, 4, 7, 19, 20, 1),          # head size not a multiple of the vector width (fp32 ok, fp16 scalar path)
+    (1, 2, 1, 9, 9, 3, 0),
+]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("case", CONCAT_CASES)
+def test_concat_kv_bit_exact(ops, orc, rng, dtype, case):
+    layers, batch, heads, max_q, max_seq, d, layer = case
+    k_src = rng.standard_normal((batch, heads, max_q, d), dtype=np.float32).astype(dtype)
+    v_src = rng.standard_normal((batch, heads, max_q, d), dtype=np.float32).astype(dtype)
+    cur = rng.integers(0, max_q + 1, batch).astype(np.int32)
+    cur[0] = max_q
+    hist = np.array([rng.integers(0, max_seq - c + 1) for c in cur], np.int32)
+    k_dst = rng.standard_normal((layers, batch, heads, max_seq, d), dtype=np.float32).astype(dtype)
+    v_dst = rng.standard_normal((layers, batch, heads, max_seq, d), dtype=np.float32).astype(dtype)
+    dk, dv = dev(k_dst), dev(v_dst)
+    ops.launchConcatKVCache(dev(k_src), dev(v_src), layer, dev(cur), dev(hist), dk, dv)
+    assert np.array_equal(host(dk).view(np.uint8), orc.concat_kv(k_dst, k_src, cur, hist, layer).view(np.uint8))
+    assert np.array_equal(host(dv).view(np.uint8), orc.concat_kv(v_dst, v_src, cur, hist, layer).view(np.uint8))
+
+
+def test_concat_kv_reference_fixture_4d_cache(ops, rng):
+    # tests/unittests/test_concat_kv.cu: src = 1, history 1, cur 16, 4-D single-layer cache
+    k_src = torch.ones((1, 2, 16, 8), device="cuda:0")
+    kd = torch.full((1, 2, 32, 8), -7.0, device="cuda:0")
+    vd = torch.full((1, 2, 32, 8), -7.0, device="cuda:0")
+    ops.launchConcatKVCache(k_src, k_src, 0, dev(np.array([16], np.int32)), dev(np.array([1], np.int32)), kd, vd)
+    for t in (host(kd), host(vd)):
+        assert np.all(t[0, :, 1:17] == 1.0) and np.all(t[0, :, 0] == -7.0) and np.all(t[0, :, 17:] == -7.0)
+
+
+def test_concat_kv_overrun_is_flagged_and_clamped(ops, orc, rng):
+    from inferspore_b200 import capi
+
+    k_src = rng.standard_normal((2, 1, 4, 8), dtype=np.float32)
+    k_dst = np.zeros((1, 2, 1, 6, 8), np.float32)
+    cur, hist = np.array([4, 4], np.int32), np.array([4, 0], np.int32)  # batch 0 would write rows 4..7 of 6
+    dk, dv = dev(k_dst), dev(k_dst)
+    ops.launchConcatKVCache(dev(k_src), dev(k_src), 0, dev(cur), dev(hist), dk, dv)
+    torch.cuda.synchronize()
+    assert capi.device_status(clear=True) & capi.DEV_KV_OVERRUN
+    assert np.array_equal(host(dk), orc.concat_kv(k_dst, k_src, cur, hist, 0))
+
+
+# ---- softmax --------------------------------------------------------------------------------------------------------------
+
+SOFTMAX_CASES = [
+    # batch, heads, q_len, k_len
+    (1, 2, 8, 8), (2, 3, 5, 64), (2, 4, 16, 512), (1, 2, 3, 1000), (4, 8, 1, 4096), (1, 1, 2, 8192),
+    (1, 2, 3, 33), (2, 2, 2, 1), (1, 1, 1, 16384), (1, 3, 7, 264), (1, 1, 2, 20000),
+]
+
+
+def _causal_mask(rng, batch, q_len, k_len, dtype):
+    lens = rng.integers(1, k_len + 1, batch)
+    mask = np.zeros((batch, q_len, k_len), dtype)
+    for b in range(batch):
+        for qi in range(q_len):
+            mask[b, qi, : max(1, lens[b] - (q_len - 1 - qi))] = 1
+    return mask
+
+
+@pytest.mark.parametrize("case", SOFTMAX_CASES)
+def test_softmax_f32(ops, orc, rng, case):
+    batch, heads, q_len, k_len = case
+    qk = rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32) * 3
+    mask = _causal_mask(rng, batch, q_len, k_len, np.float32)
+    out = torch.empty(qk.shape, device="cuda:0")
+    ops.launchScaleMaskAndSoftmax(dev(qk), dev(mask), out, 1.0 / np.sqrt(128.0))
+    want, _ = orc.scale_mask_softmax(qk, mask, np.float32(1.0 / np.sqrt(128.0)))
+    got = host(out)
+    assert_close_f32(got, want, floor=1e-30, what="softmax f32")
+    assert np.all(got[np.broadcast_to(mask[:, None] == 0, got.shape)] == 0.0)
+
+
+@pytest.mark.parametrize("case", SOFTMAX_CASES)
+def test_softmax_f16(ops, orc, rng, case):
+    batch, heads, q_len, k_len = case
+    qk = randn16(rng, (batch, heads, q_len, k_len), 3.0)
+    mask = _causal_mask(rng, batch, q_len, k_len, np.float16)
+    out = torch.empty(qk.shape, dtype=torch.float16, device="cuda:0")
+    ops.launchScaleMaskAndSoftmax(dev(qk), dev(mask), out, 1.0 / np.sqrt(128.0))
+    want, want32 = orc.scale_mask_softmax(qk, mask, np.float32(1.0 / np.sqrt(128.0)))
+    err, over, same = assert_close_f16(host(out), want32, want, "softmax f16")
+    assert over == 0 and err < 3e-4  # outputs are in [0, 1]: half spacing is at most 2^-11 there
+    rows = host(out).astype(np.float64).sum(-1)
+    assert np.all(np.abs(rows - 1.0) < 5e-3)
+
+
+def test_softmax_fully_masked_rows_are_zero_and_in_place(ops, orc, rng):
+    qk = rng.standard_normal((2, 2, 4, 128), dtype=np.float32)
+    mask = np.ones((2, 4, 128), np.float32)
+    mask[1, 2] = 0
+    d = dev(qk)
+    ops.launchScaleMaskAndSoftmax(d, dev(mask), d, 0.5)  # attn_score aliases qk
+    want, _ = orc.scale_mask_softmax(qk, mask, 0.5)
+    assert_close_f32(host(d), want, floor=1e-30, what="in-place softmax")
+    assert np.all(host(d)[1, :, 2] == 0.0)
+
+
+# ---- top-K and sampling --------------------------------------------------------------------------------------------------------
+
+def _topk_run(ops, probs, K, slices=8, index_offset=0, uniform=None, temperature=1.0):
+    rows = probs.shape[0]
+    tdt = torch.float16 if probs.dtype == np.float16 else torch.float32
+    sc_i = torch.full((rows, slices, K), -5, dtype=torch.int32, device="cuda:0")
+    sc_v = torch.zeros((rows, slices, K), dtype=tdt, device="cuda:0")
+    f_i = torch.full((rows, K), -5, dtype=torch.int32, device="cuda:0")
+    f_v = torch.zeros((rows, K), dtype=tdt, device="cuda:0")
+    picked = torch.full((rows,), -9, dtype=torch.int32, device="cuda:0") if uniform is not None else None
+    ops.launchTopKforBeamSearch(dev(probs), sc_i, sc_v, f_i, f_v, index_offset,
+                                None if uniform is None else dev(uniform), temperature, picked)
+    return host(f_i), host(f_v), None if picked is None else host(picked)
+
+
+TOPK_CASES = [(256, 32000, 50), (3, 32000, 5), (7, 1000, 1), (4, 50, 50), (4, 30, 50), (2, 128256, 50), (5, 4097, 64),
+              (3, 32001, 50), (2, 32000, 256), (1, 7, 3), (9, 5000, 17)]
+
+
+@pytest.mark.parametrize("rows,vocab,K", TOPK_CASES)
+def test_topk_f32_bit_exact(ops, orc, rng, rows, vocab, K):
+    probs = (rng.standard_normal((rows, vocab), dtype=np.float32) * 2)
+    got_i, got_v, _ = _topk_run(ops, probs, K)
+    want_i, want_v = orc.topk(probs, K)
+    assert np.array_equal(got_i, want_i)
+    assert np.array_equal(got_v.view(np.uint32), want_v.view(np.uint32))
+
+
+@pytest.mark.parametrize("rows,vocab,K", [(16, 32000, 50), (3, 999, 10)])
+def test_topk_f16_bit_exact_with_many_ties(ops, orc, rng, rows, vocab, K):
+    probs = randn16(rng, (rows, vocab), 2.0)  # half has few distinct values near the top: ties everywhere
+    got_i, got_v, _ = _topk_run(ops, probs, K)
+    want_i, want_v = orc.topk(probs, K)
+    assert np.array_equal(got_i, want_i)
+    assert np.array_equal(got_v.view(np.uint16), want_v.view(np.uint16))
+
+
+@pytest.mark.parametrize("fill", ["zeros", "const", "two_values", "neg_zero_mix", "inf", "ramp_down", "ramp_up"])
+def test_topk_adversarial_rows(ops, orc, rng, fill):
+    rows, vocab, K = 3, 32000, 50
+    probs = np.zeros((rows, vocab), np.float32)
+    if fill == "const":
+        probs[:] = 1.25
+    elif fill == "two_values":
+        probs[:] = rng.integers(0, 2, (rows, vocab)).astype(np.float32)
+    elif fill == "neg_zero_mix":
+        probs[:] = np.where(rng.integers(0, 2, (rows, vocab)) == 1, 0.0, -0.0).astype(np.float32)
+    elif fill == "inf":
+        probs[:] = rng.standard_normal((rows, vocab))
+        probs[:, 100:140] = np.inf
+        probs[:, 7] = -np.inf
+    elif fill == "ramp_down":
+        probs[:] = -np.arange(vocab, dtype=np.float32)
+    elif fill == "ramp_up":
+        probs[:] = np.arange(vocab, dtype=np.float32)
+    got_i, got_v, _ = _topk_run(ops, probs, K)
+    want_i, want_v = orc.topk(probs, K)
+    assert np.array_equal(got_i, want_i)
+    assert np.array_equal(got_v.view(np.uint32), want_v.view(np.uint32))
+
+
+def test_topk_scratch_too_small_or_k_too_large_is_an_error(ops, rng):
+    from inferspore_b200 import capi
+
+    probs = dev(rng.standard_normal((2, 400000), dtype=np.float32))
+    with pytest.raises(capi.IsporeError):  # one slice of 400000 elements does not fit shared memory
+        _topk_run(ops, host(probs), 5, slices=1)
+    with pytest.raises(capi.IsporeError):
+        _topk_run(ops, host(probs)[:, :100], 257)
+
+
+def test_topk_vocab_sharded_merge_equals_unsharded(ops, orc, rng):
+    rows, vocab, K, shards = 32, 32000, 50, 8
+    probs = (rng.standard_normal((rows, vocab), dtype=np.float32) * 2)
+    probs[:, ::97] = probs[:, 5:6]  # ties across shards
+    want_i, want_v = orc.topk(probs, K)
+    per = vocab // shards
+    cand_i, cand_v = [], []
+    for s in range(shards):
+        i, v, _ = _topk_run(ops, np.ascontiguousarray(probs[:, s * per:(s + 1) * per]), K, index_offset=s * per)
+        cand_i.append(i), cand_v.append(v)
+    ci, cv = np.stack(cand_i, 1), np.stack(cand_v, 1)  # [rows, shards, K]: what an all-gather delivers
+    f_i = torch.empty((rows, K), dtype=torch.int32, device="cuda:0")
+    f_v = torch.empty((rows, K), dtype=torch.float32, device="cuda:0")
+    ops.launchTopKMerge(dev(ci), dev(cv), f_i, f_v)
+    assert np.array_equal(host(f_i), want_i) and np.array_equal(host(f_v), want_v)
+
+
+@pytest.mark.parametrize("temperature", [1.0, 0.7, 2.5])
+def test_sampling_fused_and_standalone(ops, orc, rng, temperature):
+    rows, vocab, K = 256, 32000, 50
+    probs = (rng.standard_normal((rows, vocab), dtype=np.float32) * 2)
+    u = rng.random(rows, dtype=np.float32)
+    got_i, got_v, picked = _topk_run(ops, probs, K, uniform=u, temperature=temperature)
+    want_i, want_v = orc.topk(probs, K)
+    assert np.array_equal(got_i, want_i)
+    want_pick, margin = orc.sampling(want_i, want_v, u, temperature)
+    # a draw may legitimately differ only if u*S sits on a CDF boundary (expf differs in the last ulp)
+    differ = picked != want_pick
+    assert np.all(margin[differ] < 1e-6), f"{differ.sum()} picks differ away from a CDF boundary"
+    assert differ.sum() <= 2
+    out = torch.empty(rows, dtype=torch.int32, device="cuda:0")
+    ops.launchSampling(dev(got_i), dev(got_v), dev(u), out, temperature)
+    assert np.array_equal(host(out), picked)

@@ -1,0 +1,183 @@
+"""The oracle against the closed-form fixtures of the reference's own unit tests.
+
+Each test rebuilds the inputs a reference test constructs (file:line cited) and
+checks the oracle against the value that test's arithmetic implies.  CPU only.
+"""
+import math
+
+import numpy as np
+import pytest
+
+
+def test_half_conversion_matches_numpy(orc):
+    # every finite half pattern round-trips, and float->half agrees with numpy's RNE
+    lib = orc.lib()
+    bits = np.arange(0, 0x10000, dtype=np.uint32).astype(np.uint16)
+    f = bits.view(np.float16).astype(np.float32)
+    for b in list(range(0, 0x10000, 37)) + [0x0001, 0x03FF, 0x0400, 0x7BFF, 0x7C00, 0x8000, 0xFBFF, 0xFC00]:
+        got = lib.orc_half_to_float(b)
+        want = float(np.uint16(b).view(np.float16).astype(np.float32)) if True else 0
+        assert (math.isnan(got) and math.isnan(want)) or got == want, hex(b)
+    rng = np.random.default_rng(0)
+    xs = np.concatenate([
+        rng.standard_normal(20000).astype(np.float32) * rng.choice([1e-8, 1e-5, 1e-3, 1, 100, 7e4], 20000).astype(np.float32),
+        np.array([0.0, -0.0, 65504.0, 65519.9, 65520.0, 1e9, -1e9, 2.0 ** -24, 2.0 ** -25, 2.0 ** -25 * 1.0001,
+                  2.0 ** -14, 2.0 ** -14 * 0.9999, 1.00048828125, 1.0009765625 + 2.0 ** -12], np.float32),
+    ])
+    with np.errstate(over="ignore"):
+        want = xs.astype(np.float16).view(np.uint16)
+    got = np.array([lib.orc_float_to_half(float(x)) for x in xs], np.uint16)
+    assert np.array_equal(got, want)
+
+
+def test_norm_fixture(orc):
+    # tests/unittests/test_fused_addresidual_norm.cu:69-102: x = 1, r = 0, gamma = 1, eps = 0.5, [2, 32]
+    # -> every output = rsqrt(1 + 0.5)
+    x = np.ones((2, 32), np.float32)
+    r = np.zeros((2, 32), np.float32)
+    g = np.ones(32, np.float32)
+    out, new_r, _ = orc.add_residual_rmsnorm(x, r, None, g, 0.5)
+    assert np.allclose(out, 1.0 / math.sqrt(1.5), rtol=1e-6, atol=0)
+    assert np.array_equal(new_r, np.ones((2, 32), np.float32))
+    # same fixture in half storage
+    out16, new_r16, unr = orc.add_residual_rmsnorm(x.astype(np.float16), r.astype(np.float16), None,
+                                                   g.astype(np.float16), 0.5)
+    assert np.all(out16 == np.float16(1.0 / math.sqrt(1.5)))
+    assert np.allclose(unr, 1.0 / math.sqrt(1.5), rtol=1e-6)
+
+
+def test_act_fixture(orc):
+    # tests/unittests/test_act.cu:46-48,72-75: all-ones [16, 2, 11008] -> silu(1) * 1 = 1 / (1 + e^-1)
+    inp = np.ones((16, 2, 11008), np.float32)
+    out, _ = orc.silu_mul(inp)
+    assert np.allclose(out, 1.0 / (1.0 + math.exp(-1.0)), rtol=1e-6, atol=0)
+    out16, unr = orc.silu_mul(inp.astype(np.float16))
+    assert np.all(out16 == np.float16(1.0 / (1.0 + math.exp(-1.0))))
+
+
+def test_rope_fixture(orc):
+    # tests/unittests/test_bias_and_RoPE.cu:96-126,163-167: QKV = 32, history 0, bs 1, seq 32, 32 heads x 128,
+    # padding_offset 0 -> q[s,h,j] = 32(cos - sin), q[s,h,j+64] = 32(cos + sin), theta = s / 10000^(2j/128);
+    # v = 32.  (That test's bias of 2.0 is not applied by the reference kernel; checked without bias here,
+    # and with bias the same closed form holds for 34.)
+    bs, seq, H, d = 1, 32, 32, 128
+    QKV = np.full((bs * seq, 3 * H, d), 32.0, np.float32)
+    po = np.zeros(bs * seq, np.int32)
+    hist = np.zeros(bs, np.int32)
+    for bias, amp in ((None, 32.0), (np.full(3 * H * d, 2.0, np.float32), 34.0)):
+        q, k, v, _, _ = orc.qkv_bias_rope_transpose(QKV, bias, po, hist, bs, seq, H, H, 128, 10000.0)
+        s = np.arange(seq, dtype=np.float64)[:, None]
+        j = np.arange(64, dtype=np.float64)[None, :]
+        theta = s / 10000.0 ** (2 * j / 128.0)
+        lo = amp * (np.cos(theta) - np.sin(theta))
+        hi = amp * (np.cos(theta) + np.sin(theta))
+        for buf in (q, k):
+            assert np.allclose(buf[0, :, :, :64], lo[None], rtol=0, atol=2e-4)
+            assert np.allclose(buf[0, :, :, 64:], hi[None], rtol=0, atol=2e-4)
+        assert np.all(v == amp)
+
+
+def test_embedding_fixture(orc, rng):
+    # tests/unittests/test_input_embedding.cu:91-93,116-119: table[row, :] = row -> out[t, :] = ids[t]
+    vocab, hidden, tokens = 32000, 64, 64
+    table = np.repeat(np.arange(vocab, dtype=np.float32)[:, None], hidden, 1)
+    ids = rng.integers(0, vocab, tokens).astype(np.int32)
+    out = orc.input_embedding(ids, table)
+    assert np.array_equal(out, np.repeat(ids.astype(np.float32)[:, None], hidden, 1))
+    # half: integers are exact up to 2048
+    ids16 = rng.integers(0, 2048, tokens).astype(np.int32)
+    out16 = orc.input_embedding(ids16, table[:2048].astype(np.float16))
+    assert np.array_equal(out16.astype(np.float32), np.repeat(ids16.astype(np.float32)[:, None], hidden, 1))
+
+
+def test_concat_fixture(orc):
+    # tests/unittests/test_concat_kv.cu:16-20,57-67,91: src = 1, history 1, cur 16, max_seq 32, 2 heads x 8
+    # -> positions 1..16 of every head are 1, the rest untouched
+    src = np.ones((1, 2, 16, 8), np.float32)
+    dst = np.full((1, 1, 2, 32, 8), -7.0, np.float32)
+    out = orc.concat_kv(dst, src, [16], [1], 0)
+    assert np.all(out[0, 0, :, 1:17] == 1.0)
+    assert np.all(out[0, 0, :, 0] == -7.0) and np.all(out[0, 0, :, 17:] == -7.0)
+    # the 4-D single-layer cache the reference test passes (:81-82)
+    out4 = orc.concat_kv(dst[0], src, [16], [1], 0)
+    assert np.array_equal(out4, out[0])
+
+
+def test_softmax_fixture(orc):
+    # tests/unittests/test_mask_softmax.cu:28-35,60-65: qk[i] = i % 8, mask = 1, [1, 2, 8, 8], scale = rsqrt(4)
+    # -> every row = softmax(0, .5, ..., 3.5) with the 1e-6 in the denominator
+    qk = (np.arange(1 * 2 * 8 * 8) % 8).astype(np.float32).reshape(1, 2, 8, 8)
+    mask = np.ones((1, 8, 8), np.float32)
+    out, _ = orc.scale_mask_softmax(qk, mask, 0.5)
+    z = 0.5 * np.arange(8, dtype=np.float64)
+    e = np.exp(z - z.max())
+    want = e / (e.sum() + 1e-6)
+    assert np.allclose(out, want[None, None, None, :], rtol=1e-6, atol=0)
+    out16, unr = orc.scale_mask_softmax(qk.astype(np.float16), mask.astype(np.float16), 0.5)
+    assert np.allclose(unr, want[None, None, None, :], rtol=1e-6, atol=0)
+    assert np.array_equal(out16, unr.astype(np.float16))
+
+
+def test_softmax_fully_masked_row_is_zero(orc):
+    # m = max(FLT_MIN, ...) (attn_softmax_kernel.cu:77) => exp(-10000 - ~0) = 0 => 0 * (1 / 1e-6) = 0
+    qk = np.ones((1, 1, 2, 16), np.float32)
+    mask = np.ones((1, 2, 16), np.float32)
+    mask[0, 1] = 0
+    out, _ = orc.scale_mask_softmax(qk, mask, 1.0)
+    assert np.all(out[0, 0, 1] == 0.0)
+    assert abs(out[0, 0, 0].sum() - 1.0) < 1e-5
+
+
+def test_padding_offset_fixture_feeds_rope(orc, rng):
+    # tests/unittests/test_cal_paddingoffset.cu:31-33,57-59: lens [3,3,3], max_q_len 5 ->
+    # offsets 0,0,0,2,2,2,4,4,4.  Tokens land at (b, s) = (i // 3, i % 3); padded slots stay untouched.
+    po = np.array([0, 0, 0, 2, 2, 2, 4, 4, 4], np.int32)
+    QKV = rng.standard_normal((9, 6, 8), dtype=np.float32)  # 2 q heads + 2 k + 2 v, d = 8
+    q, k, v, _, _ = orc.qkv_bias_rope_transpose(QKV, None, po, np.zeros(3, np.int32), 3, 5, 2, 2, 8, 10000.0,
+                                                fill=123.0)
+    assert np.all(q[:, :, 3:] == 123.0) and np.all(v[:, :, 3:] == 123.0)
+    for i in range(9):
+        b, s = divmod(i, 3)
+        assert np.array_equal(v[b, :, s], QKV[i, 4:6])
+        if s == 0:  # position 0 => identity rotation
+            assert np.allclose(q[b, :, 0], QKV[i, 0:2]) and np.allclose(k[b, :, 0], QKV[i, 2:4])
+
+
+def test_topk_order_and_ties(orc):
+    probs = np.array([[1.0, 3.0, 3.0, -0.0, 0.0, 2.0, 3.0, -1.0]], np.float32)
+    ids, vals = orc.topk(probs, 6)
+    assert ids.tolist() == [[1, 2, 6, 5, 0, 3]]  # ties on lower index; -0.0 (idx 3) ties with +0.0 (idx 4)
+    assert vals[0, :5].tolist() == [3.0, 3.0, 3.0, 2.0, 1.0] and np.signbit(vals[0, 5])
+    ids, vals = orc.topk(probs, 8)
+    assert ids.tolist() == [[1, 2, 6, 5, 0, 3, 4, 7]]
+    ids, vals = orc.topk(probs[:, :3], 5)  # fewer elements than K
+    assert ids.tolist() == [[1, 2, 0, -1, -1]] and np.isneginf(vals[0, 3:]).all()
+
+
+def test_topk_merge_equals_topk(orc, rng):
+    probs = rng.standard_normal((5, 1000)).astype(np.float32)
+    probs[:, ::7] = probs[:, 3:4]  # plenty of exact ties across shards
+    K = 20
+    want_i, want_v = orc.topk(probs, K)
+    shard_i, shard_v = [], []
+    for s in range(4):
+        i, v = orc.topk(np.ascontiguousarray(probs[:, s * 250:(s + 1) * 250]), K, index_offset=s * 250)
+        shard_i.append(i), shard_v.append(v)
+    got_i, got_v = orc.topk_merge(np.stack(shard_i, 1), np.stack(shard_v, 1), K)
+    assert np.array_equal(got_i, want_i) and np.array_equal(got_v, want_v)
+
+
+def test_sampling_definition(orc):
+    ids = np.array([[10, 20, 30, 40]], np.int32)
+    vals = np.log(np.array([[4.0, 3.0, 2.0, 1.0]], np.float32))  # p ∝ 4,3,2,1 -> cdf .4 .7 .9 1
+    for u, want in ((0.0, 10), (0.39, 10), (0.41, 20), (0.69, 20), (0.71, 30), (0.95, 40), (0.999, 40)):
+        got, _ = orc.sampling(ids, vals, np.array([u], np.float32), 1.0)
+        assert got[0] == want, (u, got)
+    # temperature sharpens: T -> small picks the top id for any u < 1
+    got, _ = orc.sampling(ids, vals, np.array([0.9], np.float32), 0.05)
+    assert got[0] == 10
+    # empty slots are skipped
+    ids2 = np.array([[10, 20, -1, -1]], np.int32)
+    vals2 = np.array([[0.0, 0.0, -np.inf, -np.inf]], np.float32)
+    got, _ = orc.sampling(ids2, vals2, np.array([0.99], np.float32), 1.0)
+    assert got[0] == 20
