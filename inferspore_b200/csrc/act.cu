@@ -79,10 +79,10 @@ __global__ void silu_mul_scalar_kernel(T* __restrict__ out, const T* __restrict_
 
 template <typename T>
 int silu_dispatch(T* out, const T* in, int64_t rows, int64_t inter, cudaStream_t st) {
-    if (out == nullptr || in == nullptr) return fail(ISPORE_ENULL, "silu_mul: NULL buffer");
     if (rows < 0 || inter <= 0) return fail(ISPORE_ESHAPE, "silu_mul: bad shape [%lld,2,%lld]",
                                             (long long)rows, (long long)inter);
     if (rows == 0) return ISPORE_OK;
+    if (out == nullptr || in == nullptr) return fail(ISPORE_ENULL, "silu_mul: NULL buffer");
     constexpr int E = VecTraits<T>::kElems;
     constexpr int THREADS = 256, UNROLL = 4;
     if (inter % E == 0 && aligned16(out) && aligned16(in) && inter / E <= UINT32_MAX) {

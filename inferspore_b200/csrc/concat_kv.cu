@@ -88,8 +88,6 @@ int concat_dispatch(T* k_dst, T* v_dst, const T* k_src, const T* v_src, const in
                     const int32_t* hist_len, int64_t layer, int64_t num_layers, int64_t batch,
                     int64_t kv_heads, int64_t max_q_len, int64_t max_seq_len, int64_t head_size,
                     cudaStream_t st) {
-    if (!k_dst || !v_dst || !k_src || !v_src || !cur_len || !hist_len)
-        return fail(ISPORE_ENULL, "concat_kv: NULL buffer");
     if (batch < 0 || kv_heads <= 0 || max_q_len < 0 || max_seq_len <= 0 || head_size <= 0 ||
         layer < 0 || (num_layers > 0 && layer >= num_layers) || max_q_len > INT32_MAX)
         return fail(ISPORE_ESHAPE,
@@ -99,6 +97,8 @@ int concat_dispatch(T* k_dst, T* v_dst, const T* k_src, const T* v_src, const in
     if (batch * kv_heads > 65535)
         return fail(ISPORE_ELIMIT, "concat_kv: batch*kv_heads %lld > 65535", (long long)(batch * kv_heads));
     if (batch == 0 || max_q_len == 0) return ISPORE_OK;
+    if (!k_dst || !v_dst || !k_src || !v_src || !cur_len || !hist_len)
+        return fail(ISPORE_ENULL, "concat_kv: NULL buffer");
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "concat_kv: no device status word");
 

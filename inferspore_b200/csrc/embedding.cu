@@ -61,12 +61,12 @@ __global__ void embedding_gather_scalar_kernel(const int32_t* __restrict__ ids, 
 template <typename T>
 int embedding_dispatch(const int32_t* ids, T* out, const T* table, int64_t tokens, int64_t hidden,
                        int64_t vocab, cudaStream_t st) {
-    if (ids == nullptr || out == nullptr || table == nullptr)
-        return fail(ISPORE_ENULL, "input_embedding: NULL buffer");
     if (tokens < 0 || hidden <= 0 || vocab < 0)
         return fail(ISPORE_ESHAPE, "input_embedding: bad shape tokens=%lld hidden=%lld vocab=%lld",
                     (long long)tokens, (long long)hidden, (long long)vocab);
     if (tokens == 0) return ISPORE_OK;
+    if (ids == nullptr || out == nullptr || table == nullptr)
+        return fail(ISPORE_ENULL, "input_embedding: NULL buffer");
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "input_embedding: no device status word");
     constexpr int E = VecTraits<T>::kElems;

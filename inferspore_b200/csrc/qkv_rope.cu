@@ -220,8 +220,6 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
                  const int32_t* padding_offset, const int32_t* history_length, int64_t batch_size,
                  int64_t seq_len, int64_t token_num, int64_t head_num, int64_t kv_head_num,
                  int64_t head_size, int32_t rot_dim, float base, cudaStream_t st) {
-    if (!q_buf || !k_buf || !v_buf || !QKV || !padding_offset || !history_length)
-        return fail(ISPORE_ENULL, "qkv_bias_rope_transpose: NULL buffer");
     if (batch_size <= 0 || seq_len <= 0 || token_num < 0 || head_num <= 0 || kv_head_num <= 0 ||
         head_size <= 0 || head_size % 2 != 0 || head_num > 65535 || kv_head_num > 65535 ||
         head_size > 65536)
@@ -239,6 +237,8 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
     if (fill_denominators(&freq, rot_dim, base) != 0)
         return fail(ISPORE_ELIMIT, "qkv_bias_rope_transpose: rotary dim %d > %d", rot_dim, 2 * kMaxRotHalf);
     if (token_num == 0) return ISPORE_OK;
+    if (!q_buf || !k_buf || !v_buf || !QKV || !padding_offset || !history_length)
+        return fail(ISPORE_ENULL, "qkv_bias_rope_transpose: NULL buffer");
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "qkv_bias_rope_transpose: no device status word");
 
@@ -263,7 +263,6 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
 template <typename T>
 int rope_decode_dispatch(T* qkv, int64_t batch, int64_t head_num, int64_t kv_head_num,
                          int64_t head_size, int32_t step, int32_t rot_dim, float base, cudaStream_t st) {
-    if (!qkv) return fail(ISPORE_ENULL, "rope_decode: NULL buffer");
     if (batch < 0 || head_num <= 0 || kv_head_num <= 0 || head_size <= 0 || head_size % 2 != 0 ||
         head_num > 65535 || kv_head_num > 65535 || head_size > 65536 || batch > INT32_MAX)
         return fail(ISPORE_ESHAPE, "rope_decode: bad shape");
@@ -273,6 +272,7 @@ int rope_decode_dispatch(T* qkv, int64_t batch, int64_t head_num, int64_t kv_hea
     if (fill_denominators(&freq, rot_dim, base) != 0)
         return fail(ISPORE_ELIMIT, "rope_decode: rotary dim %d > %d", rot_dim, 2 * kMaxRotHalf);
     if (batch == 0) return ISPORE_OK;
+    if (!qkv) return fail(ISPORE_ENULL, "rope_decode: NULL buffer");
     constexpr int THREADS = 256;
     rope_decode_kernel<T, THREADS><<<static_cast<int>(batch), THREADS, 0, st>>>(
         qkv, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2,

@@ -166,11 +166,11 @@ int launch_regs(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t to
 template <typename T>
 int rmsnorm_dispatch(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens,
                      int64_t hidden, ResidualMode mode, cudaStream_t st) {
-    if (x == nullptr || gamma == nullptr) return fail(ISPORE_ENULL, "rmsnorm: decoder_out/gamma is NULL");
     if (tokens < 0 || hidden <= 0) return fail(ISPORE_ESHAPE, "rmsnorm: bad shape [%lld, %lld]",
                                                (long long)tokens, (long long)hidden);
     if (hidden > INT32_MAX) return fail(ISPORE_ELIMIT, "rmsnorm: hidden %lld too large", (long long)hidden);
-    if (tokens == 0) return ISPORE_OK;
+    if (tokens == 0) return ISPORE_OK;  // an empty tensor may legitimately carry a NULL pointer
+    if (x == nullptr || gamma == nullptr) return fail(ISPORE_ENULL, "rmsnorm: decoder_out/gamma is NULL");
     if (mode != ResidualMode::kNone && r == nullptr) mode = ResidualMode::kNone;
 
     constexpr int E = VecTraits<T>::kElems;

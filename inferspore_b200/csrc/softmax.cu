@@ -192,11 +192,11 @@ int launch_regs(T* score, const T* qk, const T* mask, int64_t total_rows, int64_
 template <typename T>
 int softmax_dispatch(T* score, const T* qk, const T* mask, int64_t batch, int64_t heads, int64_t q_len,
                      int64_t k_len, float scale, cudaStream_t st) {
-    if (!score || !qk || !mask) return fail(ISPORE_ENULL, "scale_mask_softmax: NULL buffer");
     if (batch < 0 || heads <= 0 || q_len <= 0 || k_len <= 0 || q_len > INT32_MAX)
         return fail(ISPORE_ESHAPE, "scale_mask_softmax: bad shape [%lld,%lld,%lld,%lld]",
                     (long long)batch, (long long)heads, (long long)q_len, (long long)k_len);
     if (batch == 0) return ISPORE_OK;
+    if (!score || !qk || !mask) return fail(ISPORE_ENULL, "scale_mask_softmax: NULL buffer");
     const int64_t total_rows = batch * heads * q_len;
     const int64_t rows_per_batch = heads * q_len;
     constexpr int E = VecTraits<T>::kElems;

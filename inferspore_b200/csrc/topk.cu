@@ -335,14 +335,14 @@ template <typename T>
 int merge_dispatch(const int32_t* cand_ids, const T* cand_vals, int64_t rows, int32_t lists,
                    int32_t list_stride, int32_t K, int32_t* final_ids, T* final_vals,
                    const float* uniform, float temperature, int32_t* sampled_ids, cudaStream_t st) {
-    if (!cand_ids || !cand_vals || !final_ids || !final_vals) return fail(ISPORE_ENULL, "topk_merge: NULL buffer");
-    if (uniform != nullptr && sampled_ids == nullptr) return fail(ISPORE_ENULL, "topk_merge: uniform given without sampled_ids");
     if (int rc = check_k("topk_merge", K)) return rc;
     if (rows < 0 || lists < 1 || rows > INT32_MAX) return fail(ISPORE_ESHAPE, "topk_merge: rows=%lld lists=%d", (long long)rows, lists);
     if (static_cast<int64_t>(lists) * K > kMergeCap)
         return fail(ISPORE_ELIMIT, "topk_merge: lists*K=%lld > %d", (long long)lists * K, kMergeCap);
     if (uniform != nullptr && !(temperature > 0.f)) return fail(ISPORE_ESHAPE, "topk_merge: temperature must be > 0");
     if (rows == 0) return ISPORE_OK;
+    if (!cand_ids || !cand_vals || !final_ids || !final_vals) return fail(ISPORE_ENULL, "topk_merge: NULL buffer");
+    if (uniform != nullptr && sampled_ids == nullptr) return fail(ISPORE_ENULL, "topk_merge: uniform given without sampled_ids");
     const size_t smem = static_cast<size_t>(lists) * K * sizeof(unsigned long long);
     topk_merge_kernel<T><<<static_cast<int>(rows), kTopkThreads, smem, st>>>(
         cand_ids, cand_vals, lists, list_stride, K, final_ids, final_vals, uniform, temperature, sampled_ids);
@@ -354,15 +354,15 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
                   T* scratch_vals, int32_t scratch_slices, int32_t* final_ids, T* final_vals,
                   int32_t index_offset, const float* uniform, float temperature, int32_t* sampled_ids,
                   cudaStream_t st) {
-    if (!probs || !final_ids || !final_vals) return fail(ISPORE_ENULL, "topk: NULL buffer");
-    if (!scratch_ids || !scratch_vals || scratch_slices < 1)
-        return fail(ISPORE_ESCRATCH, "topk: scratch [rows, slices>=1, K] is required");
     if (int rc = check_k("topk", K)) return rc;
     if (rows < 0 || vocab <= 0 || vocab > INT32_MAX || index_offset < 0 ||
         static_cast<int64_t>(index_offset) + vocab > INT32_MAX)
         return fail(ISPORE_ESHAPE, "topk: bad shape rows=%lld vocab=%lld offset=%d", (long long)rows,
                     (long long)vocab, index_offset);
     if (rows == 0) return ISPORE_OK;
+    if (!probs || !final_ids || !final_vals) return fail(ISPORE_ENULL, "topk: NULL buffer");
+    if (!scratch_ids || !scratch_vals || scratch_slices < 1)
+        return fail(ISPORE_ESCRATCH, "topk: scratch [rows, slices>=1, K] is required");
 
     constexpr int E = VecTraits<T>::kElems;
     // Slices of ~4K elements keep every SM busy at a few hundred rows; never more
@@ -397,11 +397,11 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
 template <typename T>
 int sampling_dispatch(const int32_t* ids, const T* vals, const float* uniform, int32_t* out, int64_t rows,
                       int32_t K, float temperature, cudaStream_t st) {
-    if (!ids || !vals || !uniform || !out) return fail(ISPORE_ENULL, "sampling: NULL buffer");
     if (int rc = check_k("sampling", K)) return rc;
     if (rows < 0) return fail(ISPORE_ESHAPE, "sampling: rows=%lld", (long long)rows);
     if (!(temperature > 0.f)) return fail(ISPORE_ESHAPE, "sampling: temperature must be > 0");
     if (rows == 0) return ISPORE_OK;
+    if (!ids || !vals || !uniform || !out) return fail(ISPORE_ENULL, "sampling: NULL buffer");
     sampling_kernel<T><<<static_cast<int>(ceil_div(rows, kTopkWarps)), kTopkThreads, 0, st>>>(
         ids, vals, uniform, out, rows, K, temperature);
     return check_launch("sampling_kernel");

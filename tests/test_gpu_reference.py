@@ -1,0 +1,234 @@
+"""The CUDA library against the REFERENCE's own GPU kernels and unit tests, on the same GPU.
+
+oracle/_ref/ holds the reference's kernel sources compiled for sm_100a (from where they lie in the
+reference tree, see oracle/build.py) behind a small C ABI, and the reference's six hot-path unit
+tests compiled unmodified against the drop-in headers.  Only reference kernels that are functional
+are run, and only on shapes they are safe for (the wrappers in oracle/ref_wrap/ refuse the rest):
+fp32 residual+RMSNorm, embedding, fp32 QKV+RoPE (the reference applies no bias), SiLU*up, KV concat,
+softmax.  Marked gpu.
+"""
+import ctypes as C
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from _util import assert_close_f16, assert_close_f32, dev, host, randn16
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parent.parent
+DROPIN = ROOT / "oracle" / "_ref" / "dropin"
+
+
+@pytest.fixture(scope="module")
+def ops(cuda):
+    from inferspore_b200 import ops as _ops
+
+    return _ops
+
+
+def _ref(orc, name):
+    if not orc.ref_available(name):
+        pytest.skip(f"oracle/_ref/{name} was not built (reference tree absent at build time)")
+    return orc.ref_lib(name)
+
+
+def _p(t):
+    return C.c_void_p(t.data_ptr())
+
+
+# ---- the reference's unit tests, unmodified, linked against this library ----------------------------
+
+def _run(name, *args):
+    exe = DROPIN / name
+    if not exe.exists():
+        pytest.skip("oracle/_ref/dropin was not built (reference tree absent at build time)")
+    proc = subprocess.run([str(exe), *args], capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    return proc.stdout
+
+
+def test_dropin_fused_addresidual_norm(cuda):
+    out = _run("test_fused_addresidual_norm")
+    assert "fused addres and rmsnorm passed" in out and "res is wrong" not in out
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_dropin_act(cuda, half):
+    out = _run("test_act", *(["1"] if half else []))
+    assert "test passed" in out and "res is wrong" not in out
+
+
+@pytest.mark.parametrize("fp32", [False, True])
+def test_dropin_input_embedding(cuda, fp32):
+    out = _run("test_input_embedding", *(["1"] if fp32 else []))
+    lines = out.splitlines()
+    if fp32:  # prints h_input[i] = id, later the first element of every output row: table[row, :] = row
+        ids = [float(l.split("=")[1]) for l in lines if l.startswith("h_input[")]
+        tail = [float(l) for l in lines[lines.index("printf h_output for check") + 1:]]
+        assert len(ids) == 64 and tail == ids
+    else:
+        assert "printf h_output for check" in out
+
+
+def test_dropin_concat_kv(cuda):
+    out = _run("test_concat_kv")
+    ks = [float(l.split("=")[1]) for l in out.splitlines() if l.startswith("res k")]
+    vs = [float(l.split("=")[1]) for l in out.splitlines() if l.startswith("res v")]
+    # printed range: flat indices 16 .. 511 of the [1, 2, 32, 8] cache; head h occupies 256*h ..;
+    # positions 1..16 of each head were written with 1.0 (history 1, 16 new tokens); cudaMalloc'ed
+    # memory is not cleared, so only the written span is checked.
+    assert len(ks) == 512 - 16 and len(vs) == len(ks)
+    for vals in (ks, vs):
+        flat = {i: v for i, v in zip(range(16, 512), vals)}
+        for h in range(2):
+            for pos in range(1, 17):
+                for j in range(8):
+                    idx = h * 256 + pos * 8 + j
+                    if idx >= 16:
+                        assert flat[idx] == 1.0, (h, pos, j)
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_dropin_mask_softmax(cuda, half):
+    out = _run("test_mask_softmax", *(["1"] if half else []))
+    vals = np.array([float(l.split("=")[1]) for l in out.splitlines() if l.startswith("attn score[")])
+    z = 0.5 * np.arange(8)
+    e = np.exp(z - z.max())
+    want = np.tile(e / (e.sum() + 1e-6), 16)
+    assert vals.shape == (128,)
+    assert np.allclose(vals, want, atol=2e-3 if half else 2e-6)
+
+
+def test_dropin_bias_and_rope(cuda):
+    out = _run("test_bias_and_RoPE")
+    assert "passed" in out
+    # q[0] = (32 + bias 2) * (cos 0 - sin 0): this library applies the bias the reference kernel drops
+    first = [l for l in out.splitlines() if l.startswith("after memcpyd2h, dq[0]")][0]
+    assert float(first.split("=")[1]) == 34.0
+
+
+# ---- this library vs the reference's GPU kernels on random data -----------------------------------------
+
+@pytest.mark.parametrize("tokens,hidden", [(64, 4096), (300, 1024), (7, 128)])
+def test_vs_reference_gpu_rmsnorm_f32(ops, orc, rng, tokens, hidden):
+    lib = _ref(orc, "libref_norm.so")
+    x = rng.standard_normal((tokens, hidden), dtype=np.float32)
+    r = rng.standard_normal((tokens, hidden), dtype=np.float32)
+    g = rng.uniform(0.5, 1.5, hidden).astype(np.float32)
+    b = (rng.standard_normal(hidden) * 0.1).astype(np.float32)
+    ox, orr, rx, rr, dg, db = dev(x), dev(r), dev(x), dev(r), dev(g), dev(b)
+    ops.launchFusedAddBiasResidualRMSNorm(orr, ox, db, dg, 1e-6)
+    assert lib.ref_gpu_fused_resid_rmsnorm_f32(_p(rr), _p(rx), _p(db), _p(dg), C.c_float(1e-6), tokens, hidden) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(orr), host(rr))
+    assert_close_f32(host(ox), host(rx), what="rmsnorm vs reference GPU kernel")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_vs_reference_gpu_embedding(ops, orc, rng, dtype):
+    lib = _ref(orc, "libref_embedding.so")
+    tokens, hidden, vocab = 300, 4096, 5000
+    table = (rng.standard_normal((vocab, hidden), dtype=np.float32) * 0.02).astype(dtype)
+    ids = rng.integers(0, vocab, tokens).astype(np.int32)
+    dt, di = dev(table), dev(ids)
+    ours, ref = torch.empty((tokens, hidden), dtype=dt.dtype, device="cuda:0"), torch.empty((tokens, hidden), dtype=dt.dtype, device="cuda:0")
+    ops.launchInputEmbedding(di, ours, dt)
+    fn = lib.ref_gpu_embedding_f32 if dtype == np.float32 else lib.ref_gpu_embedding_f16
+    fn(_p(di), _p(ref), _p(dt), tokens, hidden)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(ours).view(np.uint8), host(ref).view(np.uint8))
+
+
+def test_vs_reference_gpu_qkv_rope_f32(ops, orc, rng):
+    lib = _ref(orc, "libref_rope.so")
+    batch, seq, H, KV, d = 2, 40, 8, 8, 128
+    lens = np.array([40, 23])
+    T = int(lens.sum())
+    po = np.concatenate([np.full(n, b * seq - lens[:b].sum(), np.int32) for b, n in enumerate(lens)]).astype(np.int32)
+    hist = np.array([0, 1000], np.int32)
+    QKV = rng.standard_normal((T, H + 2 * KV, d), dtype=np.float32)
+    dQ, dpo, dh, dl = dev(QKV), dev(po), dev(hist), dev(lens.astype(np.int32))
+    mk = lambda h: torch.full((batch, h, seq, d), 5.0, device="cuda:0")
+    q, k, v, rq, rk, rv = mk(H), mk(KV), mk(KV), mk(H), mk(KV), mk(KV)
+    ops.launchAddFusedQKVBiasTransposeAndRoPE(q, k, v, dQ, None, dpo, dh, dl, 128, 10000.0)
+    assert lib.ref_gpu_qkv_rope_f32(_p(rq), _p(rk), _p(rv), _p(dQ), None, _p(dpo), _p(dh), _p(dl), batch, seq, T, H, KV, d,
+                                    128, C.c_float(10000.0)) == 0
+    torch.cuda.synchronize()
+    x = QKV.astype(np.float64)
+    mag = np.abs(x[..., :64]) + np.abs(x[..., 64:])
+    mag = np.concatenate([mag, mag], -1)
+    dst = np.arange(T) + po
+    mq = np.zeros((batch, H, seq, d)); mq[dst // seq, :, dst % seq] = mag[:, :H]
+    mkk = np.zeros((batch, KV, seq, d)); mkk[dst // seq, :, dst % seq] = mag[:, H:H + KV]
+    # the reference evaluates powf on the device (a few ulp from the host's), so theta itself can
+    # differ by ~1e-6 relative; at position 1000+ that is ~1e-3 rad * amplitude: compare with the
+    # error that implies, not with 1e-5.
+    gq, wq = host(q).astype(np.float64), host(rq).astype(np.float64)
+    gk, wk = host(k).astype(np.float64), host(rk).astype(np.float64)
+    pos = np.zeros((batch, 1, seq, 1)); pos[dst // seq, 0, dst % seq, 0] = hist[dst // seq] + dst % seq
+    bound_q = 1e-5 * np.maximum(np.abs(wq), 0.1 * mq) + 4e-7 * pos * mq
+    bound_k = 1e-5 * np.maximum(np.abs(wk), 0.1 * mkk) + 4e-7 * pos * mkk
+    assert np.all(np.abs(gq - wq) <= bound_q) and np.all(np.abs(gk - wk) <= bound_k)
+    assert np.array_equal(host(v), host(rv))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_vs_reference_gpu_act(ops, orc, rng, dtype):
+    lib = _ref(orc, "libref_act.so")
+    rows, inter = 64, 11008
+    inp = (rng.standard_normal((rows, 2, inter), dtype=np.float32) * 2).astype(dtype)
+    di = dev(inp)
+    ours, ref = torch.empty((rows, inter), dtype=di.dtype, device="cuda:0"), torch.empty((rows, inter), dtype=di.dtype, device="cuda:0")
+    ops.launchAct(di, ours)
+    (lib.ref_gpu_act_f32 if dtype == np.float32 else lib.ref_gpu_act_f16)(_p(di), _p(ref), rows, inter)
+    torch.cuda.synchronize()
+    if dtype == np.float32:
+        assert_close_f32(host(ours), host(ref), floor=1e-30, what="silu*up vs reference GPU kernel")
+    else:
+        # the reference rounds silu to half and multiplies in half (two roundings): within 2e-3 of ours
+        # except where a half cannot resolve that (|v| >= 4: spacing 2^-8)
+        a, b = host(ours).astype(np.float64), host(ref).astype(np.float64)
+        assert np.all(np.abs(a - b) <= np.maximum(2e-3, 2.0 ** (np.floor(np.log2(np.maximum(np.abs(b), 1e-8))) - 9)))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_vs_reference_gpu_concat(ops, orc, rng, dtype):
+    lib = _ref(orc, "libref_concat_softmax.so")
+    layers, batch, heads, max_q, max_seq, d, layer = 3, 4, 8, 16, 64, 128, 1
+    k_src = rng.standard_normal((batch, heads, max_q, d), dtype=np.float32).astype(dtype)
+    v_src = rng.standard_normal((batch, heads, max_q, d), dtype=np.float32).astype(dtype)
+    cur = np.array([16, 3, 0, 9], np.int32)
+    hist = np.array([0, 40, 5, 55], np.int32)
+    base = rng.standard_normal((layers, batch, heads, max_seq, d), dtype=np.float32).astype(dtype)
+    ok, ov, rk, rv = dev(base), dev(base), dev(base), dev(base)
+    dks, dvs, dc, dh = dev(k_src), dev(v_src), dev(cur), dev(hist)
+    ops.launchConcatKVCache(dks, dvs, layer, dc, dh, ok, ov)
+    fn = lib.ref_gpu_concat_kv_f32 if dtype == np.float32 else lib.ref_gpu_concat_kv_f16
+    assert fn(_p(dks), _p(dvs), layer, _p(dc), _p(dh), _p(rk), _p(rv), layers, batch, heads, max_q, max_seq, d) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(ok).view(np.uint8), host(rk).view(np.uint8))
+    assert np.array_equal(host(ov).view(np.uint8), host(rv).view(np.uint8))
+
+
+@pytest.mark.parametrize("dtype,k_len", [(np.float32, 512), (np.float32, 96), (np.float16, 4096), (np.float16, 512)])
+def test_vs_reference_gpu_softmax(ops, orc, rng, dtype, k_len):
+    lib = _ref(orc, "libref_concat_softmax.so")
+    batch, heads, q_len = 3, 4, 5
+    qk = (rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32) * 3).astype(dtype)
+    mask = np.ones((batch, q_len, k_len), dtype)
+    for b in range(batch):
+        mask[b, :, rng.integers(1, k_len):] = 0
+    dq, dm = dev(qk), dev(mask)
+    ours, ref = torch.empty_like(dq), torch.empty_like(dq)
+    ops.launchScaleMaskAndSoftmax(dq, dm, ours, 0.0883883)
+    fn = lib.ref_gpu_softmax_f32 if dtype == np.float32 else lib.ref_gpu_softmax_f16
+    assert fn(_p(dq), _p(dm), _p(ref), batch, heads, q_len, k_len, C.c_float(0.0883883)) == 0
+    torch.cuda.synchronize()
+    if dtype == np.float32:
+        assert_close_f32(host(ours), host(ref), floor=1e-30, what="softmax vs reference GPU kernel")
+    else:
+        # the reference computes scale*qk, the mask term and exp in half precision: 2e-3 absolute
+        assert np.max(np.abs(host(ours).astype(np.float32) - host(ref).astype(np.float32))) <= 2e-3
