@@ -234,7 +234,10 @@ ISPORE_API int ispore_scale_mask_softmax_f16(void* attn_score, const void* qk, c
  * Round 1 splits each row in `slices` (chosen by the library, <= scratch_slices)
  * and writes per-slice top-K lists to the caller's scratch
  * scratch_ids/scratch_vals [rows, scratch_slices, K] — the same scratch
- * tensors the reference launcher takes; round 2 merges them.  index_offset is
+ * tensors the reference launcher takes; round 2 merges them.  The scratch only
+ * bounds the number of slices: with scratch_slices <= 1 (or NULL scratch) one
+ * CTA walks each row and writes the final lists directly, which is correct for
+ * any vocab but leaves the GPU idle when there are few rows.  index_offset is
  * added to every emitted id (vocab-sharded callers pass the shard's first
  * column).  When uniform != NULL the merge also draws one id per row exactly
  * as ispore_sampling_* does and writes it to sampled_ids [rows]. */
@@ -252,7 +255,8 @@ ISPORE_API int ispore_topk_f16(const void* probs, int64_t rows, int64_t vocab, i
                                ispore_stream_t stream);
 
 /* Merge of `lists` candidate lists per row (cand_ids/cand_vals [rows, lists, K],
- * any order inside a list, id -1 = empty slot) into the global top-K with the
+ * id -1 = empty slot; lists sorted best-first, as ispore_topk_* emits them, merge
+ * by binary search, any other order is detected and ranked pairwise) into the global top-K with the
  * same total order.  This is round 2 above, exported because vocab-sharded
  * sampling all-gathers per-shard lists and merges them on every rank.
  * ref: src/kernels/topK.cu:48-74 (round 2). */

@@ -89,21 +89,21 @@ int silu_dispatch(T* out, const T* in, int64_t rows, int64_t inter, cudaStream_t
         const int64_t inter_vecs = inter / E;
         const int64_t total_vecs = rows * inter_vecs;
         const int64_t tiles = ceil_div(total_vecs, THREADS * UNROLL);
-        const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8 * 4;
-        const int grid = static_cast<int>(tiles < max_ctas ? tiles : max_ctas);
         // The input spans 2*total_vecs vectors, so 32-bit indexing needs that to fit.
-        if (total_vecs * 2 + static_cast<int64_t>(grid) * THREADS * UNROLL < (1ll << 32)) {
-            silu_mul_vec_kernel<T, uint32_t, THREADS, UNROLL><<<grid, THREADS, 0, st>>>(
+        const int64_t worst_grid = static_cast<int64_t>(sm_count()) * 8 * 64;
+        if (total_vecs * 2 + worst_grid * THREADS * UNROLL < (1ll << 32)) {
+            auto kernel = silu_mul_vec_kernel<T, uint32_t, THREADS, UNROLL>;
+            kernel<<<persistent_grid(kernel, THREADS, 0, tiles, tune(kTuneAct, 64)), THREADS, 0, st>>>(
                 out, in, static_cast<uint32_t>(total_vecs), static_cast<uint32_t>(inter_vecs));
         } else {
-            silu_mul_vec_kernel<T, uint64_t, THREADS, UNROLL><<<grid, THREADS, 0, st>>>(
+            auto kernel = silu_mul_vec_kernel<T, uint64_t, THREADS, UNROLL>;
+            kernel<<<persistent_grid(kernel, THREADS, 0, tiles, tune(kTuneAct, 64)), THREADS, 0, st>>>(
                 out, in, static_cast<uint64_t>(total_vecs), static_cast<uint32_t>(inter_vecs));
         }
         return check_launch("silu_mul_vec_kernel");
     }
     const int64_t blocks = ceil_div(rows * inter, 256);
-    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 16;
-    silu_mul_scalar_kernel<T><<<static_cast<int>(blocks < max_ctas ? blocks : max_ctas), 256, 0, st>>>(
+    silu_mul_scalar_kernel<T><<<persistent_grid(silu_mul_scalar_kernel<T>, 256, 0, blocks), 256, 0, st>>>(
         out, in, rows, inter);
     return check_launch("silu_mul_scalar_kernel");
 }

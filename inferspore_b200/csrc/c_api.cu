@@ -4,7 +4,9 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <map>
 #include <mutex>
+#include <utility>
 
 #include "common.cuh"
 
@@ -53,9 +55,52 @@ unsigned* device_status_ptr() {
     return g_status_addr[dev];
 }
 
+#ifdef ISPORE_TUNING
+static int g_tune[kTuneKeys] = {-1, -1, -1, -1, -1, -1, -1};
+int tune(int key, int dflt) { return (key >= 0 && key < kTuneKeys && g_tune[key] >= 0) ? g_tune[key] : dflt; }
+#endif
+
+int sm_count() {
+    static int cached[kMaxDevices] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kNumSMs;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = kNumSMs;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+int resident_ctas(const void* kernel, int threads, size_t dynamic_smem) {
+    static std::mutex mutex;
+    static std::map<std::pair<const void*, std::pair<int, size_t>>, int> cache[kMaxDevices];
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kNumSMs;
+    const auto key = std::make_pair(kernel, std::make_pair(threads, dynamic_smem));
+    std::lock_guard<std::mutex> lock(mutex);
+    auto it = cache[dev].find(key);
+    if (it != cache[dev].end()) return it->second;
+    int per_sm = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dynamic_smem) != cudaSuccess ||
+        per_sm <= 0) {
+        (void)cudaGetLastError();
+        per_sm = 1;
+    }
+    const int total = per_sm * sm_count();
+    cache[dev][key] = total;
+    return total;
+}
+
 }  // namespace ispore
 
 extern "C" {
+
+#ifdef ISPORE_TUNING
+__attribute__((visibility("default"))) void ispore_tune(int key, int value) {
+    if (key >= 0 && key < ispore::kTuneKeys) ispore::g_tune[key] = value;
+}
+#endif
 
 int ispore_version(void) { return 100; /* 0.1.0 */ }
 

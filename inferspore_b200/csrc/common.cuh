@@ -8,12 +8,34 @@
 
 namespace ispore {
 
-constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs; grids are sized in multiples of this
+constexpr int kNumSMs = 148;  // B200: 2 dies x 74 SMs (fallback when the device query fails)
 
 // ---- host-side status plumbing (c_api.cu owns the storage) -------------------
 int fail(int code, const char* fmt, ...);
 int check_launch(const char* what);
 unsigned* device_status_ptr();  // address of the per-device status word (device memory)
+int sm_count();                 // SMs of the current device (cached)
+// CTAs of `kernel` that are resident at once on the whole current device for the
+// given block size / dynamic shared memory (occupancy query, cached per kernel
+// and device).  Persistent grid-stride kernels launch exactly this many CTAs:
+// one more would wait for a free slot and start its whole share of the work late.
+int resident_ctas(const void* kernel, int threads, size_t dynamic_smem);
+
+// Launch-shape experiments: a build with -DISPORE_TUNING exports ispore_tune(key, value)
+// and dispatchers consult tune(key, default); the shipped build compiles this to the default.
+enum TuneKey { kTuneRmsnorm = 0, kTuneSoftmax, kTuneAct, kTuneEmbedding, kTuneQkv, kTuneConcat, kTuneTopk, kTuneKeys };
+#ifdef ISPORE_TUNING
+int tune(int key, int dflt);
+#else
+inline int tune(int, int dflt) { return dflt; }
+#endif
+
+template <typename Kernel>
+inline int persistent_grid(Kernel kernel, int threads, size_t dynamic_smem, int64_t work_items, int waves = 1) {
+    const int64_t cap = static_cast<int64_t>(waves) *
+                        resident_ctas(reinterpret_cast<const void*>(kernel), threads, dynamic_smem);
+    return static_cast<int>(work_items < cap ? (work_items > 0 ? work_items : 1) : cap);
+}
 
 // ---- storage-type traits ------------------------------------------------------
 // One 128-bit vector holds 4 floats or 8 halves.

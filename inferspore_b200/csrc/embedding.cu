@@ -73,15 +73,13 @@ int embedding_dispatch(const int32_t* ids, T* out, const T* table, int64_t token
     if (hidden % E == 0 && hidden / E <= INT32_MAX && aligned16(out) && aligned16(table)) {
         constexpr int THREADS = 256, UNROLL = 4;
         const int64_t blocks = ceil_div(tokens, THREADS / 32);
-        const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
-        embedding_gather_vec_kernel<THREADS, UNROLL>
-            <<<static_cast<int>(blocks < max_ctas ? blocks : max_ctas), THREADS, 0, st>>>(
+        auto kernel = embedding_gather_vec_kernel<THREADS, UNROLL>;
+        kernel<<<persistent_grid(kernel, THREADS, 0, blocks, tune(kTuneEmbedding, 16)), THREADS, 0, st>>>(
                 ids, reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(table), tokens,
                 static_cast<int>(hidden / E), vocab, status);
         return check_launch("embedding_gather_vec_kernel");
     }
-    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
-    embedding_gather_scalar_kernel<T><<<static_cast<int>(tokens < max_ctas ? tokens : max_ctas), 256, 0, st>>>(
+    embedding_gather_scalar_kernel<T><<<persistent_grid(embedding_gather_scalar_kernel<T>, 256, 0, tokens), 256, 0, st>>>(
         ids, out, table, tokens, hidden, vocab, status);
     return check_launch("embedding_gather_scalar_kernel");
 }

@@ -244,16 +244,25 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
 
     constexpr int THREADS = 256;
     constexpr int E = VecTraits<T>::kElems;
-    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
-    const int grid = static_cast<int>(token_num < max_ctas ? token_num : max_ctas);
     const bool vec_ok = head_size % (2 * E) == 0 && aligned16(q_buf) && aligned16(k_buf) &&
                         aligned16(v_buf) && aligned16(QKV) && (bias == nullptr || aligned16(bias));
     if (vec_ok) {
+        const int variant = tune(kTuneQkv, 127);
+        if (variant >= 10) {
+            constexpr int TH = 128;
+            const int grid = persistent_grid(qkv_rope_transpose_vec_kernel<T, TH>, TH, 0, token_num, variant - 9);
+            qkv_rope_transpose_vec_kernel<T, TH><<<grid, TH, 0, st>>>(
+                q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
+                token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
+            return check_launch("qkv_rope_transpose_vec_kernel");
+        }
+        const int grid = persistent_grid(qkv_rope_transpose_vec_kernel<T, THREADS>, THREADS, 0, token_num, variant + 1);
         qkv_rope_transpose_vec_kernel<T, THREADS><<<grid, THREADS, 0, st>>>(
             q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
             token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
         return check_launch("qkv_rope_transpose_vec_kernel");
     }
+    const int grid = persistent_grid(qkv_rope_transpose_scalar_kernel<T, THREADS>, THREADS, 0, token_num);
     qkv_rope_transpose_scalar_kernel<T, THREADS><<<grid, THREADS, 0, st>>>(
         q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len, token_num,
         (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);

@@ -20,67 +20,68 @@ enum class ResidualMode : int {
 };
 
 // Row held in registers: VPT 128-bit vectors per thread, THREADS threads per row.
-template <typename T, int VPT, int THREADS>
-__global__ void __launch_bounds__(THREADS)
+// Between the reduction and the scaled store a thread keeps its slice of the
+// pre-norm row PACKED in the storage type (for fp16 that is exactly the rounded
+// value the norm is defined on), which keeps the register count low enough for
+// MIN_BLOCKS CTAs per SM; gamma is re-read through L1 (it is 8 KB and shared by
+// every row) instead of occupying registers.
+template <typename T, int VPT, int THREADS, int MIN_BLOCKS>
+__global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __restrict__ bias,
                            const T* __restrict__ gamma, float eps, int64_t num_tokens,
                            int hidden_vecs, int hidden, int mode_i) {
     constexpr int kWarps = THREADS / 32;
+    constexpr int E = VecTraits<T>::kElems;
     const ResidualMode mode = static_cast<ResidualMode>(mode_i);
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     __shared__ float partial[2][kWarps];
-
-    // gamma slice of this thread, kept for every row.
-    uint4 g_raw[VPT];
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        g_raw[i] = (v < hidden_vecs) ? ld_keep(reinterpret_cast<const uint4*>(gamma) + v)
-                                     : make_uint4(0, 0, 0, 0);
-    }
+    const uint4* gamma_v = reinterpret_cast<const uint4*>(gamma);
+    const uint4* bias_v = reinterpret_cast<const uint4*>(bias);
 
     int parity = 0;
     for (int64_t row = blockIdx.x; row < num_tokens; row += gridDim.x, parity ^= 1) {
         uint4* xrow = reinterpret_cast<uint4*>(x) + row * hidden_vecs;
         uint4* rrow = reinterpret_cast<uint4*>(r) + row * hidden_vecs;
 
-        uint4 x_raw[VPT], r_raw[VPT];
+        uint4 s_raw[VPT], r_raw[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = tid + i * THREADS;
             if (v < hidden_vecs) {
-                x_raw[i] = ld_stream(xrow + v);
+                s_raw[i] = ld_stream(xrow + v);
                 if (mode == ResidualMode::kAdd) r_raw[i] = ld_stream(rrow + v);
             }
         }
 
-        Unpacked<T> s[VPT];
         float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = tid + i * THREADS;
             if (v < hidden_vecs) {
-                unpack(x_raw[i], s[i]);
+                Unpacked<T> s;
+                unpack(s_raw[i], s);
                 if (mode == ResidualMode::kAdd) {
                     Unpacked<T> rr;
                     unpack(r_raw[i], rr);
 #pragma unroll
-                    for (int e = 0; e < VecTraits<T>::kElems; ++e) s[i].v[e] += rr.v[e];
-                    round_to_storage(s[i]);
-                    st_stream(rrow + v, pack(s[i]));
+                    for (int e = 0; e < E; ++e) s.v[e] += rr.v[e];
+                    s_raw[i] = pack(s);  // rounds to the storage type: the new residual
+                    st_stream(rrow + v, s_raw[i]);
+                    unpack(s_raw[i], s);
                 } else if (mode == ResidualMode::kCopyOut) {
-                    st_stream(rrow + v, x_raw[i]);
+                    st_stream(rrow + v, s_raw[i]);
                 }
                 if (bias != nullptr) {
                     Unpacked<T> bb;
-                    unpack(ld_keep(reinterpret_cast<const uint4*>(bias) + v), bb);
+                    unpack(ld_keep(bias_v + v), bb);
 #pragma unroll
-                    for (int e = 0; e < VecTraits<T>::kElems; ++e) s[i].v[e] += bb.v[e];
-                    round_to_storage(s[i]);
+                    for (int e = 0; e < E; ++e) s.v[e] += bb.v[e];
+                    s_raw[i] = pack(s);
+                    unpack(s_raw[i], s);
                 }
 #pragma unroll
-                for (int e = 0; e < VecTraits<T>::kElems; ++e) acc = fmaf(s[i].v[e], s[i].v[e], acc);
+                for (int e = 0; e < E; ++e) acc = fmaf(s.v[e], s.v[e], acc);
             }
         }
 
@@ -96,11 +97,12 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
         for (int i = 0; i < VPT; ++i) {
             const int v = tid + i * THREADS;
             if (v < hidden_vecs) {
-                Unpacked<T> g;
-                unpack(g_raw[i], g);
+                Unpacked<T> s, g;
+                unpack(s_raw[i], s);
+                unpack(ld_keep(gamma_v + v), g);
 #pragma unroll
-                for (int e = 0; e < VecTraits<T>::kElems; ++e) s[i].v[e] = (g.v[e] * s[i].v[e]) * inv;
-                st_stream(xrow + v, pack(s[i]));
+                for (int e = 0; e < E; ++e) s.v[e] = (g.v[e] * s.v[e]) * inv;
+                st_stream(xrow + v, pack(s));
             }
         }
     }
@@ -149,17 +151,14 @@ rmsnorm_generic_kernel(T* __restrict__ x, T* __restrict__ r, const T* __restrict
     }
 }
 
-template <typename T, int VPT, int THREADS>
+template <typename T, int VPT, int THREADS, int MIN_BLOCKS>
 int launch_regs(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens, int64_t hidden,
                 ResidualMode mode, cudaStream_t st) {
     const int hidden_vecs = static_cast<int>(hidden / VecTraits<T>::kElems);
-    // Enough CTAs to fill every SM to its thread limit; rows beyond that are
-    // reached by the grid-stride loop so gamma is fetched once per CTA.
-    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * (2048 / THREADS);
-    const int grid = static_cast<int>(tokens < max_ctas ? tokens : max_ctas);
-    rmsnorm_row_in_regs_kernel<T, VPT, THREADS><<<grid, THREADS, 0, st>>>(
-        x, r, bias, gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden),
-        static_cast<int>(mode));
+    auto kernel = rmsnorm_row_in_regs_kernel<T, VPT, THREADS, MIN_BLOCKS>;
+    const int grid = persistent_grid(kernel, THREADS, 0, tokens, tune(kTuneConcat, 64));
+    kernel<<<grid, THREADS, 0, st>>>(x, r, bias, gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden),
+                                     static_cast<int>(mode));
     return check_launch("rmsnorm_row_in_regs_kernel");
 }
 
@@ -178,15 +177,37 @@ int rmsnorm_dispatch(T* x, T* r, const T* bias, const T* gamma, float eps, int64
                         (mode == ResidualMode::kNone || aligned16(r)) &&
                         (bias == nullptr || aligned16(bias));
     const int64_t vecs = hidden / E;
-    if (vec_ok && vecs <= 128) return launch_regs<T, 1, 128>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-    if (vec_ok && vecs <= 256) return launch_regs<T, 1, 256>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-    if (vec_ok && vecs <= 512) return launch_regs<T, 2, 256>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-    if (vec_ok && vecs <= 1024) return launch_regs<T, 4, 256>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-    if (vec_ok && vecs <= 2048) return launch_regs<T, 4, 512>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
+    // Launch shapes measured on B200 at hidden 4096 fp16 (512 vectors per row): with one
+    // input stream (plain norm) 128-thread CTAs holding 4 vectors per thread run at copy
+    // speed; with two input streams (x and the residual) 256-thread CTAs with 2 vectors
+    // per thread, 4 CTAs per SM, do.  Wider rows scale the CTA, not the per-thread count.
+    const bool one_stream = mode == ResidualMode::kNone;
+#define ISPORE_NORM(VPT, THREADS, BLOCKS) \
+    return launch_regs<T, VPT, THREADS, BLOCKS>(x, r, bias, gamma, eps, tokens, hidden, mode, st)
+    if (vec_ok && vecs <= 128) ISPORE_NORM(1, 128, 8);
+    if (vec_ok && vecs <= 256) ISPORE_NORM(2, 128, 8);
+    if (vec_ok && vecs <= 512) {
+        switch (tune(kTuneRmsnorm, one_stream ? 0 : 5)) {
+#ifdef ISPORE_TUNING
+            case 1: ISPORE_NORM(2, 256, 6);
+            case 2: ISPORE_NORM(2, 256, 8);
+            case 3: ISPORE_NORM(4, 128, 10);
+            case 4: ISPORE_NORM(1, 512, 4);
+#endif
+            case 5: ISPORE_NORM(2, 256, 4);
+            default: ISPORE_NORM(4, 128, 8);
+        }
+    }
+    if (vec_ok && vecs <= 1024) {
+        if (one_stream) ISPORE_NORM(4, 256, 4);
+        ISPORE_NORM(2, 512, 2);
+    }
+    if (vec_ok && vecs <= 2048) ISPORE_NORM(4, 512, 2);
+    if (vec_ok && vecs <= 4096) ISPORE_NORM(4, 1024, 1);
+#undef ISPORE_NORM
 
     constexpr int THREADS = 256;
-    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
-    const int grid = static_cast<int>(tokens < max_ctas ? tokens : max_ctas);
+    const int grid = persistent_grid(rmsnorm_generic_kernel<T, THREADS>, THREADS, 0, tokens);
     rmsnorm_generic_kernel<T, THREADS><<<grid, THREADS, 0, st>>>(x, r, bias, gamma, eps, tokens, hidden,
                                                                 static_cast<int>(mode));
     return check_launch("rmsnorm_generic_kernel");

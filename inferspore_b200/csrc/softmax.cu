@@ -7,11 +7,13 @@
 // the reduction, so m never drops below FLT_MIN; a fully masked row therefore
 // comes out as exact zeros).  Both storage types compute in fp32.
 //
-// A row lives in registers between the max, the sum and the store, so qk is
-// read once and the score written once.  Short rows (prefill: k_len of a few
-// hundred) take one warp per row with shuffle-only reductions; long rows
-// (decode against a 4096-deep cache) take one CTA per row.  The mask row is
-// shared by all heads and stays in L2.
+// The mask row [b, q] is shared by all heads.  A thread group (one warp for
+// short rows, one CTA for long rows) therefore takes a (b, q) pair and a group
+// of HG heads: it turns the mask row into the additive term once, keeps it in
+// registers, issues the loads of all HG qk rows together and then finishes the
+// rows one after the other.  A row lives in registers between the max, the sum
+// and the store, so qk is read once and the score written once; the index
+// arithmetic (one 32-bit division) is paid per group, not per row.
 #include <float.h>
 
 #include "common.cuh"
@@ -37,98 +39,128 @@ struct ExpPolicy<__half> {
 };
 
 // GROUP threads cooperate on one row; a CTA of THREADS threads holds
-// THREADS/GROUP rows.  Each thread keeps VPT 128-bit vectors of its row.
-template <typename T, int VPT, int GROUP, int THREADS>
-__global__ void __launch_bounds__(THREADS)
-softmax_row_in_regs_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
-                           int64_t total_rows, int64_t rows_per_batch /* heads*q_len */, int q_len,
-                           int row_vecs, float scale) {
+// THREADS/GROUP groups.  Each thread keeps VPT 128-bit vectors of a row and the
+// matching slice of the additive mask term.  A group works on HG heads of one
+// (b, q) pair per trip.
+template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS = 1>
+__global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
+softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
+                          uint32_t units /* batch*q_len*head_groups */, uint32_t head_groups,
+                          uint32_t heads, uint32_t q_len, int row_vecs, float scale) {
     constexpr int E = VecTraits<T>::kElems;
-    constexpr int kRowsPerCta = THREADS / GROUP;
+    constexpr int kGroupsPerCta = THREADS / GROUP;
     constexpr int kWarpsPerGroup = GROUP / 32;
     using Exp = ExpPolicy<T>;
-    __shared__ float red[2][kRowsPerCta][kWarpsPerGroup > 1 ? kWarpsPerGroup : 1];
+    __shared__ float red[2][kWarpsPerGroup > 1 ? kWarpsPerGroup : 1];  // only used when a CTA is one group
 
     const int tid = threadIdx.x;
-    const int g = tid / GROUP;    // row slot inside the CTA
-    const int gt = tid % GROUP;   // thread inside the row group
+    const int g = tid / GROUP;   // group slot inside the CTA
+    const int gt = tid % GROUP;  // thread inside the group
     const int lane = tid & 31;
-    const int gw = gt >> 5;       // warp inside the row group
+    const int gw = gt >> 5;      // warp inside the group
     const float a = scale * Exp::kPrescale;
     const float neg = -10000.0f * Exp::kPrescale;
     const float floor_m = FLT_MIN * Exp::kPrescale;
 
-    // All row slots of a CTA run the same trip count (block-level barriers below).
-    for (int64_t row0 = static_cast<int64_t>(blockIdx.x) * kRowsPerCta; row0 < total_rows;
-         row0 += static_cast<int64_t>(gridDim.x) * kRowsPerCta) {
-        const int64_t row = row0 + g;
-        const bool live = row < total_rows;
-        const int64_t bidx = live ? row / rows_per_batch : 0;
-        const int64_t qi = live ? (row - bidx * rows_per_batch) % q_len : 0;
-        const uint4* qrow = reinterpret_cast<const uint4*>(qk) + row * row_vecs;
-        const uint4* mrow = reinterpret_cast<const uint4*>(mask) + (bidx * q_len + qi) * row_vecs;
-        uint4* orow = reinterpret_cast<uint4*>(score) + row * row_vecs;
+    for (uint32_t u0 = blockIdx.x * kGroupsPerCta; u0 < units; u0 += gridDim.x * kGroupsPerCta) {
+        const uint32_t u = u0 + g;
+        const bool live = u < units;  // with several groups per CTA there are no block barriers below
+        // q index fastest: neighbouring groups work on neighbouring rows of the same heads.
+        const uint32_t qi = live ? u % q_len : 0;
+        const uint32_t t = live ? u / q_len : 0;
+        const uint32_t hg = t % head_groups;
+        const uint32_t b = t / head_groups;
+        const uint32_t h0 = hg * HG;
+        const int nh = live ? static_cast<int>(min(static_cast<uint32_t>(HG), heads - h0)) : 0;
 
-        uint4 q_raw[VPT], m_raw[VPT];
+        const uint4* mrow = reinterpret_cast<const uint4*>(mask) + (static_cast<int64_t>(b) * q_len + qi) * row_vecs;
+        const int64_t row0 = (static_cast<int64_t>(b) * heads + h0) * q_len + qi;  // row of head h0
+        const int64_t head_stride_vecs = static_cast<int64_t>(q_len) * row_vecs;
+        const uint4* qrow0 = reinterpret_cast<const uint4*>(qk) + row0 * row_vecs;
+        uint4* orow0 = reinterpret_cast<uint4*>(score) + row0 * row_vecs;
+
+        // All loads of the trip first: the mask slice and HG x VPT vectors of qk.
+        uint4 m_raw[VPT], q_raw[HG][VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = gt + i * GROUP;
-            if (live && v < row_vecs) {
-                q_raw[i] = ld_stream(qrow + v);
-                m_raw[i] = ld_keep(mrow + v);
+            if (live && v < row_vecs) m_raw[i] = ld_keep(mrow + v);
+        }
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+#pragma unroll
+            for (int i = 0; i < VPT; ++i) {
+                const int v = gt + i * GROUP;
+                if (hh < nh && v < row_vecs) q_raw[hh][i] = ld_stream(qrow0 + hh * head_stride_vecs + v);
             }
         }
-        Unpacked<T> z[VPT];
-        float mx = floor_m;
+        // Additive mask term (1 - mask) * (-10000), prescaled; -inf-like filler beyond the row.
+        Unpacked<T> term[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = gt + i * GROUP;
             if (live && v < row_vecs) {
-                Unpacked<T> mk;
-                unpack(q_raw[i], z[i]);
-                unpack(m_raw[i], mk);
+                unpack(m_raw[i], term[i]);
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    z[i].v[e] = fmaf(a, z[i].v[e], (1.0f - mk.v[e]) * neg);
-                    mx = fmaxf(mx, z[i].v[e]);
+                for (int e = 0; e < E; ++e) term[i].v[e] = (1.0f - term[i].v[e]) * neg;
+            }
+        }
+
+#pragma unroll
+        for (int hh = 0; hh < HG; ++hh) {
+            if (hh < nh) {  // uniform inside a group; uniform inside the CTA when GROUP == THREADS
+                Unpacked<T> z[VPT];
+                float mx = floor_m;
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int v = gt + i * GROUP;
+                    if (v < row_vecs) {
+                        unpack(q_raw[hh][i], z[i]);
+#pragma unroll
+                        for (int e = 0; e < E; ++e) {
+                            z[i].v[e] = fmaf(a, z[i].v[e], term[i].v[e]);
+                            mx = fmaxf(mx, z[i].v[e]);
+                        }
+                    }
                 }
-            }
-        }
-        mx = warp_max(mx);
-        if (kWarpsPerGroup > 1) {
-            if (lane == 0) red[0][g][gw] = mx;
-            __syncthreads();
+                mx = warp_max(mx);
+                if (kWarpsPerGroup > 1) {
+                    if (lane == 0) red[0][gw] = mx;
+                    __syncthreads();
 #pragma unroll
-            for (int w = 0; w < kWarpsPerGroup; ++w) mx = fmaxf(mx, red[0][g][w]);
-        }
-        float sum = 0.f;
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = gt + i * GROUP;
-            if (live && v < row_vecs) {
-#pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    z[i].v[e] = Exp::exp_diff(z[i].v[e], mx);
-                    sum += z[i].v[e];
+                    for (int w = 0; w < kWarpsPerGroup; ++w) mx = fmaxf(mx, red[0][w]);
                 }
-            }
-        }
-        sum = warp_sum(sum);
-        if (kWarpsPerGroup > 1) {
-            if (lane == 0) red[1][g][gw] = sum;
-            __syncthreads();
-            sum = 0.f;
+                float sum = 0.f;
 #pragma unroll
-            for (int w = 0; w < kWarpsPerGroup; ++w) sum += red[1][g][w];
-        }
-        const float inv = 1.0f / (sum + 1e-6f);
+                for (int i = 0; i < VPT; ++i) {
+                    const int v = gt + i * GROUP;
+                    if (v < row_vecs) {
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = gt + i * GROUP;
-            if (live && v < row_vecs) {
+                        for (int e = 0; e < E; ++e) {
+                            z[i].v[e] = Exp::exp_diff(z[i].v[e], mx);
+                            sum += z[i].v[e];
+                        }
+                    }
+                }
+                sum = warp_sum(sum);
+                if (kWarpsPerGroup > 1) {
+                    if (lane == 0) red[1][gw] = sum;
+                    __syncthreads();  // also orders this row's red[0] reads before the next row's writes
+                    sum = 0.f;
 #pragma unroll
-                for (int e = 0; e < E; ++e) z[i].v[e] *= inv;
-                st_stream(orow + v, pack(z[i]));
+                    for (int w = 0; w < kWarpsPerGroup; ++w) sum += red[1][w];
+                }
+                const float inv = 1.0f / (sum + 1e-6f);
+#pragma unroll
+                for (int i = 0; i < VPT; ++i) {
+                    const int v = gt + i * GROUP;
+                    if (v < row_vecs) {
+#pragma unroll
+                        for (int e = 0; e < E; ++e) z[i].v[e] *= inv;
+                        st_stream(orow0 + hh * head_stride_vecs + v, pack(z[i]));
+                    }
+                }
+                if (kWarpsPerGroup > 1) __syncthreads();  // red[1] is rewritten by the next row
             }
         }
     }
@@ -177,16 +209,21 @@ softmax_generic_kernel(T* __restrict__ score, const T* __restrict__ qk, const T*
     }
 }
 
-template <typename T, int VPT, int GROUP, int THREADS>
-int launch_regs(T* score, const T* qk, const T* mask, int64_t total_rows, int64_t rows_per_batch,
-                int q_len, int row_vecs, float scale, cudaStream_t st) {
-    constexpr int kRowsPerCta = THREADS / GROUP;
-    const int64_t ctas = ceil_div(total_rows, kRowsPerCta);
-    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * (2048 / THREADS) * 4;
-    softmax_row_in_regs_kernel<T, VPT, GROUP, THREADS>
-        <<<static_cast<int>(ctas < max_ctas ? ctas : max_ctas), THREADS, 0, st>>>(
-            score, qk, mask, total_rows, rows_per_batch, q_len, row_vecs, scale);
-    return check_launch("softmax_row_in_regs_kernel");
+template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS = 1>
+int launch_groups(T* score, const T* qk, const T* mask, int64_t batch, int64_t heads, int64_t q_len,
+                  int row_vecs, float scale, cudaStream_t st) {
+    constexpr int kGroupsPerCta = THREADS / GROUP;
+    const int64_t head_groups = ceil_div(heads, HG);
+    const int64_t units = batch * q_len * head_groups;
+    const int64_t ctas = ceil_div(units, kGroupsPerCta);
+    auto kernel = softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS>;
+    // One trip per CTA for any realistic size: the hardware scheduler hands out CTAs in
+    // address order, which keeps the DRAM access front compact.
+    const int grid = static_cast<int>(ctas < (1 << 30) ? ctas : (1 << 30));
+    kernel<<<grid, THREADS, 0, st>>>(score, qk, mask, static_cast<uint32_t>(units),
+                                     static_cast<uint32_t>(head_groups), static_cast<uint32_t>(heads),
+                                     static_cast<uint32_t>(q_len), row_vecs, scale);
+    return check_launch("softmax_head_group_kernel");
 }
 
 template <typename T>
@@ -198,24 +235,54 @@ int softmax_dispatch(T* score, const T* qk, const T* mask, int64_t batch, int64_
     if (batch == 0) return ISPORE_OK;
     if (!score || !qk || !mask) return fail(ISPORE_ENULL, "scale_mask_softmax: NULL buffer");
     const int64_t total_rows = batch * heads * q_len;
-    const int64_t rows_per_batch = heads * q_len;
     constexpr int E = VecTraits<T>::kElems;
-    const bool vec_ok = k_len % E == 0 && aligned16(score) && aligned16(qk) && aligned16(mask);
+    const bool vec_ok = k_len % E == 0 && aligned16(score) && aligned16(qk) && aligned16(mask) &&
+                        total_rows < (1ll << 32) && heads < (1ll << 31);
     const int64_t vecs = k_len / E;
-    const int q = static_cast<int>(q_len);
     if (vec_ok) {
         const int rv = static_cast<int>(vecs);
-        if (vecs <= 32) return launch_regs<T, 1, 32, 256>(score, qk, mask, total_rows, rows_per_batch, q, rv, scale, st);
-        if (vecs <= 64) return launch_regs<T, 2, 32, 256>(score, qk, mask, total_rows, rows_per_batch, q, rv, scale, st);
-        if (vecs <= 128) return launch_regs<T, 4, 32, 256>(score, qk, mask, total_rows, rows_per_batch, q, rv, scale, st);
-        if (vecs <= 256) return launch_regs<T, 1, 256, 256>(score, qk, mask, total_rows, rows_per_batch, q, rv, scale, st);
-        if (vecs <= 512) return launch_regs<T, 2, 256, 256>(score, qk, mask, total_rows, rows_per_batch, q, rv, scale, st);
-        if (vecs <= 1024) return launch_regs<T, 4, 256, 256>(score, qk, mask, total_rows, rows_per_batch, q, rv, scale, st);
-        if (vecs <= 2048) return launch_regs<T, 4, 512, 512>(score, qk, mask, total_rows, rows_per_batch, q, rv, scale, st);
+#define ISPORE_SOFTMAX(VPT, GROUP, THREADS, HG) \
+    return launch_groups<T, VPT, GROUP, THREADS, HG>(score, qk, mask, batch, heads, q_len, rv, scale, st)
+        if (vecs <= 32) ISPORE_SOFTMAX(1, 32, 256, 4);
+        if (vecs <= 64) {
+#ifdef ISPORE_TUNING
+            switch (tune(kTuneSoftmax, 0)) {
+                case 1: return launch_groups<T, 2, 32, 256, 2, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 2: return launch_groups<T, 2, 32, 256, 1, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 3: return launch_groups<T, 2, 32, 256, 4, 3>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 4: return launch_groups<T, 2, 32, 256, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 5: return launch_groups<T, 2, 32, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 6: return launch_groups<T, 2, 32, 128, 4, 6>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 7: return launch_groups<T, 2, 32, 256, 8, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                default: break;
+            }
+#endif
+            return launch_groups<T, 2, 32, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+        }
+        if (vecs <= 128) ISPORE_SOFTMAX(4, 32, 256, 2);
+        if (vecs <= 256) ISPORE_SOFTMAX(1, 256, 256, 4);
+        if (vecs <= 512) {
+#ifdef ISPORE_TUNING
+            switch (tune(kTuneSoftmax, 0)) {
+                case 1: return launch_groups<T, 2, 256, 256, 2, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 2: return launch_groups<T, 2, 256, 256, 1, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 3: return launch_groups<T, 2, 256, 256, 4, 3>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 4: return launch_groups<T, 2, 256, 256, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 5: return launch_groups<T, 2, 256, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 6: return launch_groups<T, 4, 128, 128, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                case 7: return launch_groups<T, 2, 256, 256, 8, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+                default: break;
+            }
+#endif
+            return launch_groups<T, 2, 256, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+        }
+        if (vecs <= 1024) ISPORE_SOFTMAX(4, 256, 256, 2);
+        if (vecs <= 2048) ISPORE_SOFTMAX(4, 512, 512, 2);
+#undef ISPORE_SOFTMAX
     }
-    const int64_t max_ctas = static_cast<int64_t>(kNumSMs) * 8;
-    softmax_generic_kernel<T, 256><<<static_cast<int>(total_rows < max_ctas ? total_rows : max_ctas), 256, 0, st>>>(
-        score, qk, mask, total_rows, rows_per_batch, q, k_len, scale);
+    const int64_t rows_per_batch = heads * q_len;
+    softmax_generic_kernel<T, 256><<<persistent_grid(softmax_generic_kernel<T, 256>, 256, 0, total_rows, 8), 256, 0, st>>>(
+        score, qk, mask, total_rows, rows_per_batch, static_cast<int>(q_len), k_len, scale);
     return check_launch("softmax_generic_kernel");
 }
 

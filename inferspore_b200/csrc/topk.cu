@@ -8,17 +8,22 @@
 // is a run-time value up to ISPORE_TOPK_MAX_K and the order is total:
 // (value descending, index ascending), -0.0 == +0.0.
 //
-// Round 1 (one CTA per row slice) reads its slice once from HBM into shared
-// memory as order-preserving 32-bit keys.  A threshold that is guaranteed to
-// keep at least K elements is derived from the per-thread maxima with
-// warp ballots only; the few survivors are compacted and ranked by counting
-// against each other, which yields the slice's top-K already sorted without a
-// sorting network.  Adversarial inputs (e.g. a constant row, where the
-// threshold keeps everything) fall back to an exact radix select over the keys
-// in shared memory, ties resolved by an index-ordered block scan.
-// Round 2 (one CTA per row) ranks the slices' candidates the same way and can
-// draw the sampled token in its epilogue.
+// Round 1 (one CTA per row slice) streams its slice from HBM once, a tile of
+// 8192 elements at a time, straight into registers (32 raw bit patterns per
+// thread, all loads of a tile in flight together).  A threshold that is
+// guaranteed to keep at least K elements of the tile comes from one
+// representative per thread with warp-level max-reductions only; while the
+// threshold is a positive value the per-element test is a single integer compare
+// on the raw bits.  The few survivors are compacted into shared memory and
+// ranked by counting against each other, which yields the running top-K already
+// sorted without a sorting network.  Later tiles
+// additionally have to beat the current K-th best.  Adversarial tiles (e.g.
+// constant data, where the threshold keeps everything) fall back to an exact
+// radix select over the keys in registers, ties resolved by an index-ordered
+// block scan.  Round 2 (one CTA per row) merges the slices' sorted lists by
+// binary search and can draw the sampled token in its epilogue.
 #include <float.h>
+#include <limits.h>
 #include <math.h>
 
 #include "common.cuh"
@@ -26,11 +31,20 @@
 namespace ispore {
 namespace {
 
+#ifdef ISPORE_TUNING
+__device__ int g_topk_debug = 0;  // ablation switches, tuning builds only
+#define TOPK_DEBUG(bit) (g_topk_debug & (bit))
+#else
+#define TOPK_DEBUG(bit) false
+#endif
+
 constexpr int kTopkThreads = 256;
 constexpr int kTopkWarps = kTopkThreads / 32;
-constexpr int kCandCap = 1024;        // survivors kept by the threshold path
-constexpr int kMergeCap = 4096;       // lists*K candidates the merge kernel holds in smem
-constexpr int kMaxSliceElems = 49152; // 192 KB of keys
+constexpr int kElemsPerThread = 32;                          // keys a thread holds per tile
+constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
+constexpr int kTileCap = 768;                                // survivors a tile may add on the fast path
+constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + tile survivors
+constexpr int kMergeCap = 4096;                              // lists*K candidates the merge kernel holds
 
 __device__ __forceinline__ uint32_t order_key(float f) {
     uint32_t b = __float_as_uint(f);
@@ -53,55 +67,193 @@ __device__ __forceinline__ __half neg_inf<__half>() {
     return __ushort_as_half(0xFC00u);
 }
 
-// q-th largest (1-based) of the 32 lane values, by ballots from the top bit down.
+// q-th largest (1-based, q <= 32) of the 32 lane values: q rounds of a hardware
+// max-reduction, retiring one holder of the maximum per round.
 __device__ __forceinline__ uint32_t warp_qth_largest(uint32_t v, int q) {
-    uint32_t cand = 0xffffffffu;  // lanes still tied with the prefix
-    uint32_t prefix = 0;
-    for (int bit = 31; bit >= 0; --bit) {
-        const uint32_t set = __ballot_sync(0xffffffffu, (v >> bit) & 1u) & cand;
-        const int cnt = __popc(set);
-        if (cnt >= q) {
-            cand = set;
-            prefix |= 1u << bit;
-        } else {
-            q -= cnt;
-            cand &= ~set;
-        }
+    const int lane = threadIdx.x & 31;
+    uint32_t m = 0;
+    for (int i = 0; i < q; ++i) {
+        m = __reduce_max_sync(0xffffffffu, v);
+        if (m == 0) break;  // fewer than q non-empty lanes: the threshold keeps everything
+        const uint32_t holders = __ballot_sync(0xffffffffu, v == m);
+        if (lane == __ffs(holders) - 1) v = 0;
     }
-    return prefix;
+    return m;
 }
 
-// Ranks `count` distinct composites against each other and emits those with
-// rank < K at slot `rank` of (out_ids, out_vals).  value_of(idx) returns the
-// original stored value for element idx.
-template <typename T, typename ValueOf>
-__device__ __forceinline__ void rank_and_emit(const unsigned long long* cand, int count, int K,
-                                              int32_t* out_ids, T* out_vals, int32_t index_offset,
-                                              ValueOf value_of) {
-    for (int c = threadIdx.x; c < count; c += kTopkThreads) {
-        const unsigned long long mine = cand[c];
+// Number of entries of a descending-sorted composite list that are greater than x.
+__device__ __forceinline__ int count_greater(const unsigned long long* list, int len, unsigned long long x) {
+    int lo = 0, hi = len;  // invariant: list[0..lo) > x, list[hi..len) <= x
+    while (lo < hi) {
+        const int mid = (lo + hi) >> 1;
+        if (list[mid] > x) lo = mid + 1;
+        else hi = mid;
+    }
+    return lo;
+}
+
+// Ranks the `total` distinct composites in `in` against each other; those with rank < K land
+// at out[rank].  in[0..nsorted) is already sorted (best first): an entry of that prefix starts
+// from its own position, any other entry from a binary search in the prefix, and only the
+// unsorted tail in[nsorted..total) is compared one by one.  Threads are split P per candidate
+// (P a power of two) so that short lists still use the whole CTA.
+__device__ __forceinline__ void rank_into(const unsigned long long* in, int nsorted, int total, int K,
+                                          unsigned long long* out) {
+    int P = 1;
+    while (P < 32 && total * (P * 2) <= kTopkThreads) P *= 2;
+    const int part = threadIdx.x & (P - 1);
+    for (int c0 = 0; c0 < total; c0 += kTopkThreads / P) {
+        const int c = c0 + threadIdx.x / P;
+        const bool live = c < total;
+        const unsigned long long mine = live ? in[c] : 0ull;
         int rank = 0;
-        for (int j = 0; j < count; ++j) rank += cand[j] > mine;
-        if (rank < K) {
-            const uint32_t idx = ~static_cast<uint32_t>(mine);
-            out_ids[rank] = static_cast<int32_t>(idx) + index_offset;
-            out_vals[rank] = value_of(idx);
+        if (live) {
+            if (part == 0) rank = c < nsorted ? c : count_greater(in, nsorted, mine);
+#pragma unroll 4
+            for (int j = nsorted + part; j < total; j += P) rank += in[j] > mine;
         }
-    }
-    for (int slot = count + threadIdx.x; slot < K; slot += kTopkThreads) {
-        out_ids[slot] = -1;
-        out_vals[slot] = neg_inf<T>();
+        for (int o = 1; o < P; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+        if (live && part == 0 && rank < K) out[rank] = mine;
     }
 }
 
+// A tile lives in registers as the raw fp32 bit patterns of its 32 elements per thread, viewed
+// as signed ints; element e of vector k of thread t is slice element
+// (tile_begin + (t + k*256)*E + e).  Slots beyond the slice hold INT_MIN.
+// For non-negative floats (NaNs included) signed-int order of the bits IS the output order, so
+// as long as the threshold is a positive float the per-element test is one integer compare on
+// the raw bits and nothing is converted.  `pmax` is the signed-int maximum of the thread's slots:
+// a real element of the thread (the true maximum whenever the thread holds a non-negative
+// value), which is all the threshold derivation needs.
 template <typename T>
-__global__ void __launch_bounds__(kTopkThreads)
+__device__ __forceinline__ void load_tile_bits(const T* src, int n, int tile_begin, bool vec_loads,
+                                               int (&bits)[kElemsPerThread], int& pmax) {
+    constexpr int E = VecTraits<T>::kElems;
+    constexpr int kVecs = kElemsPerThread / E;
+    pmax = INT_MIN;
+    if (vec_loads) {
+        uint4 raw[kVecs];
+        const uint4* src_v = reinterpret_cast<const uint4*>(src + tile_begin);
+#pragma unroll
+        for (int k = 0; k < kVecs; ++k) {
+            const int v = threadIdx.x + k * kTopkThreads;
+            // L1-allocating load: the few survivors are re-read below and should hit L1.
+            if (tile_begin + v * E < n) raw[k] = ld_keep(src_v + v);  // n % E == 0 on this path
+        }
+#pragma unroll
+        for (int k = 0; k < kVecs; ++k) {
+            const int v = threadIdx.x + k * kTopkThreads;
+            const bool ok = tile_begin + v * E < n;
+            Unpacked<T> x;
+            if (ok) unpack(raw[k], x);
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                bits[k * E + e] = ok ? __float_as_int(x.v[e]) : INT_MIN;
+                pmax = max(pmax, bits[k * E + e]);
+            }
+        }
+    } else {
+#pragma unroll
+        for (int k = 0; k < kVecs; ++k) {
+            const int v = threadIdx.x + k * kTopkThreads;
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                const int i = tile_begin + v * E + e;
+                bits[k * E + e] = i < n ? __float_as_int(to_float<T>(src[i])) : INT_MIN;
+                pmax = max(pmax, bits[k * E + e]);
+            }
+        }
+    }
+}
+
+// Exact selection of a tile's K largest keys, for tiles the threshold cannot thin out
+// (constant data, K close to the tile size): radix select, 8 bits per pass, then an
+// index-ordered block scan that hands the tied key to the lowest indices.  Writes exactly K
+// composites to `mine`.  Kept out of line, and re-reading the tile from global memory (it is
+// cache-resident) instead of taking the caller's registers, so that it costs the fast path
+// neither registers nor stack traffic.
+struct SelectScratch {
+    int* hist;      // [256]
+    int* warp_cnt;  // [kTopkWarps]
+    int* s_count;
+    int* s_digit;
+    int* s_need;
+};
+template <typename T>
+__device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int n, long long begin, int K,
+                                               unsigned long long* mine, SelectScratch sm) {
+    const int tid = threadIdx.x;
+    int* hist = sm.hist;
+    int* warp_cnt = sm.warp_cnt;
+    int& s_count = *sm.s_count;
+    int& s_digit = *sm.s_digit;
+    int& s_need = *sm.s_need;
+    int tile_end = tile_begin + kTileElems;
+    if (tile_end > n) tile_end = n;
+    auto key_at = [&](int el) { return order_key(to_float<T>(src[el])); };
+
+    uint32_t prefix = 0, prefix_mask = 0;
+    int need = K;  // the caller saw more than kTileCap >= K survivors, so the tile holds at least K elements
+    for (int shift = 24; shift >= 0; shift -= 8) {
+        hist[tid] = 0;  // kTopkThreads == 256 bins
+        __syncthreads();
+        for (int el = tile_begin + tid; el < tile_end; el += kTopkThreads) {
+            const uint32_t key = key_at(el);
+            if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int cum = 0, d = 255;
+            for (; d > 0; --d) {
+                if (cum + hist[d] >= need) break;
+                cum += hist[d];
+            }
+            s_digit = d;
+            s_need = need - cum;
+        }
+        __syncthreads();
+        prefix |= static_cast<uint32_t>(s_digit) << shift;
+        prefix_mask |= 255u << shift;
+        need = s_need;
+        __syncthreads();
+    }
+    // keys > prefix: all of them (fewer than K); keys == prefix: the `need` lowest indices.
+    if (tid == 0) s_count = 0;
+    __syncthreads();
+    for (int el = tile_begin + tid; el < tile_end; el += kTopkThreads) {
+        const uint32_t key = key_at(el);
+        if (key > prefix) mine[atomicAdd(&s_count, 1)] = composite(key, static_cast<uint32_t>(begin + el));
+    }
+    __syncthreads();
+    const int greater = s_count;
+    int taken = 0;
+    for (int base = tile_begin; base < tile_end && taken < need; base += kTopkThreads) {  // uniform trip count
+        const int el = base + tid;
+        const bool tie = el < tile_end && key_at(el) == prefix;
+        const uint32_t ballot = __ballot_sync(0xffffffffu, tie);
+        if ((tid & 31) == 0) warp_cnt[tid >> 5] = __popc(ballot);
+        __syncthreads();
+        int before = 0, total = 0;
+#pragma unroll
+        for (int w = 0; w < kTopkWarps; ++w) {
+            if (w < (tid >> 5)) before += warp_cnt[w];
+            total += warp_cnt[w];
+        }
+        const int ordinal = taken + before + __popc(ballot & ((1u << (tid & 31)) - 1u));
+        if (tie && ordinal < need) mine[greater + ordinal] = composite(prefix, static_cast<uint32_t>(begin + el));
+        taken += total;
+        __syncthreads();
+    }
+}
+
+template <typename T, int MIN_BLOCKS>
+__global__ void __launch_bounds__(kTopkThreads, MIN_BLOCKS)
 topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int slices, int K,
-                  int32_t* __restrict__ scratch_ids, T* __restrict__ scratch_vals, int scratch_slices,
+                  int32_t* __restrict__ out_ids_base, T* __restrict__ out_vals_base, int out_lists,
                   int32_t index_offset, int vec_loads) {
-    extern __shared__ __align__(16) unsigned char smem_raw[];
-    uint32_t* keys = reinterpret_cast<uint32_t*>(smem_raw);  // [slice_len]
-    __shared__ unsigned long long cand[kCandCap];
+    constexpr int E = VecTraits<T>::kElems;
+    constexpr int kVecs = kElemsPerThread / E;
+    __shared__ unsigned long long cand[2][kCandSlots];  // [cur]: running best then tile survivors
     __shared__ uint32_t warp_thr[kTopkWarps];
     __shared__ int s_count;
     __shared__ int hist[256];
@@ -116,121 +268,96 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     if (n64 > slice_len) n64 = slice_len;
     const int n = n64 > 0 ? static_cast<int>(n64) : 0;
     const T* src = probs + row * vocab + begin;
-    int32_t* out_ids = scratch_ids + (row * scratch_slices + slice) * K;
-    T* out_vals = scratch_vals + (row * scratch_slices + slice) * K;
 
-    if (tid == 0) s_count = 0;
-
-    // 1. slice -> keys in shared memory, per-thread maximum on the way.
-    uint32_t tmax = 0;
-    if (vec_loads) {
-        constexpr int E = VecTraits<T>::kElems;
-        const int n_vecs = n / E;  // launcher guarantees n % E == 0 on this path
-        const uint4* src_v = reinterpret_cast<const uint4*>(src);
-#pragma unroll 4
-        for (int v = tid; v < n_vecs; v += kTopkThreads) {
-            Unpacked<T> x;
-            unpack(ld_stream(src_v + v), x);
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-                const uint32_t k = order_key(x.v[e]);
-                keys[v * E + e] = k;
-                tmax = max(tmax, k);
-            }
-        }
-    } else {
-#pragma unroll 4
-        for (int i = tid; i < n; i += kTopkThreads) {
-            const uint32_t k = order_key(to_float<T>(src[i]));
-            keys[i] = k;
-            tmax = max(tmax, k);
-        }
-    }
-
-    // 2. threshold: the ceil(K/warps)-th largest thread maximum of every warp,
-    //    minimum over warps => at least K elements have key >= threshold.
+    int cur = 0;    // which cand[] buffer holds the running best
+    int nbest = 0;  // entries of the running best (sorted, best first)
     const int q = (K + kTopkWarps - 1) / kTopkWarps;
-    const uint32_t wq = warp_qth_largest(tmax, q);
-    if ((tid & 31) == 0) warp_thr[tid >> 5] = wq;
-    __syncthreads();
-    uint32_t thr = warp_thr[0];
-#pragma unroll
-    for (int w = 1; w < kTopkWarps; ++w) thr = min(thr, warp_thr[w]);
 
-    // 3. compact the survivors.
-    for (int i = tid; i < n; i += kTopkThreads) {
-        const uint32_t k = keys[i];
-        if (k >= thr) {
-            const int pos = atomicAdd(&s_count, 1);
-            if (pos < kCandCap) cand[pos] = composite(k, static_cast<uint32_t>(begin + i));
-        }
-    }
-    __syncthreads();
-    int count = s_count;
+    for (int tile_begin = 0; tile_begin < n; tile_begin += kTileElems) {
+        int bits[kElemsPerThread];
+        int pmax;
+        load_tile_bits<T>(src, n, tile_begin, vec_loads != 0, bits, pmax);
+        // Slot i of this thread is slice element elem_of(i); a slot is live iff that is < n.
+        auto elem_of = [&](int i) { return tile_begin + (tid + (i / E) * kTopkThreads) * E + (i % E); };
 
-    if (count > kCandCap) {
-        // 4'. exact radix select: the K-th largest key, 8 bits per pass.
-        uint32_t prefix = 0, prefix_mask = 0;
-        int need = K;  // K <= n here because count > kCandCap >= K
-        for (int shift = 24; shift >= 0; shift -= 8) {
-            hist[tid] = 0;  // kTopkThreads == 256 bins
+        // Threshold.  First tile(s), while fewer than K entries are held: the q-th largest
+        // thread representative of every warp, minimum over warps => at least K tile elements
+        // have key >= threshold.  Once K entries are held an element only matters if it beats
+        // the current K-th best outright (on a tie the earlier index, already held, wins).
+        uint32_t thr;
+        if (nbest == K) {
+            const uint32_t kth = static_cast<uint32_t>(cand[cur][K - 1] >> 32);
+            thr = kth == 0xffffffffu ? kth : kth + 1u;
+            if (tid == 0) s_count = 0;
             __syncthreads();
-            for (int i = tid; i < n; i += kTopkThreads) {
-                const uint32_t k = keys[i];
-                if ((k & prefix_mask) == prefix) atomicAdd(&hist[(k >> shift) & 255u], 1);
-            }
+        } else {
+            const bool any_live = elem_of(0) < n;
+            const uint32_t wq = warp_qth_largest(any_live ? order_key(__int_as_float(pmax)) : 0u, q);
+            if ((tid & 31) == 0) warp_thr[tid >> 5] = wq;
+            if (tid == 0) s_count = 0;
             __syncthreads();
-            if (tid == 0) {
-                int cum = 0, d = 255;
-                for (; d > 0; --d) {
-                    if (cum + hist[d] >= need) break;
-                    cum += hist[d];
-                }
-                s_digit = d;
-                s_need = need - cum;
-            }
-            __syncthreads();
-            prefix |= static_cast<uint32_t>(s_digit) << shift;
-            prefix_mask |= 255u << shift;
-            need = s_need;
-            __syncthreads();
-        }
-        // keys > prefix: all of them (fewer than K); keys == prefix: the `need`
-        // lowest indices, found by an index-ordered scan.
-        if (tid == 0) s_count = 0;
-        __syncthreads();
-        for (int i = tid; i < n; i += kTopkThreads) {
-            const uint32_t k = keys[i];
-            if (k > prefix) cand[atomicAdd(&s_count, 1)] = composite(k, static_cast<uint32_t>(begin + i));
-        }
-        __syncthreads();
-        const int greater = s_count;
-        int taken = 0;
-        for (int base = 0; base < n && taken < need; base += kTopkThreads) {
-            const int i = base + tid;
-            const bool tie = i < n && keys[i] == prefix;
-            const uint32_t ballot = __ballot_sync(0xffffffffu, tie);
-            if ((tid & 31) == 0) warp_cnt[tid >> 5] = __popc(ballot);
-            __syncthreads();
-            int before = 0, total = 0;
+            thr = warp_thr[0];
 #pragma unroll
-            for (int w = 0; w < kTopkWarps; ++w) {
-                if (w < (tid >> 5)) before += warp_cnt[w];
-                total += warp_cnt[w];
+            for (int w = 1; w < kTopkWarps; ++w) thr = min(thr, warp_thr[w]);
+        }
+
+        // Survivor mask of this thread's 32 slots.
+        uint32_t mask = 0;
+        if (TOPK_DEBUG(16)) {
+            mask = 0;
+        } else if (thr > 0x80000000u) {
+            // thr is the key of a positive float: survivors are exactly the slots whose raw
+            // bits, as signed ints, reach thr's bits (empty slots hold INT_MIN and never do).
+            const int thr_bits = static_cast<int>(thr & 0x7fffffffu);
+#pragma unroll
+            for (int i = 0; i < kElemsPerThread; ++i) mask |= (bits[i] >= thr_bits ? 1u : 0u) << i;
+        } else {
+#pragma unroll
+            for (int i = 0; i < kElemsPerThread; ++i)
+                mask |= (elem_of(i) < n && order_key(__int_as_float(bits[i])) >= thr ? 1u : 0u) << i;
+        }
+        unsigned long long* mine = cand[cur] + nbest;  // tile survivors go behind the running best
+        if (mask != 0 && !TOPK_DEBUG(8)) {
+            int pos = atomicAdd(&s_count, __popc(mask));
+            while (mask != 0 && pos < kTileCap) {
+                const int i = __ffs(mask) - 1;
+                mask &= mask - 1;
+                const int el = elem_of(i);
+                // The slot's value is re-read (cache hit) rather than picked out of the register
+                // array with a run-time index.
+                mine[pos++] = composite(order_key(to_float<T>(src[el])), static_cast<uint32_t>(begin + el));
             }
-            const int ordinal = taken + before + __popc(ballot & ((1u << (tid & 31)) - 1u));
-            if (tie && ordinal < need)
-                cand[greater + ordinal] = composite(prefix, static_cast<uint32_t>(begin + i));
-            taken += total;
+        }
+        __syncthreads();
+        int count = s_count;
+
+        if (count > kTileCap) {
+            exact_select_tile<T>(src, tile_begin, n, begin, K, mine,
+                                 SelectScratch{hist, warp_cnt, &s_count, &s_digit, &s_need});
+            count = K;
             __syncthreads();
         }
-        count = K;
+
+        // Merge the tile's survivors into the running best: rank everything, keep rank < K.
+        const int total = nbest + count;
+        if (!TOPK_DEBUG(4)) rank_into(cand[cur], nbest, total, K, cand[cur ^ 1]);
+        cur ^= 1;
+        nbest = total < K ? total : K;
         __syncthreads();
     }
 
-    // 5. rank the survivors against each other; rank < K are the slice's top-K.
-    rank_and_emit<T>(cand, count, K, out_ids, out_vals, index_offset,
-                     [&](uint32_t idx) { return src[static_cast<int64_t>(idx) - begin]; });
+    int32_t* out_ids = out_ids_base + (row * out_lists + slice) * K;
+    T* out_vals = out_vals_base + (row * out_lists + slice) * K;
+    for (int s = tid; s < K; s += kTopkThreads) {
+        if (s < nbest) {
+            const uint32_t idx = ~static_cast<uint32_t>(cand[cur][s]);
+            out_ids[s] = static_cast<int32_t>(idx) + index_offset;
+            out_vals[s] = src[static_cast<int64_t>(idx) - begin];  // original bits (keeps -0.0)
+        } else {
+            out_ids[s] = -1;
+            out_vals[s] = neg_inf<T>();
+        }
+    }
 }
 
 // exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.
@@ -294,11 +421,25 @@ topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ ca
         fin_vals[s] = neg_inf<T>();
     }
     __syncthreads();
+    // Lists produced by the slice kernel are sorted (best first, empties last).  Check it
+    // rather than trust it: unsorted input takes the all-pairs ranking instead.
+    int unsorted = 0;
+    for (int c = tid; c < total; c += kTopkThreads)
+        if (c % K != 0 && comp[c] > comp[c - 1]) unsorted = 1;
+    unsorted = __syncthreads_or(unsorted);
+
     for (int c = tid; c < total; c += kTopkThreads) {
         const unsigned long long mine = comp[c];
         if (mine == 0ull) continue;
         int rank = 0;
-        for (int j = 0; j < total; ++j) rank += comp[j] > mine;
+        if (!unsorted) {
+            const int a = c / K;
+            rank = c - a * K;  // entries ahead of it in its own list
+            for (int b = 0; b < lists; ++b)
+                if (b != a) rank += count_greater(comp + b * K, K, mine);
+        } else {
+            for (int j = 0; j < total; ++j) rank += comp[j] > mine;
+        }
         if (rank < K) {
             fin_ids[rank] = ids[c];
             fin_vals[rank] = vals[c];
@@ -332,6 +473,19 @@ int check_k(const char* who, int32_t K) {
 }
 
 template <typename T>
+int sampling_dispatch(const int32_t* ids, const T* vals, const float* uniform, int32_t* out, int64_t rows,
+                      int32_t K, float temperature, cudaStream_t st) {
+    if (int rc = check_k("sampling", K)) return rc;
+    if (rows < 0) return fail(ISPORE_ESHAPE, "sampling: rows=%lld", (long long)rows);
+    if (!(temperature > 0.f)) return fail(ISPORE_ESHAPE, "sampling: temperature must be > 0");
+    if (rows == 0) return ISPORE_OK;
+    if (!ids || !vals || !uniform || !out) return fail(ISPORE_ENULL, "sampling: NULL buffer");
+    sampling_kernel<T><<<static_cast<int>(ceil_div(rows, kTopkWarps)), kTopkThreads, 0, st>>>(
+        ids, vals, uniform, out, rows, K, temperature);
+    return check_launch("sampling_kernel");
+}
+
+template <typename T>
 int merge_dispatch(const int32_t* cand_ids, const T* cand_vals, int64_t rows, int32_t lists,
                    int32_t list_stride, int32_t K, int32_t* final_ids, T* final_vals,
                    const float* uniform, float temperature, int32_t* sampled_ids, cudaStream_t st) {
@@ -359,34 +513,43 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
         static_cast<int64_t>(index_offset) + vocab > INT32_MAX)
         return fail(ISPORE_ESHAPE, "topk: bad shape rows=%lld vocab=%lld offset=%d", (long long)rows,
                     (long long)vocab, index_offset);
+    if (uniform != nullptr && !(temperature > 0.f)) return fail(ISPORE_ESHAPE, "topk: temperature must be > 0");
     if (rows == 0) return ISPORE_OK;
     if (!probs || !final_ids || !final_vals) return fail(ISPORE_ENULL, "topk: NULL buffer");
-    if (!scratch_ids || !scratch_vals || scratch_slices < 1)
-        return fail(ISPORE_ESCRATCH, "topk: scratch [rows, slices>=1, K] is required");
+    if (uniform != nullptr && sampled_ids == nullptr) return fail(ISPORE_ENULL, "topk: uniform given without sampled_ids");
 
     constexpr int E = VecTraits<T>::kElems;
-    // Slices of ~4K elements keep every SM busy at a few hundred rows; never more
-    // than the scratch the caller gave, nor than the merge kernel can hold.
-    int64_t slices = ceil_div(vocab, 4096);
-    if (slices > scratch_slices) slices = scratch_slices;
+    // Slices per row: enough CTAs to fill the GPU once (a CTA walks a long slice tile by
+    // tile, and later tiles are cheap because they must beat the running K-th best), at
+    // least 1024 elements per slice, never more than the scratch or the merge kernel hold.
+    const int variant = tune(kTuneTopk, 0);
+    const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
+    auto kernel = (variant & 1) ? topk_slice_kernel<T, 3> : topk_slice_kernel<T, 4>;
+    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, 0);
+    int64_t slices;
+    switch (variant >> 1) {
+        case 1: slices = ceil_div(vocab, kTileElems); if (ceil_div(resident, rows) > slices) slices = ceil_div(resident, rows); break;
+        case 2: slices = 8; break;
+        default: slices = resident / rows; if (slices < 1) slices = 1; break;
+    }
+    if (slices > ceil_div(vocab, 1024)) slices = ceil_div(vocab, 1024);
     if (slices * K > kMergeCap) slices = kMergeCap / K;
-    int64_t slice_len = ceil_div(vocab, slices);
-    slice_len = ceil_div(slice_len, E) * E;
-    if (slice_len > kMaxSliceElems)
-        return fail(ISPORE_ESCRATCH, "topk: vocab %lld needs more than %d scratch slices", (long long)vocab,
-                    scratch_slices);
+    if (slices > (have_scratch ? scratch_slices : 1)) slices = have_scratch ? scratch_slices : 1;
+    if (slices < 1) slices = 1;
+    int64_t slice_len = ceil_div(ceil_div(vocab, slices), E) * E;
     slices = ceil_div(vocab, slice_len);
     if (rows * slices > INT32_MAX) return fail(ISPORE_ELIMIT, "topk: rows*slices too large");
     const int vec_loads = (vocab % E == 0) && aligned16(probs);
 
-    const size_t smem = static_cast<size_t>(slice_len) * sizeof(uint32_t);
-    static_assert(kTopkThreads == 256, "radix pass uses one thread per bin");
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(topk_slice_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             kMaxSliceElems * (int)sizeof(uint32_t));
-        if (e != cudaSuccess) return fail(ISPORE_ELAUNCH, "topk: cannot raise dynamic smem: %s", cudaGetErrorString(e));
+    if (slices == 1) {
+        // The slice kernel's sorted list is already the answer.
+        kernel<<<static_cast<int>(rows), kTopkThreads, 0, st>>>(probs, vocab, static_cast<int>(slice_len), 1, K,
+                                                                final_ids, final_vals, 1, index_offset, vec_loads);
+        if (int rc = check_launch("topk_slice_kernel")) return rc;
+        if (uniform == nullptr) return ISPORE_OK;
+        return sampling_dispatch<T>(final_ids, final_vals, uniform, sampled_ids, rows, K, temperature, st);
     }
-    topk_slice_kernel<T><<<static_cast<int>(rows * slices), kTopkThreads, smem, st>>>(
+    kernel<<<static_cast<int>(rows * slices), kTopkThreads, 0, st>>>(
         probs, vocab, static_cast<int>(slice_len), static_cast<int>(slices), K, scratch_ids, scratch_vals,
         scratch_slices, index_offset, vec_loads);
     if (int rc = check_launch("topk_slice_kernel")) return rc;
@@ -394,21 +557,14 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
                              final_ids, final_vals, uniform, temperature, sampled_ids, st);
 }
 
-template <typename T>
-int sampling_dispatch(const int32_t* ids, const T* vals, const float* uniform, int32_t* out, int64_t rows,
-                      int32_t K, float temperature, cudaStream_t st) {
-    if (int rc = check_k("sampling", K)) return rc;
-    if (rows < 0) return fail(ISPORE_ESHAPE, "sampling: rows=%lld", (long long)rows);
-    if (!(temperature > 0.f)) return fail(ISPORE_ESHAPE, "sampling: temperature must be > 0");
-    if (rows == 0) return ISPORE_OK;
-    if (!ids || !vals || !uniform || !out) return fail(ISPORE_ENULL, "sampling: NULL buffer");
-    sampling_kernel<T><<<static_cast<int>(ceil_div(rows, kTopkWarps)), kTopkThreads, 0, st>>>(
-        ids, vals, uniform, out, rows, K, temperature);
-    return check_launch("sampling_kernel");
-}
-
 }  // namespace
 }  // namespace ispore
+
+#ifdef ISPORE_TUNING
+extern "C" __attribute__((visibility("default"))) void ispore_topk_debug(int v) {
+    cudaMemcpyToSymbol(ispore::g_topk_debug, &v, sizeof(int));
+}
+#endif
 
 extern "C" {
 

@@ -58,7 +58,9 @@ def test_bad_arguments_return_codes_without_a_device(lib):
     assert lib.ispore_concat_kv_f16(one, one, one, one, one, one, 3, 2, 1, 1, 1, 8, 8, None) == capi.ISPORE_ESHAPE
     assert lib.ispore_scale_mask_softmax_f32(one, one, one, 1, 0, 1, 8, 1.0, None) == capi.ISPORE_ESHAPE
     assert lib.ispore_topk_f32(one, 1, 100, 300, one, one, 8, one, one, 0, None, 1.0, None, None) == capi.ISPORE_ELIMIT
-    assert lib.ispore_topk_f32(one, 1, 100, 5, None, None, 0, one, one, 0, None, 1.0, None, None) == capi.ISPORE_ESCRATCH
+    # a uniform without a place for the sampled ids
+    assert lib.ispore_topk_f32(one, 1, 100, 5, None, None, 0, one, one, 0, one, 1.0, None, None) == capi.ISPORE_ENULL
+    assert lib.ispore_topk_f32(one, 1, 100, 5, None, None, 0, one, one, -1, None, 1.0, None, None) == capi.ISPORE_ESHAPE
     assert lib.ispore_sampling_f32(one, one, one, one, 1, 5, 0.0, None) == capi.ISPORE_ESHAPE
     # rotary dim larger than the head / odd head size
     args = [one] * 8 + [1, 4, 4, 2, 2, 8]
