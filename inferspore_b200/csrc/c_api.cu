@@ -4,9 +4,7 @@
 #include <stdarg.h>
 #include <stdio.h>
 
-#include <map>
 #include <mutex>
-#include <utility>
 
 #include "common.cuh"
 
@@ -73,14 +71,24 @@ int sm_count() {
 }
 
 int resident_ctas(const void* kernel, int threads, size_t dynamic_smem) {
+    // Fixed-size cache (no heap): (kernel, threads, smem) -> resident CTAs, per device.
+    struct Entry {
+        const void* kernel;
+        int threads;
+        size_t smem;
+        int total;
+    };
+    constexpr int kSlots = 128;
     static std::mutex mutex;
-    static std::map<std::pair<const void*, std::pair<int, size_t>>, int> cache[kMaxDevices];
+    static Entry cache[kMaxDevices][kSlots] = {};
+    static int used[kMaxDevices] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return kNumSMs;
-    const auto key = std::make_pair(kernel, std::make_pair(threads, dynamic_smem));
     std::lock_guard<std::mutex> lock(mutex);
-    auto it = cache[dev].find(key);
-    if (it != cache[dev].end()) return it->second;
+    for (int i = 0; i < used[dev]; ++i) {
+        const Entry& e = cache[dev][i];
+        if (e.kernel == kernel && e.threads == threads && e.smem == dynamic_smem) return e.total;
+    }
     int per_sm = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, threads, dynamic_smem) != cudaSuccess ||
         per_sm <= 0) {
@@ -88,7 +96,7 @@ int resident_ctas(const void* kernel, int threads, size_t dynamic_smem) {
         per_sm = 1;
     }
     const int total = per_sm * sm_count();
-    cache[dev][key] = total;
+    if (used[dev] < kSlots) cache[dev][used[dev]++] = Entry{kernel, threads, dynamic_smem, total};
     return total;
 }
 
