@@ -254,6 +254,35 @@ ISPORE_API int ispore_topk_f16(const void* probs, int64_t rows, int64_t vocab, i
                                const float* uniform, float temperature, int32_t* sampled_ids,
                                ispore_stream_t stream);
 
+/* ---- top-K without caller scratch and without any allocation --------------------------- *
+ * ref: none — the reference has no counterpart; its launcher always takes
+ *      caller-allocated scratch tensors (src/kernels/topK.h:41-46).
+ * For callers that are not allowed to allocate device memory at the point where
+ * they sample: code running inside a serving loop whose HBM is fully carved up
+ * in advance (weights + KV cache own the device, so a cudaMalloc there can fail
+ * or stall), plugin-style "enqueue" callbacks that must not allocate, and
+ * latency-critical threads that cannot afford cudaMalloc's device-wide
+ * synchronisation.  Same results as ispore_topk_f32; the per-slice candidate
+ * lists live in a fixed array inside the library image instead of
+ * caller-provided scratch.  Neither this call nor anything it reaches calls
+ * cudaMalloc/cudaFree or any allocating library routine.
+ *   - Limit: rows * K <= ISPORE_TOPK_STATIC_ENTRIES (131072 list entries,
+ *     1 MiB of device memory that every GPU loading the library holds until the
+ *     process exits).  Larger requests return ISPORE_ELIMIT with an explanatory
+ *     message; use ispore_topk_f32 for those.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and caches it; make that
+ *     first call before starting any stream capture on the device.
+ *   - All calls on a device share the one array, which keeps whatever the last
+ *     call left in it.  Nothing needs clearing (every slot that is read is
+ *     written first), but two calls that overlap on the GPU — different streams,
+ *     or different host threads — race on it: serialise them. */
+#define ISPORE_TOPK_STATIC_ENTRIES 131072
+ISPORE_API int ispore_topk_static_f32(const float* probs, int64_t rows, int64_t vocab, int32_t K,
+                                      int32_t* final_ids, float* final_vals, int32_t index_offset,
+                                      const float* uniform, float temperature, int32_t* sampled_ids,
+                                      ispore_stream_t stream);
+
 /* Merge of `lists` candidate lists per row (cand_ids/cand_vals [rows, lists, K],
  * id -1 = empty slot; lists sorted best-first, as ispore_topk_* emits them, merge
  * by binary search, any other order is detected and ranked pairwise) into the global top-K with the

@@ -43,6 +43,9 @@ for _t in ("f32", "f16"):
     SIGNATURES[f"ispore_topk_merge_{_t}"] = [_p, _p, _i64, _i32, _i32, _p, _p, _p, _f, _p, _p]
     SIGNATURES[f"ispore_sampling_{_t}"] = [_p, _p, _p, _p, _i64, _i32, _f, _p]
 
+SIGNATURES["ispore_topk_static_f32"] = [_p, _i64, _i64, _i32, _p, _p, _i32, _p, _f, _p, _p]
+TOPK_STATIC_ENTRIES = 131072
+
 _lib = None
 
 

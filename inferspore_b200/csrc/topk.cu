@@ -26,6 +26,8 @@
 #include <limits.h>
 #include <math.h>
 
+#include <mutex>
+
 #include "common.cuh"
 
 namespace ispore {
@@ -560,6 +562,49 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
 }  // namespace
 }  // namespace ispore
 
+// ---- top-K for callers that cannot allocate ------------------------------------------------
+//
+// Round 1 needs a place for the per-slice candidate lists.  ispore_topk_* takes it from the
+// caller; ispore_topk_static_f32 takes it from this array instead, which is part of the
+// library image: every GPU that loads the library holds these kStaticScratchBytes until the
+// process exits.  First kStaticScratchEntries int32 ids, then as many fp32 values.
+constexpr int kStaticScratchEntries = ISPORE_TOPK_STATIC_ENTRIES;
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(kStaticScratchEntries) * (sizeof(int32_t) + sizeof(float));
+static __device__ __align__(256) unsigned char g_topk_static_scratch[kStaticScratchBytes];
+
+namespace ispore {
+namespace {
+
+constexpr int kMaxStaticDevices = 64;
+std::mutex g_static_mutex;
+unsigned char* g_static_scratch_addr[kMaxStaticDevices] = {};
+
+// Device address of the scratch array on the CURRENT device.  In host code the array's name
+// is only a handle for the runtime, not something a kernel may dereference; the address a
+// kernel needs comes from cudaGetSymbolAddress, asked once per device with that device
+// current, and is cached.
+int static_scratch(unsigned char** out) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail(ISPORE_ELAUNCH, "topk_static: cudaGetDevice: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= kMaxStaticDevices) return fail(ISPORE_ELIMIT, "topk_static: device %d out of range", dev);
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_scratch_addr[dev] == nullptr) {
+        unsigned char* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_topk_static_scratch);
+        if (e != cudaSuccess || ptr == nullptr) {
+            (void)cudaGetLastError();
+            return fail(ISPORE_ELAUNCH, "topk_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        }
+        g_static_scratch_addr[dev] = ptr;
+    }
+    *out = g_static_scratch_addr[dev];
+    return ISPORE_OK;
+}
+
+}  // namespace
+}  // namespace ispore
+
 #ifdef ISPORE_TUNING
 extern "C" __attribute__((visibility("default"))) void ispore_topk_debug(int v) {
     cudaMemcpyToSymbol(ispore::g_topk_debug, &v, sizeof(int));
@@ -611,6 +656,32 @@ int ispore_sampling_f16(const int32_t* topk_ids, const void* topk_vals, const fl
     return ispore::sampling_dispatch<__half>(topk_ids, static_cast<const __half*>(topk_vals), uniform,
                                              output_ids, rows, K, temperature,
                                              static_cast<cudaStream_t>(stream));
+}
+
+int ispore_topk_static_f32(const float* probs, int64_t rows, int64_t vocab, int32_t K, int32_t* final_ids,
+                           float* final_vals, int32_t index_offset, const float* uniform, float temperature,
+                           int32_t* sampled_ids, ispore_stream_t stream) {
+    if (K < 1 || K > ISPORE_TOPK_MAX_K)
+        return ispore::fail(ISPORE_ELIMIT, "topk_static: K=%d outside [1,%d]", K, ISPORE_TOPK_MAX_K);
+    if (rows < 0) return ispore::fail(ISPORE_ESHAPE, "topk_static: rows=%lld", (long long)rows);
+    // The lists of one slice per row must fit; more slices are used when they fit too.
+    const int64_t per_slice = rows * K;
+    if (per_slice > kStaticScratchEntries)
+        return ispore::fail(ISPORE_ELIMIT,
+                            "topk_static: rows*K = %lld exceeds the built-in scratch of %d entries; use ispore_topk_f32 "
+                            "with caller-provided scratch",
+                            (long long)per_slice, kStaticScratchEntries);
+    int32_t slices = per_slice > 0 ? static_cast<int32_t>(kStaticScratchEntries / per_slice) : ISPORE_TOPK_REF_SLICES;
+    if (slices > ISPORE_TOPK_REF_SLICES) slices = ISPORE_TOPK_REF_SLICES;
+    unsigned char* base = nullptr;
+    if (int rc = ispore::static_scratch(&base)) return rc;
+    int32_t* scratch_ids = reinterpret_cast<int32_t*>(base);
+    float* scratch_vals = reinterpret_cast<float*>(base + static_cast<size_t>(kStaticScratchEntries) * sizeof(int32_t));
+    // Round 1 writes every slot round 2 reads (empty slots included), so whatever an earlier
+    // call left in the array is never seen and nothing has to be cleared.
+    return ispore::topk_dispatch<float>(probs, rows, vocab, K, scratch_ids, scratch_vals, slices, final_ids,
+                                        final_vals, index_offset, uniform, temperature, sampled_ids,
+                                        static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"
