@@ -51,7 +51,8 @@ enum {
 enum {
     ISPORE_DEV_BAD_TOKEN_ID = 1u << 0, /* embedding id outside [0, vocab)          */
     ISPORE_DEV_KV_OVERRUN = 1u << 1,   /* history+t >= max_seq_len: row skipped    */
-    ISPORE_DEV_BAD_PADDING = 1u << 2   /* un-padded token lands outside [0,bs*seq) */
+    ISPORE_DEV_BAD_PADDING = 1u << 2,  /* un-padded token lands outside [0,bs*seq) */
+    ISPORE_DEV_TIMEOUT = 1u << 3       /* a bounded wait on an async copy ran out     */
 };
 
 /* ---- library-level ------------------------------------------------------ */

@@ -13,7 +13,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libispore_kernels.so"
 
 ISPORE_OK = 0
 ISPORE_ENULL, ISPORE_ESHAPE, ISPORE_EALIGN, ISPORE_ELAUNCH, ISPORE_ESCRATCH, ISPORE_ELIMIT = -1, -2, -3, -4, -5, -6
-DEV_BAD_TOKEN_ID, DEV_KV_OVERRUN, DEV_BAD_PADDING = 1, 2, 4
+DEV_BAD_TOKEN_ID, DEV_KV_OVERRUN, DEV_BAD_PADDING, DEV_TIMEOUT = 1, 2, 4, 8
 TOPK_MAX_K = 256
 
 _p, _i64, _i32, _f = C.c_void_p, C.c_int64, C.c_int32, C.c_float

@@ -6,6 +6,7 @@
 // warp owns a row and moves it as 128-bit vectors, four independent loads in
 // flight per lane, rows taken grid-stride.
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace ispore {
 namespace {
@@ -44,6 +45,47 @@ embedding_gather_vec_kernel(const int32_t* __restrict__ ids, uint4* __restrict__
     }
 }
 
+// TMA variant: a row never touches registers.  Lane l of a one-warp CTA owns row
+// (blockIdx.x * ROWS + l): it asks the copy engine to bring the table row into its slot of
+// shared memory (cp.async.bulk, completion on the lane's own mbarrier), waits, and hands the
+// slot back to the engine for the store to the output row.  ROWS rows per CTA are in flight
+// together and many small CTAs per SM keep several hundred KB on the wire without a single
+// data register.  Needs row_bytes % 16 == 0 and 16-byte aligned bases.
+template <int ROWS>
+__global__ void __launch_bounds__(32)
+embedding_gather_tma_kernel(const int32_t* __restrict__ ids, unsigned char* __restrict__ out,
+                            const unsigned char* __restrict__ table, int64_t num_tokens, uint32_t row_bytes,
+                            int64_t vocab, unsigned* __restrict__ status) {
+    extern __shared__ __align__(128) unsigned char slots[];  // [ROWS][row_bytes]
+    __shared__ __align__(8) uint64_t full[ROWS];
+    const int lane = threadIdx.x;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * ROWS + lane;
+    const bool mine = lane < ROWS && t < num_tokens;
+    if (lane < ROWS) tma::mbar_init(&full[lane], 1);
+    tma::fence_mbar_init();
+    __syncwarp();
+    if (!mine) return;  // no block-level barrier below
+
+    const int64_t id = __ldg(ids + t);
+    unsigned char* dst = out + t * row_bytes;
+    if (vocab > 0 && (id < 0 || id >= vocab)) {
+        atomicOr(status, ISPORE_DEV_BAD_TOKEN_ID);
+        for (uint32_t o = 0; o < row_bytes; o += 16) *reinterpret_cast<uint4*>(dst + o) = make_uint4(0, 0, 0, 0);
+        return;
+    }
+    unsigned char* slot = slots + static_cast<size_t>(lane) * row_bytes;
+    tma::mbar_arrive_expect_tx(&full[lane], row_bytes);
+    tma::load(slot, table + id * row_bytes, row_bytes, &full[lane]);
+    if (!tma::mbar_wait(&full[lane], 0)) {
+        atomicOr(status, ISPORE_DEV_TIMEOUT);
+        tma::mbar_wait(&full[lane], 0);  // one more bounded wait for the copy in flight, then give up
+        return;
+    }
+    tma::store(dst, slot, row_bytes);
+    tma::commit_group();
+    tma::wait_group_read<0>();  // the slot must stay allocated until the engine has read it
+}
+
 template <typename T>
 __global__ void embedding_gather_scalar_kernel(const int32_t* __restrict__ ids, T* __restrict__ out,
                                                const T* __restrict__ table, int64_t num_tokens,
@@ -70,11 +112,33 @@ int embedding_dispatch(const int32_t* ids, T* out, const T* table, int64_t token
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "input_embedding: no device status word");
     constexpr int E = VecTraits<T>::kElems;
+    const int64_t row_bytes = hidden * static_cast<int64_t>(sizeof(T));
+    if (tune(kTuneEmbedding, 1004) >= 1000 && row_bytes % 16 == 0 && row_bytes <= 32 * 1024 && aligned16(out) && aligned16(table)) {
+        // rows per CTA so that one CTA's slots take about 32 KB of shared memory
+        const int variant = tune(kTuneEmbedding, 1004) - 1000;
+        const unsigned char* tb = reinterpret_cast<const unsigned char*>(table);
+        unsigned char* ob = reinterpret_cast<unsigned char*>(out);
+#define ISPORE_EMB_TMA(ROWS)                                                                                     \
+    do {                                                                                                         \
+        const size_t smem = static_cast<size_t>(ROWS) * row_bytes;                                               \
+        if (smem > 48 * 1024)                                                                                    \
+            cudaFuncSetAttribute(embedding_gather_tma_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                 static_cast<int>(smem));                                                        \
+        embedding_gather_tma_kernel<ROWS><<<static_cast<unsigned>(ceil_div(tokens, ROWS)), 32, smem, st>>>(      \
+            ids, ob, tb, tokens, static_cast<uint32_t>(row_bytes), vocab, status);                               \
+        return check_launch("embedding_gather_tma_kernel");                                                      \
+    } while (0)
+        if (variant == 1) ISPORE_EMB_TMA(1);
+        if (variant == 2) ISPORE_EMB_TMA(2);
+        if (variant == 8) ISPORE_EMB_TMA(8);
+        ISPORE_EMB_TMA(4);
+#undef ISPORE_EMB_TMA
+    }
     if (hidden % E == 0 && hidden / E <= INT32_MAX && aligned16(out) && aligned16(table)) {
         constexpr int THREADS = 256, UNROLL = 4;
         const int64_t blocks = ceil_div(tokens, THREADS / 32);
         auto kernel = embedding_gather_vec_kernel<THREADS, UNROLL>;
-        kernel<<<persistent_grid(kernel, THREADS, 0, blocks, tune(kTuneEmbedding, 16)), THREADS, 0, st>>>(
+        kernel<<<persistent_grid(kernel, THREADS, 0, blocks, 16), THREADS, 0, st>>>(
                 ids, reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(table), tokens,
                 static_cast<int>(hidden / E), vocab, status);
         return check_launch("embedding_gather_vec_kernel");

@@ -33,18 +33,23 @@ int fill_denominators(RopeDenominators* out, int rot_dim, float base) {
     return 0;
 }
 
-template <typename T, int THREADS>
+// HEAD_SIZE > 0 fixes the head size at compile time (the task -> (head, vector) split becomes
+// shifts instead of run-time divisions, which otherwise cost as much as the arithmetic);
+// HEAD_SIZE == 0 takes it from the argument.  FULL_ROT: rotary_dim == head_size, so the
+// per-element "is this pair rotated" test disappears.  HAS_BIAS likewise.
+template <typename T, int THREADS, int HEAD_SIZE, bool FULL_ROT, bool HAS_BIAS, int STORE = 0>
 __global__ void __launch_bounds__(THREADS)
 qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* __restrict__ v_buf,
                               const T* __restrict__ QKV, const T* __restrict__ bias,
                               const int32_t* __restrict__ padding_offset,
                               const int32_t* __restrict__ history_length, int64_t batch_size,
                               int64_t seq_len, int64_t token_num, int head_num, int kv_head_num,
-                              int head_size, int rot_half, const RopeDenominators freq,
+                              int head_size_arg, int rot_half, const RopeDenominators freq,
                               unsigned* __restrict__ status) {
     constexpr int E = VecTraits<T>::kElems;
     __shared__ float2 cos_sin[kMaxRotHalf];
     const int tid = threadIdx.x;
+    const int head_size = HEAD_SIZE > 0 ? HEAD_SIZE : head_size_arg;
     const int head_vecs = head_size / E;
     const int half_vecs = head_vecs / 2;
     const int qkv_heads = head_num + 2 * kv_head_num;
@@ -52,14 +57,49 @@ qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
     const int v_tasks = kv_head_num * head_vecs;
     const uint4* bias_v = reinterpret_cast<const uint4*>(bias);
 
+    constexpr int U = 4;  // tasks per thread per trip
     for (int64_t token = blockIdx.x; token < token_num; token += gridDim.x) {
+        // The token's data does not depend on where it lands: start the first trip's loads
+        // now, so they fly while the position is looked up and cos/sin are evaluated.
+        const uint4* src = reinterpret_cast<const uint4*>(QKV) + token * qkv_heads * head_vecs;
+        const uint4* vsrc = src + (head_num + kv_head_num) * head_vecs;
+        uint4 lo_raw[U], hi_raw[U], v_raw[U];
+        auto load_rope_trip = [&](int task0) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int task = task0 + u * THREADS;
+                if (task < rope_tasks) {
+                    const int hh = task / half_vecs;
+                    const int c = task - hh * half_vecs;
+                    lo_raw[u] = ld_stream(src + hh * head_vecs + c);
+                    hi_raw[u] = ld_stream(src + hh * head_vecs + half_vecs + c);
+                }
+            }
+        };
+        auto load_v_trip = [&](int task0) {
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int task = task0 + u * THREADS;
+                if (task < v_tasks) v_raw[u] = ld_stream(vsrc + task);
+            }
+        };
+        load_rope_trip(tid);
+        load_v_trip(tid);
         const int64_t dst_token = token + __ldg(padding_offset + token);
         if (dst_token < 0 || dst_token >= batch_size * seq_len) {
             if (tid == 0) atomicOr(status, ISPORE_DEV_BAD_PADDING);
             continue;  // uniform over the CTA
         }
-        const int64_t b = dst_token / seq_len;
-        const int64_t s = dst_token - b * seq_len;
+        // One 64-bit division per token (32-bit when the destination index allows it).
+        int64_t b, s;
+        if (dst_token < (1ll << 31) && seq_len < (1ll << 31)) {
+            const uint32_t bq = static_cast<uint32_t>(dst_token) / static_cast<uint32_t>(seq_len);
+            b = bq;
+            s = static_cast<uint32_t>(dst_token) - bq * static_cast<uint32_t>(seq_len);
+        } else {
+            b = dst_token / seq_len;
+            s = dst_token - b * seq_len;
+        }
         const float m = static_cast<float>(__ldg(history_length + b) + static_cast<int>(s));
 
         __syncthreads();  // previous token's readers are done with cos_sin
@@ -70,65 +110,79 @@ qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
         }
         __syncthreads();
 
-        const uint4* src = reinterpret_cast<const uint4*>(QKV) + token * qkv_heads * head_vecs;
+        // Row (b, head 0, s) of q and of k/v, in vectors; heads are seq_len*head_vecs apart.
+        const int64_t head_stride = seq_len * head_vecs;
+        uint4* q_row = reinterpret_cast<uint4*>(q_buf) + (b * head_num * seq_len + s) * head_vecs;
+        uint4* k_row = reinterpret_cast<uint4*>(k_buf) + (b * kv_head_num * seq_len + s) * head_vecs;
+        uint4* v_row = reinterpret_cast<uint4*>(v_buf) + (b * kv_head_num * seq_len + s) * head_vecs;
 
-        // q and k heads: rotate (low-half vector, high-half vector) pairs.
-#pragma unroll 2
-        for (int task = tid; task < rope_tasks; task += THREADS) {
-            const int hh = task / half_vecs;  // head index inside [q heads | k heads]
-            const int c = task - hh * half_vecs;
-            const uint4 lo_raw = ld_stream(src + hh * head_vecs + c);
-            const uint4 hi_raw = ld_stream(src + hh * head_vecs + half_vecs + c);
-            Unpacked<T> lo, hi;
-            unpack(lo_raw, lo);
-            unpack(hi_raw, hi);
-            if (bias != nullptr) {
-                Unpacked<T> blo, bhi;
-                unpack(ld_keep(bias_v + hh * head_vecs + c), blo);
-                unpack(ld_keep(bias_v + hh * head_vecs + half_vecs + c), bhi);
+        // q and k heads: rotate (low-half vector, high-half vector) pairs, U tasks per trip
+        // with all loads of the trip issued before the first use.
+        for (int task0 = tid; task0 < rope_tasks; task0 += THREADS * U) {
+            if (task0 != tid) load_rope_trip(task0);  // the first trip is already on its way
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    lo.v[e] += blo.v[e];
-                    hi.v[e] += bhi.v[e];
+            for (int u = 0; u < U; ++u) {
+                const int task = task0 + u * THREADS;
+                if (task < rope_tasks) {
+                    const int hh = task / half_vecs;  // head index inside [q heads | k heads]
+                    const int c = task - hh * half_vecs;
+                    Unpacked<T> lo, hi;
+                    unpack(lo_raw[u], lo);
+                    unpack(hi_raw[u], hi);
+                    if (HAS_BIAS) {
+                        Unpacked<T> blo, bhi;
+                        unpack(ld_keep(bias_v + hh * head_vecs + c), blo);
+                        unpack(ld_keep(bias_v + hh * head_vecs + half_vecs + c), bhi);
+#pragma unroll
+                        for (int e = 0; e < E; ++e) {
+                            lo.v[e] += blo.v[e];
+                            hi.v[e] += bhi.v[e];
+                        }
+                    }
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        const int j = c * E + e;
+                        if (FULL_ROT || j < rot_half) {
+                            const float2 cs = cos_sin[j];
+                            const float x0 = lo.v[e], x1 = hi.v[e];
+                            lo.v[e] = cs.x * x0 - cs.y * x1;
+                            hi.v[e] = cs.x * x1 + cs.y * x0;
+                        }
+                    }
+                    const bool is_q = hh < head_num;
+                    uint4* dst = is_q ? q_row + hh * head_stride : k_row + (hh - head_num) * head_stride;
+                    if (STORE == 0) {
+                        st_stream(dst + c, pack(lo));
+                        st_stream(dst + half_vecs + c, pack(hi));
+                    } else {
+                        dst[c] = pack(lo);
+                        dst[half_vecs + c] = pack(hi);
+                    }
                 }
             }
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-                const int j = c * E + e;
-                if (j < rot_half) {
-                    const float2 cs = cos_sin[j];
-                    const float x0 = lo.v[e], x1 = hi.v[e];
-                    lo.v[e] = cs.x * x0 - cs.y * x1;
-                    hi.v[e] = cs.x * x1 + cs.y * x0;
-                }
-            }
-            const bool is_q = hh < head_num;
-            const int h = is_q ? hh : hh - head_num;
-            T* base = is_q ? q_buf : k_buf;
-            const int64_t heads = is_q ? head_num : kv_head_num;
-            uint4* dst = reinterpret_cast<uint4*>(base) + ((b * heads + h) * seq_len + s) * head_vecs;
-            st_stream(dst + c, pack(lo));
-            st_stream(dst + half_vecs + c, pack(hi));
         }
 
         // v heads: bias add and transposed copy.
-        const uint4* vsrc = src + (head_num + kv_head_num) * head_vecs;
-#pragma unroll 2
-        for (int task = tid; task < v_tasks; task += THREADS) {
-            const int h = task / head_vecs;
-            const int c = task - h * head_vecs;
-            uint4 raw = ld_stream(vsrc + task);
-            if (bias != nullptr) {
-                Unpacked<T> x, bb;
-                unpack(raw, x);
-                unpack(ld_keep(bias_v + (head_num + kv_head_num) * head_vecs + task), bb);
+        for (int task0 = tid; task0 < v_tasks; task0 += THREADS * U) {
+            if (task0 != tid) load_v_trip(task0);
 #pragma unroll
-                for (int e = 0; e < E; ++e) x.v[e] += bb.v[e];
-                raw = pack(x);
+            for (int u = 0; u < U; ++u) {
+                const int task = task0 + u * THREADS;
+                if (task < v_tasks) {
+                    const int h = task / head_vecs;
+                    const int c = task - h * head_vecs;
+                    if (HAS_BIAS) {
+                        Unpacked<T> x, bb;
+                        unpack(v_raw[u], x);
+                        unpack(ld_keep(bias_v + (head_num + kv_head_num) * head_vecs + task), bb);
+#pragma unroll
+                        for (int e = 0; e < E; ++e) x.v[e] += bb.v[e];
+                        v_raw[u] = pack(x);
+                    }
+                    if (STORE == 0) st_stream(v_row + h * head_stride + c, v_raw[u]);
+                    else v_row[h * head_stride + c] = v_raw[u];
+                }
             }
-            uint4* dst = reinterpret_cast<uint4*>(v_buf) +
-                         ((b * kv_head_num + h) * seq_len + s) * head_vecs;
-            st_stream(dst + c, raw);
         }
     }
 }
@@ -247,20 +301,50 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
     const bool vec_ok = head_size % (2 * E) == 0 && aligned16(q_buf) && aligned16(k_buf) &&
                         aligned16(v_buf) && aligned16(QKV) && (bias == nullptr || aligned16(bias));
     if (vec_ok) {
-        const int variant = tune(kTuneQkv, 127);
-        if (variant >= 10) {
-            constexpr int TH = 128;
-            const int grid = persistent_grid(qkv_rope_transpose_vec_kernel<T, TH>, TH, 0, token_num, variant - 9);
-            qkv_rope_transpose_vec_kernel<T, TH><<<grid, TH, 0, st>>>(
+        // One token per CTA, as many CTAs as tokens: measured faster on B200 than a persistent
+        // grid-stride loop (the CTA scheduler walks the tokens in address order).
+        constexpr int TH = 64;
+        const int grid = static_cast<int>(token_num < (1ll << 30) ? token_num : (1ll << 30));
+        const bool full_rot = rot_dim == head_size;
+        const bool has_bias = bias != nullptr;
+#define ISPORE_QKV(HS, FR, HB)                                                                           \
+    do {                                                                                                 \
+        qkv_rope_transpose_vec_kernel<T, TH, HS, FR, HB><<<grid, TH, 0, st>>>(                           \
+            q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,        \
+            token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);     \
+        return check_launch("qkv_rope_transpose_vec_kernel");                                           \
+    } while (0)
+#ifdef ISPORE_TUNING
+        if (head_size == 128 && full_rot && has_bias && tune(kTuneQkv, 0) == 1) {
+            qkv_rope_transpose_vec_kernel<T, TH, 128, true, true, 1><<<grid, TH, 0, st>>>(
                 q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
                 token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
-            return check_launch("qkv_rope_transpose_vec_kernel");
+            return check_launch("qkv");
         }
-        const int grid = persistent_grid(qkv_rope_transpose_vec_kernel<T, THREADS>, THREADS, 0, token_num, variant + 1);
-        qkv_rope_transpose_vec_kernel<T, THREADS><<<grid, THREADS, 0, st>>>(
-            q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
-            token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
-        return check_launch("qkv_rope_transpose_vec_kernel");
+        if (head_size == 128 && full_rot && has_bias && tune(kTuneQkv, 0) == 2) {
+            qkv_rope_transpose_vec_kernel<T, 256, 128, true, true, 0><<<grid, 256, 0, st>>>(
+                q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
+                token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
+            return check_launch("qkv");
+        }
+        if (head_size == 128 && full_rot && has_bias && tune(kTuneQkv, 0) == 3) {
+            qkv_rope_transpose_vec_kernel<T, 64, 128, true, true, 0><<<grid, 64, 0, st>>>(
+                q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
+                token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
+            return check_launch("qkv");
+        }
+#endif
+        if (head_size == 128 && full_rot) {
+            if (has_bias) ISPORE_QKV(128, true, true);
+            ISPORE_QKV(128, true, false);
+        }
+        if (head_size == 64 && full_rot) {
+            if (has_bias) ISPORE_QKV(64, true, true);
+            ISPORE_QKV(64, true, false);
+        }
+        if (has_bias) ISPORE_QKV(0, false, true);
+        ISPORE_QKV(0, false, false);
+#undef ISPORE_QKV
     }
     const int grid = persistent_grid(qkv_rope_transpose_scalar_kernel<T, THREADS>, THREADS, 0, token_num);
     qkv_rope_transpose_scalar_kernel<T, THREADS><<<grid, THREADS, 0, st>>>(

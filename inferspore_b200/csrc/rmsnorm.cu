@@ -25,14 +25,18 @@ enum class ResidualMode : int {
 // value the norm is defined on), which keeps the register count low enough for
 // MIN_BLOCKS CTAs per SM; gamma is re-read through L1 (it is 8 KB and shared by
 // every row) instead of occupying registers.
-template <typename T, int VPT, int THREADS, int MIN_BLOCKS>
+// MODE is the ResidualMode; FAST means the row is exactly VPT*THREADS vectors long and there is
+// no bias, so no per-vector guard (each costs a branch) and no bias test remain in the loop.
+template <typename T, int VPT, int THREADS, int MIN_BLOCKS, int MODE, bool FAST>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
-rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __restrict__ bias,
+rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __restrict__ bias_arg,
                            const T* __restrict__ gamma, float eps, int64_t num_tokens,
-                           int hidden_vecs, int hidden, int mode_i) {
+                           int hidden_vecs_arg, int hidden) {
     constexpr int kWarps = THREADS / 32;
     constexpr int E = VecTraits<T>::kElems;
-    const ResidualMode mode = static_cast<ResidualMode>(mode_i);
+    constexpr ResidualMode mode = static_cast<ResidualMode>(MODE);
+    const int hidden_vecs = FAST ? VPT * THREADS : hidden_vecs_arg;
+    const T* bias = FAST ? nullptr : bias_arg;
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
     __shared__ float partial[2][kWarps];
@@ -48,7 +52,7 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = tid + i * THREADS;
-            if (v < hidden_vecs) {
+            if (FAST || v < hidden_vecs) {
                 s_raw[i] = ld_stream(xrow + v);
                 if (mode == ResidualMode::kAdd) r_raw[i] = ld_stream(rrow + v);
             }
@@ -58,7 +62,7 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = tid + i * THREADS;
-            if (v < hidden_vecs) {
+            if (FAST || v < hidden_vecs) {
                 Unpacked<T> s;
                 unpack(s_raw[i], s);
                 if (mode == ResidualMode::kAdd) {
@@ -96,7 +100,7 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = tid + i * THREADS;
-            if (v < hidden_vecs) {
+            if (FAST || v < hidden_vecs) {
                 Unpacked<T> s, g;
                 unpack(s_raw[i], s);
                 unpack(ld_keep(gamma_v + v), g);
@@ -151,15 +155,30 @@ rmsnorm_generic_kernel(T* __restrict__ x, T* __restrict__ r, const T* __restrict
     }
 }
 
+template <typename T, int VPT, int THREADS, int MIN_BLOCKS, int MODE, bool FAST>
+int launch_regs_as(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens, int64_t hidden,
+                   cudaStream_t st) {
+    const int hidden_vecs = static_cast<int>(hidden / VecTraits<T>::kElems);
+    auto kernel = rmsnorm_row_in_regs_kernel<T, VPT, THREADS, MIN_BLOCKS, MODE, FAST>;
+    // One row per CTA and as many CTAs as rows: measured faster on B200 than a persistent loop.
+    const int grid = static_cast<int>(tokens < (1ll << 30) ? tokens : (1ll << 30));
+    kernel<<<grid, THREADS, 0, st>>>(x, r, bias, gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden));
+    return check_launch("rmsnorm_row_in_regs_kernel");
+}
+
 template <typename T, int VPT, int THREADS, int MIN_BLOCKS>
 int launch_regs(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens, int64_t hidden,
                 ResidualMode mode, cudaStream_t st) {
-    const int hidden_vecs = static_cast<int>(hidden / VecTraits<T>::kElems);
-    auto kernel = rmsnorm_row_in_regs_kernel<T, VPT, THREADS, MIN_BLOCKS>;
-    const int grid = persistent_grid(kernel, THREADS, 0, tokens, tune(kTuneConcat, 64));
-    kernel<<<grid, THREADS, 0, st>>>(x, r, bias, gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden),
-                                     static_cast<int>(mode));
-    return check_launch("rmsnorm_row_in_regs_kernel");
+    const bool fast = bias == nullptr && hidden == static_cast<int64_t>(VPT) * THREADS * VecTraits<T>::kElems;
+#define ISPORE_NORM_MODE(M)                                                                                  \
+    return fast ? launch_regs_as<T, VPT, THREADS, MIN_BLOCKS, M, true>(x, r, bias, gamma, eps, tokens, hidden, st) \
+                : launch_regs_as<T, VPT, THREADS, MIN_BLOCKS, M, false>(x, r, bias, gamma, eps, tokens, hidden, st)
+    switch (mode) {
+        case ResidualMode::kAdd: ISPORE_NORM_MODE(1);
+        case ResidualMode::kCopyOut: ISPORE_NORM_MODE(2);
+        default: ISPORE_NORM_MODE(0);
+    }
+#undef ISPORE_NORM_MODE
 }
 
 template <typename T>

@@ -42,7 +42,9 @@ struct ExpPolicy<__half> {
 // THREADS/GROUP groups.  Each thread keeps VPT 128-bit vectors of a row and the
 // matching slice of the additive mask term.  A group works on HG heads of one
 // (b, q) pair per trip.
-template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS = 1>
+// FULL: every row is exactly VPT*GROUP vectors long and heads is a multiple of HG, so the
+// per-vector and per-head guards (and the branches they cost) disappear.
+template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS, bool FULL>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
                           uint32_t units /* batch*q_len*head_groups */, uint32_t head_groups,
@@ -71,7 +73,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
         const uint32_t hg = t % head_groups;
         const uint32_t b = t / head_groups;
         const uint32_t h0 = hg * HG;
-        const int nh = live ? static_cast<int>(min(static_cast<uint32_t>(HG), heads - h0)) : 0;
+        const int nh = FULL ? (live ? HG : 0) : (live ? static_cast<int>(min(static_cast<uint32_t>(HG), heads - h0)) : 0);
 
         const uint4* mrow = reinterpret_cast<const uint4*>(mask) + (static_cast<int64_t>(b) * q_len + qi) * row_vecs;
         const int64_t row0 = (static_cast<int64_t>(b) * heads + h0) * q_len + qi;  // row of head h0
@@ -84,14 +86,14 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = gt + i * GROUP;
-            if (live && v < row_vecs) m_raw[i] = ld_keep(mrow + v);
+            if (live && (FULL || v < row_vecs)) m_raw[i] = ld_keep(mrow + v);
         }
 #pragma unroll
         for (int hh = 0; hh < HG; ++hh) {
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = gt + i * GROUP;
-                if (hh < nh && v < row_vecs) q_raw[hh][i] = ld_stream(qrow0 + hh * head_stride_vecs + v);
+                if (hh < nh && (FULL || v < row_vecs)) q_raw[hh][i] = ld_stream(qrow0 + hh * head_stride_vecs + v);
             }
         }
         // Additive mask term (1 - mask) * (-10000), prescaled; -inf-like filler beyond the row.
@@ -99,7 +101,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = gt + i * GROUP;
-            if (live && v < row_vecs) {
+            if (live && (FULL || v < row_vecs)) {
                 unpack(m_raw[i], term[i]);
 #pragma unroll
                 for (int e = 0; e < E; ++e) term[i].v[e] = (1.0f - term[i].v[e]) * neg;
@@ -114,7 +116,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int v = gt + i * GROUP;
-                    if (v < row_vecs) {
+                    if (FULL || v < row_vecs) {
                         unpack(q_raw[hh][i], z[i]);
 #pragma unroll
                         for (int e = 0; e < E; ++e) {
@@ -134,7 +136,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int v = gt + i * GROUP;
-                    if (v < row_vecs) {
+                    if (FULL || v < row_vecs) {
 #pragma unroll
                         for (int e = 0; e < E; ++e) {
                             z[i].v[e] = Exp::exp_diff(z[i].v[e], mx);
@@ -154,7 +156,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int v = gt + i * GROUP;
-                    if (v < row_vecs) {
+                    if (FULL || v < row_vecs) {
 #pragma unroll
                         for (int e = 0; e < E; ++e) z[i].v[e] *= inv;
                         st_stream(orow0 + hh * head_stride_vecs + v, pack(z[i]));
@@ -216,7 +218,9 @@ int launch_groups(T* score, const T* qk, const T* mask, int64_t batch, int64_t h
     const int64_t head_groups = ceil_div(heads, HG);
     const int64_t units = batch * q_len * head_groups;
     const int64_t ctas = ceil_div(units, kGroupsPerCta);
-    auto kernel = softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS>;
+    const bool full = row_vecs == VPT * GROUP && heads % HG == 0;
+    auto kernel = full ? softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, true>
+                       : softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, false>;
     // One trip per CTA for any realistic size: the hardware scheduler hands out CTAs in
     // address order, which keeps the DRAM access front compact.
     const int grid = static_cast<int>(ctas < (1 << 30) ? ctas : (1 << 30));
@@ -274,7 +278,7 @@ int softmax_dispatch(T* score, const T* qk, const T* mask, int64_t batch, int64_
                 default: break;
             }
 #endif
-            return launch_groups<T, 2, 256, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
+            return launch_groups<T, 4, 128, 128, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
         }
         if (vecs <= 1024) ISPORE_SOFTMAX(4, 256, 256, 2);
         if (vecs <= 2048) ISPORE_SOFTMAX(4, 512, 512, 2);
