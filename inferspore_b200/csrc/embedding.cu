@@ -2,9 +2,11 @@
 //
 // Semantics: src/kernels/input_embedding.cu:5-23 of the reference —
 // output[t, :] = table[input_ids[t], :], a bit-exact row copy.  The reference
-// moves one element per thread-iteration with a div/mod per element; here one
-// warp owns a row and moves it as 128-bit vectors, four independent loads in
-// flight per lane, rows taken grid-stride.
+// moves one element per thread-iteration with a div/mod per element.  Default
+// path here: TMA bulk copies, one lane per row (table row -> shared memory ->
+// output row), nothing in registers.  Fallback for rows that are not a multiple
+// of 16 bytes or larger than 32 KB: one warp per row moving 128-bit vectors,
+// four independent loads in flight per lane; then a scalar kernel.
 #include "common.cuh"
 #include "tma.cuh"
 

@@ -29,6 +29,7 @@
 #include <mutex>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace ispore {
 namespace {
@@ -44,7 +45,7 @@ constexpr int kTopkThreads = 256;
 constexpr int kTopkWarps = kTopkThreads / 32;
 constexpr int kElemsPerThread = 32;                          // keys a thread holds per tile
 constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
-constexpr int kTileCap = 768;                                // survivors a tile may add on the fast path
+constexpr int kTileCap = 256;                                // survivors a tile may add on the fast path
 constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + tile survivors
 constexpr int kMergeCap = 4096;                              // lists*K candidates the merge kernel holds
 
@@ -248,13 +249,20 @@ __device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int
     }
 }
 
-template <typename T, int MIN_BLOCKS>
+// TMA: the tiles arrive through the copy engine (cp.async.bulk into one of two shared-memory
+// stages, completion on an mbarrier), issued one tile ahead, so tile t+1 is on its way while
+// tile t is being thresholded and ranked; the registers are filled from shared memory.  Needs
+// the vector-load conditions (16-byte aligned rows, slice length a multiple of the vector).
+// Without TMA the tile is loaded straight into registers.
+template <typename T, int MIN_BLOCKS, bool TMA>
 __global__ void __launch_bounds__(kTopkThreads, MIN_BLOCKS)
 topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int slices, int K,
                   int32_t* __restrict__ out_ids_base, T* __restrict__ out_vals_base, int out_lists,
-                  int32_t index_offset, int vec_loads) {
+                  int32_t index_offset, int vec_loads, unsigned* __restrict__ status) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int kVecs = kElemsPerThread / E;
+    extern __shared__ __align__(128) unsigned char stage_raw[];  // TMA: [2][kTileElems * sizeof(T)]
+    __shared__ __align__(8) uint64_t full[2];
     __shared__ unsigned long long cand[2][kCandSlots];  // [cur]: running best then tile survivors
     __shared__ uint32_t warp_thr[kTopkWarps];
     __shared__ int s_count;
@@ -275,10 +283,55 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     int nbest = 0;  // entries of the running best (sorted, best first)
     const int q = (K + kTopkWarps - 1) / kTopkWarps;
 
-    for (int tile_begin = 0; tile_begin < n; tile_begin += kTileElems) {
+    constexpr uint32_t kStageBytes = kTileElems * sizeof(T);
+    auto tile_bytes = [&](int tile_begin) {
+        const int left = n - tile_begin;
+        return static_cast<uint32_t>(left < kTileElems ? left : kTileElems) * static_cast<uint32_t>(sizeof(T));
+    };
+    if (TMA) {
+        if (tid == 0) {
+            tma::mbar_init(&full[0], 1);
+            tma::mbar_init(&full[1], 1);
+            tma::fence_mbar_init();
+        }
+        __syncthreads();
+        if (tid == 0 && n > 0) {
+            tma::mbar_arrive_expect_tx(&full[0], tile_bytes(0));
+            tma::load(stage_raw, src, tile_bytes(0), &full[0]);
+        }
+    }
+
+    int tile_no = 0;
+    for (int tile_begin = 0; tile_begin < n; tile_begin += kTileElems, ++tile_no) {
         int bits[kElemsPerThread];
         int pmax;
-        load_tile_bits<T>(src, n, tile_begin, vec_loads != 0, bits, pmax);
+        const T* stage = reinterpret_cast<const T*>(stage_raw + static_cast<size_t>(tile_no & 1) * kStageBytes);
+        if (TMA) {
+            const bool arrived = tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1);
+            if (__syncthreads_or(!arrived)) {  // uniform: a copy did not land in time
+                if (tid == 0) {
+                    atomicOr(status, ISPORE_DEV_TIMEOUT);
+                    tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1);  // once more for the copy in flight
+                }
+                return;
+            }
+            pmax = INT_MIN;
+            const uint4* stage_v = reinterpret_cast<const uint4*>(stage);
+#pragma unroll
+            for (int k = 0; k < kVecs; ++k) {
+                const int v = tid + k * kTopkThreads;
+                const bool ok = tile_begin + v * E < n;
+                Unpacked<T> x;
+                if (ok) unpack(stage_v[v], x);
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    bits[k * E + e] = ok ? __float_as_int(x.v[e]) : INT_MIN;
+                    pmax = max(pmax, bits[k * E + e]);
+                }
+            }
+        } else {
+            load_tile_bits<T>(src, n, tile_begin, vec_loads != 0, bits, pmax);
+        }
         // Slot i of this thread is slice element elem_of(i); a slot is live iff that is < n.
         auto elem_of = [&](int i) { return tile_begin + (tid + (i / E) * kTopkThreads) * E + (i % E); };
 
@@ -301,6 +354,15 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             thr = warp_thr[0];
 #pragma unroll
             for (int w = 1; w < kTopkWarps; ++w) thr = min(thr, warp_thr[w]);
+        }
+
+        // Every thread has its tile in registers (the barrier above): the other stage is free,
+        // so the next tile can start flying now and land while this one is ranked.
+        if (TMA && tid == 0 && tile_begin + kTileElems < n) {
+            const int next = tile_begin + kTileElems;
+            uint64_t* bar = &full[(tile_no + 1) & 1];
+            tma::mbar_arrive_expect_tx(bar, tile_bytes(next));
+            tma::load(stage_raw + static_cast<size_t>((tile_no + 1) & 1) * kStageBytes, src + next, tile_bytes(next), bar);
         }
 
         // Survivor mask of this thread's 32 slots.
@@ -327,7 +389,8 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
                 const int el = elem_of(i);
                 // The slot's value is re-read (cache hit) rather than picked out of the register
                 // array with a run-time index.
-                mine[pos++] = composite(order_key(to_float<T>(src[el])), static_cast<uint32_t>(begin + el));
+                const T value = TMA ? stage[el - tile_begin] : src[el];
+                mine[pos++] = composite(order_key(to_float<T>(value)), static_cast<uint32_t>(begin + el));
             }
         }
         __syncthreads();
@@ -526,8 +589,24 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     // least 1024 elements per slice, never more than the scratch or the merge kernel hold.
     const int variant = tune(kTuneTopk, 0);
     const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
-    auto kernel = (variant & 1) ? topk_slice_kernel<T, 3> : topk_slice_kernel<T, 4>;
-    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, 0);
+    const int vec_loads = (vocab % E == 0) && aligned16(probs);
+    const bool use_tma = vec_loads && !(variant & 1);
+    constexpr size_t kTmaSmem = 2 * static_cast<size_t>(kTileElems) * sizeof(T);
+    auto kernel = use_tma ? topk_slice_kernel<T, 3, true> : topk_slice_kernel<T, 4, false>;
+    const size_t smem = use_tma ? kTmaSmem : 0;
+    if (use_tma && kTmaSmem > 48 * 1024) {
+        static bool raised[64] = {};  // per device (and per instantiation); setting it twice is harmless
+        int dev = 0;
+        (void)cudaGetDevice(&dev);
+        if (dev < 0 || dev >= 64 || !raised[dev]) {
+            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTmaSmem));
+            if (e != cudaSuccess) return fail(ISPORE_ELAUNCH, "topk: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
+            if (dev >= 0 && dev < 64) raised[dev] = true;
+        }
+    }
+    unsigned* status = device_status_ptr();
+    if (status == nullptr) return fail(ISPORE_ELAUNCH, "topk: no device status word");
+    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, smem);
     int64_t slices;
     switch (variant >> 1) {
         case 1: slices = ceil_div(vocab, kTileElems); if (ceil_div(resident, rows) > slices) slices = ceil_div(resident, rows); break;
@@ -541,19 +620,19 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     int64_t slice_len = ceil_div(ceil_div(vocab, slices), E) * E;
     slices = ceil_div(vocab, slice_len);
     if (rows * slices > INT32_MAX) return fail(ISPORE_ELIMIT, "topk: rows*slices too large");
-    const int vec_loads = (vocab % E == 0) && aligned16(probs);
 
     if (slices == 1) {
         // The slice kernel's sorted list is already the answer.
-        kernel<<<static_cast<int>(rows), kTopkThreads, 0, st>>>(probs, vocab, static_cast<int>(slice_len), 1, K,
-                                                                final_ids, final_vals, 1, index_offset, vec_loads);
+        kernel<<<static_cast<int>(rows), kTopkThreads, smem, st>>>(probs, vocab, static_cast<int>(slice_len), 1, K,
+                                                                   final_ids, final_vals, 1, index_offset, vec_loads,
+                                                                   status);
         if (int rc = check_launch("topk_slice_kernel")) return rc;
         if (uniform == nullptr) return ISPORE_OK;
         return sampling_dispatch<T>(final_ids, final_vals, uniform, sampled_ids, rows, K, temperature, st);
     }
-    kernel<<<static_cast<int>(rows * slices), kTopkThreads, 0, st>>>(
+    kernel<<<static_cast<int>(rows * slices), kTopkThreads, smem, st>>>(
         probs, vocab, static_cast<int>(slice_len), static_cast<int>(slices), K, scratch_ids, scratch_vals,
-        scratch_slices, index_offset, vec_loads);
+        scratch_slices, index_offset, vec_loads, status);
     if (int rc = check_launch("topk_slice_kernel")) return rc;
     return merge_dispatch<T>(scratch_ids, scratch_vals, rows, static_cast<int32_t>(slices), scratch_slices, K,
                              final_ids, final_vals, uniform, temperature, sampled_ids, st);
