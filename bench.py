@@ -45,6 +45,11 @@ FALLBACK_HBM_GBS = 6650.0
 KERNELS = ["input_embedding", "rmsnorm", "qkv_bias_rope_transpose", "concat_kv", "scale_mask_softmax",
            "add_residual_rmsnorm", "silu_mul", "topk_sampling"]
 LAUNCHES_PER_STEP = 9  # one per kernel, two for top-K (slice round + merge round)
+# DRAM traffic of the roofline kernel (SiLU*up) from the ncu capture summarised in
+# profiles/silu_mul_16384tok.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch at 16,384
+# tokens (1,036.1 MB) over that launch's algorithmic bytes (1,082.1 MB).  The kernel is a flat
+# streaming pass, so traffic grows in proportion to the rows; a full-size launch is scaled by it.
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1036.1 / 1082.13
 
 
 def algorithmic_bytes(tokens: int, topk_rows: int) -> dict:
@@ -351,6 +356,9 @@ def run_ours(args) -> dict:
     device = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        # NCCL prints its version banner on stdout at VERSION/INFO level; stdout carries the one JSON line.
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
@@ -436,7 +444,8 @@ def run_ours(args) -> dict:
         "kernels": kernels,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
                      "frac": round(kernels[dom]["gbs"] / peak, 4), "peak_kind": f"{peak_kind} copy bandwidth",
-                     "traffic": args.traffic},
+                     "traffic": args.traffic if args.traffic is not None
+                     else round(NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per[dom])},
         "clocks": clocks.summary(),
         "e2e": {"value": round(world * args.e2e_tokens / (e2e_ms_per_step * 1e-3), 1), "unit": "rows/s",
                 "h2d_bytes_per_step": hd.h2d, "d2h_bytes_per_step": hd.d2h, "rows_per_step": args.e2e_tokens,
@@ -511,7 +520,7 @@ def main() -> int:
     ap.add_argument("--only", choices=KERNELS, default=None,
                     help="run one kernel of the chain alone at --tokens (small cases for profiler captures)")
     ap.add_argument("--traffic", type=float, default=None,
-                    help="DRAM bytes per launch of the roofline kernel from an ncu capture (profiles/)")
+                    help="override: DRAM bytes per launch of the roofline kernel from a fresh ncu capture")
     args = ap.parse_args()
     if args.tokens % SEQ or args.e2e_tokens % SEQ or args.tokens <= 0:
         ap.error("--tokens and --e2e-tokens must be positive multiples of 512")

@@ -611,6 +611,8 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     switch (variant >> 1) {
         case 1: slices = ceil_div(vocab, kTileElems); if (ceil_div(resident, rows) > slices) slices = ceil_div(resident, rows); break;
         case 2: slices = 8; break;
+        case 3: slices = 2; break;
+        case 4: slices = 3; break;
         default: slices = resident / rows; if (slices < 1) slices = 1; break;
     }
     if (slices > ceil_div(vocab, 1024)) slices = ceil_div(vocab, 1024);
