@@ -315,6 +315,58 @@ ISPORE_API int ispore_sampling_f16(const int32_t* topk_ids, const void* topk_val
                                    const float* uniform, int32_t* output_ids, int64_t rows,
                                    int32_t K, float temperature, ispore_stream_t stream);
 
+/* ---- layout kernels either side of attention ---------------------------------------------- *
+ * Causal / padding mask.
+ * ref: src/kernels/build_casual_mask.h:7-10 (launchBuildCausalMasks), .cu:5-42 (kernel; the
+ *      predicate is line 36), :44-54 (launcher).
+ * mask[b, q, k] = 1 if q < q_lens[b] && k < k_lens[b] && k <= q + (k_lens[b] - q_lens[b])
+ *                      && k >= k_lens[b] - q_lens[b], else 0;   mask [batch, max_q_len, max_k_len]. */
+ISPORE_API int ispore_build_causal_mask_f32(float* mask, const int32_t* q_lens, const int32_t* k_lens,
+                                            int64_t batch_size, int64_t max_q_len, int64_t max_k_len,
+                                            ispore_stream_t stream);
+ISPORE_API int ispore_build_causal_mask_f16(void* mask, const int32_t* q_lens, const int32_t* k_lens,
+                                            int64_t batch_size, int64_t max_q_len, int64_t max_k_len,
+                                            ispore_stream_t stream);
+
+/* Padding offsets of packed (un-padded) tokens.
+ * ref: src/kernels/cal_paddingoffset.h:8-11 (launchCalPaddingoffset), .cu:18-45 (a one-thread
+ *      serial loop), :49-59 (launcher).
+ * cum_seqlens [batch+1]: tokens before each sequence (last = total); padding_offset: for token
+ * i of sequence b, padding_offset[cum_seqlens[b] + i] = b*max_q_len - cum_seqlens[b]; entries
+ * past the total are left untouched.  A block scan replaces the serial loop. */
+ISPORE_API int ispore_cal_padding_offset(int32_t* padding_offset, int32_t* cum_seqlens,
+                                         const int32_t* input_lengths, int64_t batch_size,
+                                         int64_t max_q_len, ispore_stream_t stream);
+
+/* Transpose + remove padding after attention.
+ * ref: declared in src/kernels/fused_transpose_and_remv_pad.h:7-10 (launchTransposeOutRemovePadding)
+ *      but never defined in the reference; semantics from tests/unittests/test_fused_trans_remv_pad.cu:3-4,28-38.
+ * in [batch, heads, seq_len, head_size] -> out [num_tokens, heads, head_size]:
+ * out[t, h, :] = in[b, h, s, :] with (b, s) = divmod(t + padding_offset[t], seq_len). */
+ISPORE_API int ispore_transpose_remove_padding_f32(float* out, const float* in, const int32_t* padding_offset,
+                                                   int64_t batch_size, int64_t head_num, int64_t seq_len,
+                                                   int64_t head_size, int64_t num_tokens, ispore_stream_t stream);
+ISPORE_API int ispore_transpose_remove_padding_f16(void* out, const void* in, const int32_t* padding_offset,
+                                                   int64_t batch_size, int64_t head_num, int64_t seq_len,
+                                                   int64_t head_size, int64_t num_tokens, ispore_stream_t stream);
+
+/* Repeat-KV: broadcast cached K/V heads to the query heads (GQA / MQA).
+ * ref: src/kernels/repeat_kv.h:7-13 (launchRepeatKVCache), .cu:11-50 (kernel), :52-100 (launcher).
+ * src caches [num_layers, batch, kv_heads, max_seq_len, head_size] ->
+ * dst [batch, heads, max_k_len, head_size]:
+ * dst[b, h, s, :] = src[layer, b, h / (heads/kv_heads), s, :] for s < context_length[b];
+ * other positions of dst are left untouched.  K and V in one launch; 64-bit offsets. */
+ISPORE_API int ispore_repeat_kv_f32(float* k_dst, float* v_dst, const float* k_src, const float* v_src,
+                                    const int32_t* context_length, int64_t layer, int64_t num_layers,
+                                    int64_t batch_size, int64_t kv_head_num, int64_t head_num,
+                                    int64_t max_seq_len, int64_t max_k_len, int64_t head_size,
+                                    ispore_stream_t stream);
+ISPORE_API int ispore_repeat_kv_f16(void* k_dst, void* v_dst, const void* k_src, const void* v_src,
+                                    const int32_t* context_length, int64_t layer, int64_t num_layers,
+                                    int64_t batch_size, int64_t kv_head_num, int64_t head_num,
+                                    int64_t max_seq_len, int64_t max_k_len, int64_t head_size,
+                                    ispore_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -42,7 +42,11 @@ for _t in ("f32", "f16"):
     SIGNATURES[f"ispore_topk_{_t}"] = [_p, _i64, _i64, _i32, _p, _p, _i32, _p, _p, _i32, _p, _f, _p, _p]
     SIGNATURES[f"ispore_topk_merge_{_t}"] = [_p, _p, _i64, _i32, _i32, _p, _p, _p, _f, _p, _p]
     SIGNATURES[f"ispore_sampling_{_t}"] = [_p, _p, _p, _p, _i64, _i32, _f, _p]
+    SIGNATURES[f"ispore_build_causal_mask_{_t}"] = [_p, _p, _p, _i64, _i64, _i64, _p]
+    SIGNATURES[f"ispore_transpose_remove_padding_{_t}"] = [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]
+    SIGNATURES[f"ispore_repeat_kv_{_t}"] = [_p] * 5 + [_i64] * 8 + [_p]
 
+SIGNATURES["ispore_cal_padding_offset"] = [_p, _p, _p, _i64, _i64, _p]
 SIGNATURES["ispore_topk_static_f32"] = [_p, _i64, _i64, _i32, _p, _p, _i32, _p, _f, _p, _p]
 TOPK_STATIC_ENTRIES = 131072
 

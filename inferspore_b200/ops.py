@@ -180,3 +180,41 @@ def launchSampling(topk_id: torch.Tensor, topk_val: torch.Tensor, uniform: torch
     rows, K = topk_id.shape
     _call(f"ispore_sampling_{_suffix(topk_val)}", topk_val, _ptr(topk_id), _ptr(topk_val), _ptr(uniform),
           _ptr(output_id), rows, K, temperature)
+
+
+def launchBuildCausalMasks(mask: torch.Tensor, q_lens: torch.Tensor, k_lens: torch.Tensor) -> None:
+    """mask [bs, max_q_len, max_k_len] of 0/1 from per-sequence lengths (build_casual_mask.h:7-10)."""
+    _dev(mask, q_lens, k_lens)
+    batch, max_q, max_k = mask.shape
+    _call(f"ispore_build_causal_mask_{_suffix(mask)}", mask, _ptr(mask), _ptr(q_lens), _ptr(k_lens), batch, max_q, max_k)
+
+
+def launchCalPaddingoffset(padding_offset: torch.Tensor, cum_seqlens: torch.Tensor, input_lengths: torch.Tensor) -> None:
+    """padding_offset [bs, max_q_len], cum_seqlens [bs+1] from input_lengths [bs] (cal_paddingoffset.h:8-11)."""
+    _dev(padding_offset, cum_seqlens, input_lengths)
+    batch, max_q = padding_offset.shape
+    if input_lengths.shape[0] != batch or cum_seqlens.shape[0] != batch + 1:
+        raise ValueError("input lengths must be [bs] and cum_seqlens [bs + 1]")
+    _call("ispore_cal_padding_offset", padding_offset, _ptr(padding_offset), _ptr(cum_seqlens), _ptr(input_lengths),
+          batch, max_q)
+
+
+def launchTransposeOutRemovePadding(qkv_buf_w_pad: torch.Tensor, padding_offset: torch.Tensor,
+                                    qkv_buf_wo_pad: torch.Tensor) -> None:
+    """[bs, heads, seq, d] -> [num_tokens, heads, d] (fused_transpose_and_remv_pad.h:7-10)."""
+    _dev(qkv_buf_w_pad, padding_offset, qkv_buf_wo_pad)
+    batch, heads, seq_len, head_size = qkv_buf_w_pad.shape
+    num_tokens = qkv_buf_wo_pad.shape[0]
+    _call(f"ispore_transpose_remove_padding_{_suffix(qkv_buf_w_pad)}", qkv_buf_w_pad, _ptr(qkv_buf_wo_pad),
+          _ptr(qkv_buf_w_pad), _ptr(padding_offset), batch, heads, seq_len, head_size, num_tokens)
+
+
+def launchRepeatKVCache(k_cache_src: torch.Tensor, v_cache_src: torch.Tensor, context_length: torch.Tensor,
+                        layer_id: int, k_cache_dst: torch.Tensor, v_cache_dst: torch.Tensor) -> None:
+    """caches [layers, bs, kv_heads, max_seq, d] -> [bs, heads, max_k_len, d] (repeat_kv.h:7-13)."""
+    _dev(k_cache_src, v_cache_src, context_length, k_cache_dst, v_cache_dst)
+    num_layers, batch, kv_heads, max_seq_len, head_size = k_cache_src.shape
+    heads, max_k_len = k_cache_dst.shape[1], k_cache_dst.shape[2]
+    _call(f"ispore_repeat_kv_{_suffix(k_cache_src)}", k_cache_src, _ptr(k_cache_dst), _ptr(v_cache_dst),
+          _ptr(k_cache_src), _ptr(v_cache_src), _ptr(context_length), layer_id, num_layers, batch, kv_heads, heads,
+          max_seq_len, max_k_len, head_size)

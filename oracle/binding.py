@@ -266,3 +266,52 @@ def ref_cpu_qkv_rope(QKV, bias, history_length, batch, seq_len, head_num, kv_hea
         _ptr(il), C.c_int(batch), C.c_int(seq_len), C.c_int(batch * seq_len), C.c_int(head_num),
         C.c_int(kv_head_num), C.c_int(head_size), C.c_int(rot_dim), _f(base))
     return q, k
+
+
+# ---- layout kernels either side of attention ---------------------------------------------------------
+
+def build_causal_mask(q_lens, k_lens, max_q_len, max_k_len, dtype=np.float32):
+    ql = np.ascontiguousarray(q_lens, np.int32)
+    kl = np.ascontiguousarray(k_lens, np.int32)
+    mask = np.empty((ql.size, max_q_len, max_k_len), dtype)
+    lib().orc_build_causal_mask(_ptr(mask), _ptr(ql), _ptr(kl), _i64(ql.size), _i64(max_q_len), _i64(max_k_len),
+                                _i64(mask.dtype.itemsize))
+    return mask
+
+
+def cal_padding_offset(input_lengths, max_q_len, fill=-1):
+    """Returns (padding_offset [bs, max_q_len] with untouched entries = fill, cum_seqlens [bs+1])."""
+    il = np.ascontiguousarray(input_lengths, np.int32)
+    po = np.full((il.size, max_q_len), fill, np.int32)
+    cum = np.empty(il.size + 1, np.int32)
+    lib().orc_cal_padding_offset(_ptr(po), _ptr(cum), _ptr(il), _i64(il.size), _i64(max_q_len))
+    return po, cum
+
+
+def transpose_remove_padding(inp, padding_offset, num_tokens, fill=0):
+    batch, heads, seq_len, head_size = inp.shape
+    po = np.ascontiguousarray(padding_offset, np.int32)
+    out = np.full((num_tokens, heads, head_size), fill, inp.dtype)
+    lib().orc_transpose_remove_padding(_ptr(out), _ptr(np.ascontiguousarray(inp)), _ptr(po), _i64(batch), _i64(heads),
+                                       _i64(seq_len), _i64(head_size), _i64(num_tokens), _i64(inp.dtype.itemsize))
+    return out
+
+
+def repeat_kv(dst, src, context_length, layer, heads):
+    """Writes into a copy of dst [bs, heads, max_k_len, d] from src [layers, bs, kv_heads, max_seq, d]."""
+    dst = np.array(dst, copy=True)
+    _, batch, kv_heads, max_seq_len, head_size = src.shape
+    cl = np.ascontiguousarray(context_length, np.int32)
+    lib().orc_repeat_kv(_ptr(dst), _ptr(np.ascontiguousarray(src)), _ptr(cl), _i64(layer), _i64(batch), _i64(kv_heads),
+                        _i64(heads), _i64(max_seq_len), _i64(dst.shape[2]), _i64(head_size), _i64(src.dtype.itemsize))
+    return dst
+
+
+def ref_cpu_causal_mask(q_lens, k_lens, max_q_len, max_k_len):
+    """The reference's CPUbuildCasualMask (tests/unittests/test_casual_mask.cu:12-32)."""
+    ql = np.ascontiguousarray(q_lens, np.int32)
+    kl = np.ascontiguousarray(k_lens, np.int32)
+    mask = np.empty((ql.size, max_q_len, max_k_len), np.float32)
+    ref_lib("libref_layout.so").ref_cpu_causal_mask_f32(_ptr(mask), _ptr(ql), _ptr(kl), C.c_int(max_q_len),
+                                                       C.c_int(max_k_len), C.c_int(ql.size))
+    return mask

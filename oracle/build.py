@@ -46,6 +46,10 @@ REF_LIBS = {
         "ref_wrap/ref_concat_softmax.cu",
         ["src/kernels/concat_past_kv.cu", "src/kernels/attn_softmax_kernel.cu"],
     ),
+    "libref_layout.so": (
+        "ref_wrap/ref_layout.cu",
+        ["src/kernels/build_casual_mask.cu", "src/kernels/cal_paddingoffset.cu", "src/kernels/repeat_kv.cu"],
+    ),
 }
 
 DROPIN_TESTS = [
@@ -55,6 +59,10 @@ DROPIN_TESTS = [
     "test_concat_kv",
     "test_mask_softmax",
     "test_bias_and_RoPE",
+    "test_casual_mask",
+    "test_cal_paddingoffset",
+    "test_fused_trans_remv_pad",
+    "test_repeat_kv",
 ]
 
 

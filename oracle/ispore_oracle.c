@@ -697,3 +697,79 @@ ORC_API void orc_sampling(const int32_t* topk_ids, const void* topk_vals, const 
         if (margin) margin[r] = total > 0.f ? best_margin / total : 0.f;
     }
 }
+
+/* ---- layout kernels either side of attention ------------------------------------------------------------- */
+
+/* Causal / padding mask.  Follows src/kernels/build_casual_mask.cu:5-42; the predicate is line 36:
+ *   q < qlen && k < klen && k <= q + (klen - qlen) && k >= klen - qlen.
+ * (The reference's CPU function, tests/unittests/test_casual_mask.cu:12-32, lacks the last
+ * clause; the two agree whenever klen == qlen, which is what its fixture uses.)
+ * elem_size 4 writes floats, 2 writes half bit patterns.                                            */
+ORC_API void orc_build_causal_mask(void* mask, const int32_t* q_lens, const int32_t* k_lens, int64_t batch,
+                                   int64_t max_q_len, int64_t max_k_len, int64_t elem_size) {
+    for (int64_t b = 0; b < batch; ++b) {
+        const int qlen = q_lens[b], klen = k_lens[b];
+        for (int64_t q = 0; q < max_q_len; ++q)
+            for (int64_t k = 0; k < max_k_len; ++k) {
+                const int one = q < qlen && k < klen && k <= q + (klen - qlen) && k >= klen - qlen;
+                const int64_t at = (b * max_q_len + q) * max_k_len + k;
+                if (elem_size == 4)
+                    ((float*)mask)[at] = one ? 1.0f : 0.0f;
+                else
+                    ((uint16_t*)mask)[at] = one ? 0x3C00u : 0u;
+            }
+    }
+}
+
+/* Padding offsets.  Follows src/kernels/cal_paddingoffset.cu:18-45 line by line (lengths are
+ * clamped to [0, max_q_len], which the reference leaves to the caller).                            */
+ORC_API void orc_cal_padding_offset(int32_t* padding_offset, int32_t* cum_seqlens, const int32_t* input_lengths,
+                                    int64_t batch, int64_t max_q_len) {
+    int64_t ind = 0, cum_offset = 0, total = 0;
+    for (int64_t b = 0; b < batch; ++b) {
+        int64_t len = input_lengths[b];
+        if (len < 0) len = 0;
+        if (len > max_q_len) len = max_q_len;
+        cum_seqlens[b] = (int32_t)total;
+        for (int64_t i = 0; i < len; ++i) padding_offset[ind++] = (int32_t)cum_offset;
+        cum_offset += max_q_len - len;
+        total += len;
+    }
+    cum_seqlens[batch] = (int32_t)total;
+}
+
+/* Transpose + remove padding: [b, h, s, d] -> [num_tokens, h, d]
+ * (tests/unittests/test_fused_trans_remv_pad.cu:3-4; the launcher is declared in
+ * src/kernels/fused_transpose_and_remv_pad.h:7-10 and never defined upstream).                      */
+ORC_API void orc_transpose_remove_padding(void* out, const void* in, const int32_t* padding_offset, int64_t batch,
+                                          int64_t heads, int64_t seq_len, int64_t head_size, int64_t num_tokens,
+                                          int64_t elem_size) {
+    const int64_t row = head_size * elem_size;
+    for (int64_t t = 0; t < num_tokens; ++t) {
+        const int64_t dst = t + padding_offset[t];
+        if (dst < 0 || dst >= batch * seq_len) continue;
+        const int64_t b = dst / seq_len, s = dst % seq_len;
+        for (int64_t h = 0; h < heads; ++h)
+            memcpy((char*)out + (t * heads + h) * row, (const char*)in + (((b * heads + h) * seq_len) + s) * row,
+                   (size_t)row);
+    }
+}
+
+/* Repeat-KV.  Follows src/kernels/repeat_kv.cu:11-50 (index arithmetic :34-47) and the layer
+ * offset of the launcher (:71), in 64 bits.  One call handles one of K / V.                          */
+ORC_API void orc_repeat_kv(void* dst, const void* src, const int32_t* context_length, int64_t layer, int64_t batch,
+                           int64_t kv_heads, int64_t heads, int64_t max_seq_len, int64_t max_k_len,
+                           int64_t head_size, int64_t elem_size) {
+    const int64_t row = head_size * elem_size;
+    const int64_t q_per_kv = heads / kv_heads;
+    const char* base = (const char*)src + layer * batch * kv_heads * max_seq_len * row;
+    for (int64_t b = 0; b < batch; ++b) {
+        int64_t len = context_length[b];
+        if (len > max_k_len) len = max_k_len;
+        if (len > max_seq_len) len = max_seq_len;
+        for (int64_t h = 0; h < heads; ++h)
+            for (int64_t s = 0; s < len; ++s)
+                memcpy((char*)dst + ((b * heads + h) * max_k_len + s) * row,
+                       base + ((b * kv_heads + h / q_per_kv) * max_seq_len + s) * row, (size_t)row);
+    }
+}

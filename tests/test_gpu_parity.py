@@ -513,3 +513,142 @@ def test_sampling_fused_and_standalone(ops, orc, rng, temperature):
     out = torch.empty(rows, dtype=torch.int32, device="cuda:0")
     ops.launchSampling(dev(got_i), dev(got_v), dev(u), out, temperature)
     assert np.array_equal(host(out), picked)
+
+
+# ---- layout kernels either side of attention: all bit-exact ----------------------------------------------
+
+def _i32(a):
+    return dev(np.ascontiguousarray(a, np.int32))
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("batch,max_q,max_k", [(1, 5, 5), (3, 7, 13), (4, 64, 128), (2, 1, 300), (5, 33, 40),
+                                                (2, 512, 1024)])
+def test_build_causal_mask(ops, orc, rng, dtype, batch, max_q, max_k):
+    ql = rng.integers(0, max_q + 1, batch)
+    kl = np.minimum(ql + rng.integers(0, max_k, batch), max_k)
+    ql[0], kl[0] = min(max_q, max_k), min(max_q, max_k)  # the reference fixture's case: no history
+    mask = torch.full((batch, max_q, max_k), 7.0, dtype=torch.float16 if dtype == np.float16 else torch.float32,
+                      device="cuda:0")
+    ops.launchBuildCausalMasks(mask, _i32(ql), _i32(kl))
+    assert np.array_equal(host(mask), orc.build_causal_mask(ql, kl, max_q, max_k, dtype))
+
+
+def test_build_causal_mask_fixture(ops):
+    # tests/unittests/test_casual_mask.cu:45-68
+    mask = torch.empty((1, 5, 5), device="cuda:0")
+    ops.launchBuildCausalMasks(mask, _i32([3]), _i32([3]))
+    want = np.zeros((1, 5, 5), np.float32)
+    want[0, :3, :3] = np.tril(np.ones((3, 3)))
+    assert np.array_equal(host(mask), want)
+
+
+def test_build_causal_mask_unaligned_view(ops, orc):
+    buf = torch.zeros(1 + 2 * 6 * 8, device="cuda:0")
+    mask = buf[1:].view(2, 6, 8)  # 4-byte aligned only: scalar path
+    ops.launchBuildCausalMasks(mask, _i32([6, 2]), _i32([8, 5]))
+    assert np.array_equal(host(mask), orc.build_causal_mask([6, 2], [8, 5], 6, 8))
+    assert float(buf[0]) == 0.0
+
+
+@pytest.mark.parametrize("lens,max_q", [([3, 3, 3], 5), ([2, 0, 4, 1], 4), ([1], 1), ([4096] * 16, 4096),
+                                        (None, 37)])
+def test_cal_padding_offset(ops, orc, rng, lens, max_q):
+    if lens is None:  # more sequences than one scan chunk holds
+        lens = rng.integers(0, max_q + 1, 2500)
+    batch = len(lens)
+    po = torch.full((batch, max_q), -5, dtype=torch.int32, device="cuda:0")
+    cum = torch.full((batch + 1,), -5, dtype=torch.int32, device="cuda:0")
+    ops.launchCalPaddingoffset(po, cum, _i32(lens))
+    want_po, want_cum = orc.cal_padding_offset(lens, max_q, fill=-5)
+    assert np.array_equal(host(cum), want_cum)
+    assert np.array_equal(host(po), want_po)  # entries past the total stay untouched
+
+
+def test_cal_padding_offset_clamps_bad_lengths(ops, orc):
+    po = torch.full((3, 4), -1, dtype=torch.int32, device="cuda:0")
+    cum = torch.empty(4, dtype=torch.int32, device="cuda:0")
+    ops.launchCalPaddingoffset(po, cum, _i32([9, -2, 3]))
+    want_po, want_cum = orc.cal_padding_offset([9, -2, 3], 4)
+    assert host(cum).tolist() == [0, 4, 4, 7] == want_cum.tolist()
+    assert np.array_equal(host(po), want_po)
+
+
+def test_cal_padding_offset_empty_batch(ops):
+    po = torch.empty((0, 4), dtype=torch.int32, device="cuda:0")
+    cum = torch.full((1,), -1, dtype=torch.int32, device="cuda:0")
+    ops.launchCalPaddingoffset(po, cum, torch.empty(0, dtype=torch.int32, device="cuda:0"))
+    assert host(cum).tolist() == [0]
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("lens,seq,heads,d", [([2, 3], 4, 2, 2), ([5, 1, 8], 8, 4, 128), ([7], 7, 3, 20),
+                                              ([0, 6, 2], 6, 32, 64), ([100, 37], 100, 8, 128)])
+def test_transpose_remove_padding(ops, orc, rng, dtype, lens, seq, heads, d):
+    po, cum = orc.cal_padding_offset(lens, seq)
+    tokens = int(cum[-1])
+    offs = po.reshape(-1)[:tokens]
+    inp = rng.standard_normal((len(lens), heads, seq, d), dtype=np.float32).astype(dtype)
+    out = torch.full((tokens, heads, d), 3.0, dtype=torch.float16 if dtype == np.float16 else torch.float32,
+                     device="cuda:0")
+    ops.launchTransposeOutRemovePadding(dev(inp), _i32(offs), out)
+    assert np.array_equal(host(out), orc.transpose_remove_padding(inp, offs, tokens))
+
+
+def test_transpose_remove_padding_fixture(ops):
+    # tests/unittests/test_fused_trans_remv_pad.cu:7-38
+    inp = np.arange(32, dtype=np.float32).reshape(2, 2, 4, 2)
+    out = torch.empty((5, 2, 2), device="cuda:0")
+    ops.launchTransposeOutRemovePadding(dev(inp), _i32([0, 0, 2, 2, 2]), out)
+    assert host(out).reshape(-1).tolist() == [0, 1, 8, 9, 2, 3, 10, 11, 16, 17, 24, 25, 18, 19, 26, 27, 20, 21, 28, 29]
+
+
+def test_transpose_remove_padding_flags_bad_offset(ops):
+    from inferspore_b200 import capi
+
+    inp = torch.ones((1, 2, 4, 8), device="cuda:0")
+    out = torch.zeros((3, 2, 8), device="cuda:0")
+    ops.launchTransposeOutRemovePadding(inp, _i32([0, 50, 0]), out)
+    torch.cuda.synchronize()
+    assert capi.device_status(clear=True) & capi.DEV_BAD_PADDING
+    got = host(out)
+    assert (got[0] == 1).all() and (got[1] == 0).all() and (got[2] == 1).all()  # the bad token is skipped
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("layers,batch,kv,heads,max_seq,max_k,d", [(2, 1, 2, 2, 4, 2, 2), (3, 2, 2, 8, 64, 40, 128),
+                                                                    (1, 3, 1, 5, 16, 16, 20), (2, 4, 8, 32, 128, 100, 64)])
+def test_repeat_kv(ops, orc, rng, dtype, layers, batch, kv, heads, max_seq, max_k, d):
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    ksrc = rng.standard_normal((layers, batch, kv, max_seq, d), dtype=np.float32).astype(dtype)
+    vsrc = rng.standard_normal((layers, batch, kv, max_seq, d), dtype=np.float32).astype(dtype)
+    ctx = rng.integers(0, max_k + 1, batch)
+    ctx[0] = max_k
+    layer = layers - 1
+    kd = torch.full((batch, heads, max_k, d), -9.0, dtype=tdt, device="cuda:0")
+    vd = torch.full((batch, heads, max_k, d), -9.0, dtype=tdt, device="cuda:0")
+    ops.launchRepeatKVCache(dev(ksrc), dev(vsrc), _i32(ctx), layer, kd, vd)
+    fill = np.full((batch, heads, max_k, d), -9.0, dtype)
+    assert np.array_equal(host(kd), orc.repeat_kv(fill, ksrc, ctx, layer, heads))
+    assert np.array_equal(host(vd), orc.repeat_kv(fill, vsrc, ctx, layer, heads))
+
+
+def test_repeat_kv_fixture(ops):
+    # tests/unittests/test_repeat_kv.cu:14-56
+    src = dev(np.arange(32, dtype=np.float32).reshape(2, 1, 2, 4, 2))
+    kd, vd = torch.zeros((1, 2, 2, 2), device="cuda:0"), torch.zeros((1, 2, 2, 2), device="cuda:0")
+    ops.launchRepeatKVCache(src, src, _i32([2]), 0, kd, vd)
+    assert host(kd).reshape(-1).tolist() == [0, 1, 2, 3, 8, 9, 10, 11] == host(vd).reshape(-1).tolist()
+
+
+def test_layout_ops_reject_bad_shapes(ops):
+    with pytest.raises(Exception):
+        ops.launchCalPaddingoffset(torch.empty((2, 4), dtype=torch.int32, device="cuda:0"),
+                                   torch.empty(2, dtype=torch.int32, device="cuda:0"), _i32([1, 2]))
+    src = torch.zeros((1, 1, 3, 4, 8), device="cuda:0")
+    with pytest.raises(Exception):  # 4 heads over 3 kv heads
+        ops.launchRepeatKVCache(src, src, _i32([1]), 0, torch.zeros((1, 4, 4, 8), device="cuda:0"),
+                                torch.zeros((1, 4, 4, 8), device="cuda:0"))
+    with pytest.raises(Exception):  # layer out of range
+        ops.launchRepeatKVCache(src, src, _i32([1]), 1, torch.zeros((1, 3, 4, 8), device="cuda:0"),
+                                torch.zeros((1, 3, 4, 8), device="cuda:0"))

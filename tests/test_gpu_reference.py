@@ -110,6 +110,33 @@ def test_dropin_bias_and_rope(cuda):
     assert float(first.split("=")[1]) == 34.0
 
 
+def test_dropin_casual_mask(cuda):
+    out = _run("test_casual_mask")
+    assert "test passed!" in out and "res is wrong" not in out
+
+
+def test_dropin_cal_paddingoffset(cuda):
+    out = _run("test_cal_paddingoffset")
+    po = [int(l.split("=")[1]) for l in out.splitlines() if l.startswith("padding_offset")]
+    cum = [int(l.split("=")[1]) for l in out.splitlines() if l.startswith("cum_seqlens")]
+    # expected values as written in the reference test (test_cal_paddingoffset.cu:57-59); the six
+    # entries past the 9 tokens are never written by either implementation
+    assert len(po) == 15 and po[:9] == [0, 0, 0, 2, 2, 2, 4, 4, 4]
+    assert cum == [0, 3, 6, 9]
+
+
+def test_dropin_fused_trans_remv_pad(cuda):
+    out = _run("test_fused_trans_remv_pad")
+    vals = [float(l.split("=")[-1]) for l in out.splitlines() if l.startswith("after trans and remv pad")]
+    assert vals == [0, 1, 8, 9, 2, 3, 10, 11, 16, 17, 24, 25, 18, 19, 26, 27, 20, 21, 28, 29]
+
+
+def test_dropin_repeat_kv(cuda):
+    out = _run("test_repeat_kv")
+    vals = [float(l.split("=")[-1]) for l in out.splitlines() if l.startswith("k trans[")]
+    assert vals == [0, 1, 2, 3, 8, 9, 10, 11]
+
+
 # ---- this library vs the reference's GPU kernels on random data -----------------------------------------
 
 @pytest.mark.parametrize("tokens,hidden", [(64, 4096), (300, 1024), (7, 128)])
@@ -232,3 +259,52 @@ def test_vs_reference_gpu_softmax(ops, orc, rng, dtype, k_len):
     else:
         # the reference computes scale*qk, the mask term and exp in half precision: 2e-3 absolute
         assert np.max(np.abs(host(ours).astype(np.float32) - host(ref).astype(np.float32))) <= 2e-3
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_vs_reference_gpu_causal_mask(ops, orc, rng, half):
+    lib = _ref(orc, "libref_layout.so")
+    batch, max_q, max_k = 5, 48, 96
+    ql = rng.integers(0, max_q + 1, batch).astype(np.int32)
+    kl = np.minimum(ql + rng.integers(0, 48, batch), max_k).astype(np.int32)
+    dq, dk = dev(ql), dev(kl)
+    dt = torch.float16 if half else torch.float32
+    ours = torch.full((batch, max_q, max_k), 3.0, dtype=dt, device="cuda:0")
+    ref = torch.full((batch, max_q, max_k), 4.0, dtype=dt, device="cuda:0")
+    ops.launchBuildCausalMasks(ours, dq, dk)
+    fn = lib.ref_gpu_causal_mask_f16 if half else lib.ref_gpu_causal_mask_f32
+    assert fn(_p(ref), _p(dq), _p(dk), batch, max_q, max_k) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(ours), host(ref))
+
+
+def test_vs_reference_gpu_padding_offset(ops, orc, rng):
+    lib = _ref(orc, "libref_layout.so")
+    batch, max_q = 37, 29
+    lens = rng.integers(0, max_q + 1, batch).astype(np.int32)
+    dl = dev(lens)
+    mk = lambda n: torch.full((n,), -3, dtype=torch.int32, device="cuda:0")
+    po, cum, rpo, rcum = mk(batch * max_q).view(batch, max_q), mk(batch + 1), mk(batch * max_q).view(batch, max_q), mk(batch + 1)
+    ops.launchCalPaddingoffset(po, cum, dl)
+    assert lib.ref_gpu_cal_padding_offset(_p(rpo), _p(rcum), _p(dl), lens.ctypes.data_as(C.c_void_p), batch, max_q) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(po), host(rpo)) and np.array_equal(host(cum), host(rcum))
+
+
+@pytest.mark.parametrize("half", [False, True])
+def test_vs_reference_gpu_repeat_kv(ops, orc, rng, half):
+    lib = _ref(orc, "libref_layout.so")
+    layers, batch, kv, heads, max_seq, max_k, d = 3, 2, 2, 8, 48, 40, 64
+    npdt, dt = (np.float16, torch.float16) if half else (np.float32, torch.float32)
+    ks = dev(rng.standard_normal((layers, batch, kv, max_seq, d), dtype=np.float32).astype(npdt))
+    vs = dev(rng.standard_normal((layers, batch, kv, max_seq, d), dtype=np.float32).astype(npdt))
+    ctx = np.array([40, 17], np.int32)
+    dctx = dev(ctx)
+    mk = lambda: torch.full((batch, heads, max_k, d), 2.0, dtype=dt, device="cuda:0")
+    kd, vd, rkd, rvd = mk(), mk(), mk(), mk()
+    ops.launchRepeatKVCache(ks, vs, dctx, 1, kd, vd)
+    fn = lib.ref_gpu_repeat_kv_f16 if half else lib.ref_gpu_repeat_kv_f32
+    assert fn(_p(ks), _p(vs), _p(dctx), ctx.ctypes.data_as(C.c_void_p), 1, _p(rkd), _p(rvd), layers, batch, kv, heads,
+              max_seq, max_k, d) == 0
+    torch.cuda.synchronize()
+    assert np.array_equal(host(kd), host(rkd)) and np.array_equal(host(vd), host(rvd))

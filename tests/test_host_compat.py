@@ -13,10 +13,14 @@ PROGRAM = r"""
 #include <stdexcept>
 #include "src/kernels/act_kernel.h"
 #include "src/kernels/attn_softmax_kernel.h"
+#include "src/kernels/build_casual_mask.h"
+#include "src/kernels/cal_paddingoffset.h"
 #include "src/kernels/concat_past_kv.h"
 #include "src/kernels/fused_addresidual_norm.h"
+#include "src/kernels/fused_transpose_and_remv_pad.h"
 #include "src/kernels/input_embedding.h"
 #include "src/kernels/qkv_bias_and_RoPE.h"
+#include "src/kernels/repeat_kv.h"
 #include "src/kernels/topK.h"
 #include "src/weights/llama/attention_weights.h"
 #include "src/weights/llama/ffn_weights.h"
@@ -71,6 +75,10 @@ int main() {
     TensorWrapper<int> fid(GPU, INT32, {2, 300}, idummy);
     TensorWrapper<float> fval(GPU, FP32, {2, 300}, dummy);
     EXPECT(throws([&] { launchTopKforBeamSearch(&probs, &fid, &fval, &fid, &fval); }));  // K = 300 > limit
+    TensorWrapper<int> po(GPU, INT32, {3, 5}, idummy), cum3(GPU, INT32, {3}, idummy), len3(GPU, INT32, {3}, idummy);
+    EXPECT(throws([&] { launchCalPaddingoffset(&po, &cum3, &len3); }));          // cum_seqlens must be [bs + 1] (cal_paddingoffset.cu:36)
+    TensorWrapper<float> cache4(GPU, FP32, {1, 2, 4, 4}, dummy);
+    EXPECT(throws([&] { launchRepeatKVCache(&cache4, &cache4, &ids, &layer, &cache4, &cache4); }));  // source caches carry a layer axis
     std::printf("compat ok\n");
     return 0;
 }

@@ -181,3 +181,85 @@ def test_sampling_definition(orc):
     vals2 = np.array([[0.0, 0.0, -np.inf, -np.inf]], np.float32)
     got, _ = orc.sampling(ids2, vals2, np.array([0.99], np.float32), 1.0)
     assert got[0] == 20
+
+
+# ---- layout kernels either side of attention -----------------------------------------------------------
+
+def test_causal_mask_fixture(orc):
+    # tests/unittests/test_casual_mask.cu:45-68: q_len = k_len = 3 inside a 5 x 5 mask; the expected
+    # values are those of its CPU function (:12-32): ones in the lower triangle of the 3 x 3 corner.
+    mask = orc.build_causal_mask([3], [3], 5, 5)
+    want = np.zeros((1, 5, 5), np.float32)
+    want[0, :3, :3] = np.tril(np.ones((3, 3), np.float32))
+    assert np.array_equal(mask, want)
+    assert np.array_equal(orc.build_causal_mask([3], [3], 5, 5, np.float16), want.astype(np.float16))
+
+
+def test_causal_mask_with_history(orc):
+    # q tokens sit at the END of the k axis: row q sees keys (klen - qlen) .. (klen - qlen) + q, and
+    # the kernel's last clause (src/kernels/build_casual_mask.cu:36) hides the history keys before.
+    mask = orc.build_causal_mask([2, 1], [5, 4], 3, 6)[..., :]
+    want = np.zeros((2, 3, 6), np.float32)
+    want[0, 0, 3] = 1
+    want[0, 1, 3:5] = 1
+    want[1, 0, 3] = 1
+    assert np.array_equal(mask, want)
+
+
+def test_cal_padding_offset_fixture(orc):
+    # tests/unittests/test_cal_paddingoffset.cu:31-33 and the expected values written at :57-59.
+    po, cum = orc.cal_padding_offset([3, 3, 3], 5, fill=-7)
+    assert po.reshape(-1)[:9].tolist() == [0, 0, 0, 2, 2, 2, 4, 4, 4]
+    assert (po.reshape(-1)[9:] == -7).all()  # the reference leaves the tail unwritten
+    assert cum.tolist() == [0, 3, 6, 9]
+
+
+def test_cal_padding_offset_ragged_and_empty(orc):
+    po, cum = orc.cal_padding_offset([2, 0, 4, 1], 4, fill=-1)
+    assert po.reshape(-1)[:7].tolist() == [0, 0, 6, 6, 6, 6, 6]
+    assert cum.tolist() == [0, 2, 2, 6, 7]
+    po, cum = orc.cal_padding_offset([], 4)
+    assert po.size == 0 and cum.tolist() == [0]
+
+
+def test_transpose_remove_padding_fixture(orc):
+    # tests/unittests/test_fused_trans_remv_pad.cu:7-38: [2, 2, 4, 2] input of 0..31, sequence
+    # lengths 2 and 3, padding offsets 0,0,2,2,2.  Token t = (b, s) takes rows [b, h, s, :].
+    inp = np.arange(32, dtype=np.float32).reshape(2, 2, 4, 2)
+    out = orc.transpose_remove_padding(inp, [0, 0, 2, 2, 2], 5)
+    want = np.stack([inp[0, :, 0], inp[0, :, 1], inp[1, :, 0], inp[1, :, 1], inp[1, :, 2]])
+    assert np.array_equal(out, want)
+    assert out.reshape(-1)[:8].tolist() == [0, 1, 8, 9, 2, 3, 10, 11]
+
+
+def test_transpose_remove_padding_inverts_rope_scatter(orc, rng):
+    # the QKV kernel scatters token t to [b, h, s, :] with the same padding offsets; V has no
+    # rotation, so gathering it back must return the input V slice exactly.
+    lens, seq, heads, kv, d = [3, 5, 1], 5, 4, 2, 8
+    po, cum = orc.cal_padding_offset(lens, seq)
+    tokens = int(cum[-1])
+    offs = po.reshape(-1)[:tokens]
+    qkv = rng.standard_normal((tokens, heads + 2 * kv, d), dtype=np.float32)
+    _, _, v, _, _ = orc.qkv_bias_rope_transpose(qkv, None, offs, [0, 0, 0], 3, seq, heads, kv, d, 10000.0)
+    back = orc.transpose_remove_padding(v, offs, tokens)
+    assert np.array_equal(back, qkv[:, heads + kv:, :])
+
+
+def test_repeat_kv_fixture(orc):
+    # tests/unittests/test_repeat_kv.cu:14-56: caches [2, 1, 2, 4, 2] of 0..31, context length 2,
+    # layer 0, 2 heads over 2 kv heads, max_k_len 2: head h copies positions 0..1 of kv head h.
+    src = np.arange(32, dtype=np.float32).reshape(2, 1, 2, 4, 2)
+    out = orc.repeat_kv(np.zeros((1, 2, 2, 2), np.float32), src, [2], 0, 2)
+    assert out.reshape(-1).tolist() == [0, 1, 2, 3, 8, 9, 10, 11]
+    out1 = orc.repeat_kv(np.zeros((1, 2, 2, 2), np.float32), src, [2], 1, 2)
+    assert out1.reshape(-1).tolist() == [16, 17, 18, 19, 24, 25, 26, 27]
+
+
+def test_repeat_kv_groups_and_lengths(orc, rng):
+    src = rng.standard_normal((3, 2, 2, 6, 4), dtype=np.float32)
+    dst = np.full((2, 8, 5, 4), -9.0, np.float32)
+    out = orc.repeat_kv(dst, src, [5, 2], 2, 8)
+    for b, n in enumerate([5, 2]):
+        for h in range(8):
+            assert np.array_equal(out[b, h, :n], src[2, b, h // 4, :n])
+            assert (out[b, h, n:] == -9.0).all()
