@@ -224,6 +224,20 @@ ISPORE_API int ispore_scale_mask_softmax_f16(void* attn_score, const void* qk, c
                                              int64_t batch_size, int64_t head_num, int64_t q_len,
                                              int64_t k_len, float scale, ispore_stream_t stream);
 
+/* The same softmax with the mask derived inside the kernel from the two length arrays the
+ * mask would have been built from; the [batch, q_len, k_len] mask tensor is never formed.
+ * ref: the predicate of src/kernels/build_casual_mask.cu:36 applied inside the kernel of
+ *      src/kernels/attn_softmax_kernel.cu:50-125; replaces the pair of calls
+ *      launchBuildCausalMasks + launchScaleMaskAndSoftmax of the reference's context attention.
+ * q_lens, k_lens [batch] int32.  The result is bit-identical to ispore_build_causal_mask_* followed
+ * by ispore_scale_mask_softmax_* on the same inputs. */
+ISPORE_API int ispore_scale_causal_softmax_f32(float* attn_score, const float* qk, const int32_t* q_lens,
+                                               const int32_t* k_lens, int64_t batch_size, int64_t head_num,
+                                               int64_t q_len, int64_t k_len, float scale, ispore_stream_t stream);
+ISPORE_API int ispore_scale_causal_softmax_f16(void* attn_score, const void* qk, const int32_t* q_lens,
+                                               const int32_t* k_lens, int64_t batch_size, int64_t head_num,
+                                               int64_t q_len, int64_t k_len, float scale, ispore_stream_t stream);
+
 /* ---- top-K (+ sampling) ----------------------------------------------------- *
  * ref: src/kernels/topK.h:41-46 (launchTopKforBeamSearch), src/kernels/topK.cu:17-74
  *      (two rounds), :76-110 (launcher; K fixed at 5, 8 blocks per row).

@@ -39,6 +39,7 @@ for _t in ("f32", "f16"):
     SIGNATURES[f"ispore_silu_mul_{_t}"] = [_p, _p, _i64, _i64, _p]
     SIGNATURES[f"ispore_concat_kv_{_t}"] = [_p] * 6 + [_i64] * 7 + [_p]
     SIGNATURES[f"ispore_scale_mask_softmax_{_t}"] = [_p, _p, _p, _i64, _i64, _i64, _i64, _f, _p]
+    SIGNATURES[f"ispore_scale_causal_softmax_{_t}"] = [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _p]
     SIGNATURES[f"ispore_topk_{_t}"] = [_p, _i64, _i64, _i32, _p, _p, _i32, _p, _p, _i32, _p, _f, _p, _p]
     SIGNATURES[f"ispore_topk_merge_{_t}"] = [_p, _p, _i64, _i32, _i32, _p, _p, _p, _f, _p, _p]
     SIGNATURES[f"ispore_sampling_{_t}"] = [_p, _p, _p, _p, _i64, _i32, _f, _p]

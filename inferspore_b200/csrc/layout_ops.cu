@@ -6,6 +6,8 @@
 //   repeat-KV (GQA head broadcast) (reference: src/kernels/repeat_kv.cu:11-50)
 // All four are index/copy work: bit-exact, 64-bit offsets, 128-bit vectors where the rows
 // allow it and a scalar path otherwise.
+#include <type_traits>
+
 #include "common.cuh"
 
 namespace ispore {
@@ -44,48 +46,60 @@ build_causal_mask_kernel(T* __restrict__ mask, const int32_t* __restrict__ q_len
 // ---- padding offsets ----------------------------------------------------------------------------
 // cum_seqlens[b] = sum of lengths before b (cum_seqlens[batch] = total);
 // padding_offset[cum_seqlens[b] + i] = b*max_q_len - cum_seqlens[b] for i < len[b]
-// (src/kernels/cal_paddingoffset.cu:25-45).  One CTA: a block scan over the lengths in chunks
-// of 1024; the warps then fill the tokens of the chunk's sequences, one sequence per warp at a time.
-__global__ void __launch_bounds__(1024)
+// (src/kernels/cal_paddingoffset.cu:25-45).  CTA (x, y) owns sequences x*256 .. x*256+255: it sums
+// the lengths in front of its chunk (no CTA waits for another), scans its own 256 lengths, and
+// its warps fill the tokens, sequence by sequence; the y CTAs of a chunk split every sequence's
+// tokens between them.
+constexpr int kSeqPerCta = 256;
+
+__device__ __forceinline__ int clamp_len(int len, int max_q_len) { return len < 0 ? 0 : (len > max_q_len ? max_q_len : len); }
+
+__global__ void __launch_bounds__(kSeqPerCta)
 padding_offset_kernel(int32_t* __restrict__ padding_offset, int32_t* __restrict__ cum_seqlens,
                       const int32_t* __restrict__ input_lengths, int batch, int max_q_len) {
-    __shared__ int warp_tot[32];
-    __shared__ int carry;
-    __shared__ int seq_start[1024], seq_len[1024];
+    constexpr int kWarps = kSeqPerCta / 32;
+    __shared__ int warp_tot[2][kWarps];
+    __shared__ int seq_start[kSeqPerCta], seq_len[kSeqPerCta];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    if (tid == 0) carry = 0;
-    __syncthreads();
-    for (int base = 0; base < batch; base += 1024) {
-        const int b = base + tid;
-        int len = b < batch ? input_lengths[b] : 0;
-        if (len < 0) len = 0;
-        if (len > max_q_len) len = max_q_len;
-        int incl = len;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) {
-            const int up = __shfl_up_sync(0xffffffffu, incl, o);
-            if (lane >= o) incl += up;
-        }
-        if (lane == 31) warp_tot[warp] = incl;
-        __syncthreads();
-        int before = carry;
-        for (int w = 0; w < warp; ++w) before += warp_tot[w];
-        const int start = before + incl - len;  // tokens before sequence b
-        if (b < batch) cum_seqlens[b] = start;
-        seq_start[tid] = start;
-        seq_len[tid] = len;
-        __syncthreads();
-        // warp w fills sequences w, w + 32, ... of this chunk, one token per lane
-        const int in_chunk = min(1024, batch - base);
-        for (int j = warp; j < in_chunk; j += 32) {
-            const int st = seq_start[j], n = seq_len[j], off = (base + j) * max_q_len - st;
-            for (int i = lane; i < n; i += 32) padding_offset[st + i] = off;
-        }
-        __syncthreads();
-        if (tid == 1023) carry = before + incl;
-        __syncthreads();
+    const int base = blockIdx.x * kSeqPerCta;
+    const bool writes_cum = blockIdx.y == 0;
+    if (batch == 0) {
+        if (tid == 0 && writes_cum) cum_seqlens[0] = 0;
+        return;
     }
-    if (tid == 0) cum_seqlens[batch] = carry;
+    // tokens in front of this chunk
+    int part = 0;
+    for (int b = tid; b < base; b += kSeqPerCta) part += clamp_len(__ldg(input_lengths + b), max_q_len);
+    part = warp_sum(part);
+    // inclusive scan of this chunk's lengths
+    const int b = base + tid;
+    const int len = b < batch ? clamp_len(__ldg(input_lengths + b), max_q_len) : 0;
+    int incl = len;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
+    }
+    if (lane == 0) warp_tot[0][warp] = part;
+    if (lane == 31) warp_tot[1][warp] = incl;
+    __syncthreads();
+    int before = 0;
+#pragma unroll
+    for (int w = 0; w < kWarps; ++w) before += warp_tot[0][w] + (w < warp ? warp_tot[1][w] : 0);
+    const int start = before + incl - len;  // tokens before sequence b
+    if (writes_cum && b < batch) {
+        cum_seqlens[b] = start;
+        if (b == batch - 1) cum_seqlens[batch] = start + len;
+    }
+    seq_start[tid] = start;
+    seq_len[tid] = len;
+    __syncthreads();
+    const int in_chunk = min(kSeqPerCta, batch - base);
+    const int first = blockIdx.y * 32 + lane, step = gridDim.y * 32;
+    for (int j = warp; j < in_chunk; j += kWarps) {
+        const int st = seq_start[j], n = seq_len[j], off = (base + j) * max_q_len - st;
+        for (int i = first; i < n; i += step) padding_offset[st + i] = off;
+    }
 }
 
 // ---- transpose + remove padding ---------------------------------------------------------------------
@@ -123,38 +137,42 @@ transpose_remove_padding_kernel(T* __restrict__ out, const T* __restrict__ in,
     }
 }
 
+__device__ __forceinline__ uint4 ld_unit(const uint4* p) { return ld_stream(p); }
+template <typename U>
+__device__ __forceinline__ U ld_unit(const U* p) { return *p; }
+__device__ __forceinline__ void st_unit(uint4* p, const uint4& x) { st_stream(p, x); }
+template <typename U>
+__device__ __forceinline__ void st_unit(U* p, const U& x) { *p = x; }
+
 // ---- repeat-KV -----------------------------------------------------------------------------------------
 // dst[b, h, s, :] = cache[layer, b, h / (heads/kv_heads), s, :] for s < context_length[b]
-// (src/kernels/repeat_kv.cu:34-49).  For a fixed (b, h) both sides are contiguous spans.
+// (src/kernels/repeat_kv.cu:34-49).  For a fixed (b, kv head) the source and each of its
+// heads/kv_heads destinations are contiguous spans: a CTA reads a piece of the source once and
+// stores it q_per_kv times.
 template <typename T, bool VEC>
 __global__ void __launch_bounds__(128)
 repeat_kv_kernel(T* __restrict__ k_dst, T* __restrict__ v_dst, const T* __restrict__ k_src,
                  const T* __restrict__ v_src, const int32_t* __restrict__ context_length,
-                 int64_t layer_offset, int heads, int q_per_kv, int64_t max_seq_len, int64_t max_k_len,
+                 int64_t layer_offset, int kv_heads, int q_per_kv, int64_t max_seq_len, int64_t max_k_len,
                  int head_size) {
-    constexpr int E = VecTraits<T>::kElems;
-    const int bh = blockIdx.x;  // b * heads + h
-    const int b = bh / heads, h = bh - b * heads;
+    using Unit = typename std::conditional<VEC, uint4, T>::type;
+    constexpr int E = VEC ? VecTraits<T>::kElems : 1;
+    const int bkv = blockIdx.x;  // b * kv_heads + kv head
+    const int b = bkv / kv_heads, kvh = bkv - b * kv_heads;
     const bool is_v = blockIdx.z != 0;
     int64_t len = __ldg(context_length + b);
     if (len > max_k_len) len = max_k_len;
     if (len > max_seq_len) len = max_seq_len;
-    const int kv_heads = heads / q_per_kv;
-    const int64_t src_row = (static_cast<int64_t>(b) * kv_heads + h / q_per_kv) * max_seq_len;
-    const int64_t dst_row = static_cast<int64_t>(bh) * max_k_len;
-    const T* src = (is_v ? v_src : k_src) + layer_offset + src_row * head_size;
-    T* dst = (is_v ? v_dst : k_dst) + dst_row * head_size;
-    const int64_t span = len * head_size;
-    if (VEC) {
-        const uint4* s4 = reinterpret_cast<const uint4*>(src);
-        uint4* d4 = reinterpret_cast<uint4*>(dst);
-        for (int64_t i = blockIdx.y * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < span / E;
-             i += static_cast<int64_t>(gridDim.y) * blockDim.x)
-            st_stream(d4 + i, ld_stream(s4 + i));
-    } else {
-        for (int64_t i = blockIdx.y * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < span;
-             i += static_cast<int64_t>(gridDim.y) * blockDim.x)
-            dst[i] = src[i];
+    const Unit* src = reinterpret_cast<const Unit*>((is_v ? v_src : k_src) + layer_offset +
+                                                    static_cast<int64_t>(bkv) * max_seq_len * head_size);
+    const int64_t dst_head = max_k_len * head_size / E;  // units per destination head
+    Unit* dst = reinterpret_cast<Unit*>(is_v ? v_dst : k_dst) +
+                (static_cast<int64_t>(b) * kv_heads * q_per_kv + static_cast<int64_t>(kvh) * q_per_kv) * dst_head;
+    const int64_t span = len * head_size / E;
+    for (int64_t i = blockIdx.y * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < span;
+         i += static_cast<int64_t>(gridDim.y) * blockDim.x) {
+        const Unit x = VEC ? ld_unit(src + i) : src[i];
+        for (int r = 0; r < q_per_kv; ++r) st_unit(dst + r * dst_head + i, x);
     }
 }
 
@@ -222,17 +240,17 @@ int repeat_dispatch(T* k_dst, T* v_dst, const T* k_src, const T* v_src, const in
     constexpr int E = VecTraits<T>::kElems;
     const int64_t layer_offset = layer * batch * kv_heads * max_seq_len * head_size;
     const bool vec = head_size % E == 0 && aligned16(k_dst) && aligned16(v_dst) && aligned16(k_src) && aligned16(v_src);
-    int64_t gx = ceil_div(max_k_len * head_size / (vec ? E : 1), 128 * 4);
-    if (gx > 64) gx = 64;
+    int64_t gx = ceil_div(max_k_len * head_size / (vec ? E : 1), 128 * 2);
+    if (gx > 1024) gx = 1024;
     if (gx < 1) gx = 1;
-    dim3 grid(static_cast<unsigned>(batch * heads), static_cast<unsigned>(gx), 2);
+    dim3 grid(static_cast<unsigned>(batch * kv_heads), static_cast<unsigned>(gx), 2);
     if (vec)
         repeat_kv_kernel<T, true><<<grid, 128, 0, st>>>(k_dst, v_dst, k_src, v_src, context_length, layer_offset,
-                                                        (int)heads, (int)(heads / kv_heads), max_seq_len, max_k_len,
+                                                        (int)kv_heads, (int)(heads / kv_heads), max_seq_len, max_k_len,
                                                         (int)head_size);
     else
         repeat_kv_kernel<T, false><<<grid, 128, 0, st>>>(k_dst, v_dst, k_src, v_src, context_length, layer_offset,
-                                                         (int)heads, (int)(heads / kv_heads), max_seq_len, max_k_len,
+                                                         (int)kv_heads, (int)(heads / kv_heads), max_seq_len, max_k_len,
                                                          (int)head_size);
     return check_launch("repeat_kv_kernel");
 }
@@ -260,7 +278,12 @@ int ispore_cal_padding_offset(int32_t* padding_offset, int32_t* cum_seqlens, con
                             (long long)max_q_len);
     if (!cum_seqlens || (batch_size > 0 && (!padding_offset || !input_lengths)))
         return ispore::fail(ISPORE_ENULL, "cal_padding_offset: NULL buffer");
-    ispore::padding_offset_kernel<<<1, 1024, 0, static_cast<cudaStream_t>(stream)>>>(
+    const unsigned chunks = batch_size > 0 ? static_cast<unsigned>(ispore::ceil_div(batch_size, ispore::kSeqPerCta)) : 1u;
+    // split long sequences over up to 16 CTAs per chunk; short ones need no split
+    unsigned split = static_cast<unsigned>(ispore::ceil_div(max_q_len, 256));
+    if (split > 16) split = 16;
+    if (chunks >= 32) split = 1;
+    ispore::padding_offset_kernel<<<dim3(chunks, split), ispore::kSeqPerCta, 0, static_cast<cudaStream_t>(stream)>>>(
         padding_offset, cum_seqlens, input_lengths, static_cast<int>(batch_size), static_cast<int>(max_q_len));
     return ispore::check_launch("padding_offset_kernel");
 }

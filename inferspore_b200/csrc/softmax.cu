@@ -44,9 +44,13 @@ struct ExpPolicy<__half> {
 // (b, q) pair per trip.
 // FULL: every row is exactly VPT*GROUP vectors long and heads is a multiple of HG, so the
 // per-vector and per-head guards (and the branches they cost) disappear.
-template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS, bool FULL>
+// CAUSAL: there is no mask tensor; the 0/1 mask row is derived from q_lens[b] and k_lens[b] with
+// the predicate of the reference's mask builder (src/kernels/build_casual_mask.cu:36), so the
+// result is bit-identical to building the mask first and the [bs, q, k] tensor is never read.
+template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS, bool FULL, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
+                          const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
                           uint32_t units /* batch*q_len*head_groups */, uint32_t head_groups,
                           uint32_t heads, uint32_t q_len, int row_vecs, float scale) {
     constexpr int E = VecTraits<T>::kElems;
@@ -83,10 +87,19 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 
         // All loads of the trip first: the mask slice and HG x VPT vectors of qk.
         uint4 m_raw[VPT], q_raw[HG][VPT];
+        int lo = 0, hi = -1;  // CAUSAL: the ones of the mask row span k in [lo, hi]
+        if (CAUSAL) {
+            if (live) {
+                const int qlen = __ldg(q_lens + b), klen = __ldg(k_lens + b);
+                lo = klen - qlen;
+                hi = static_cast<int>(qi) < qlen ? min(klen - 1, static_cast<int>(qi) + lo) : -1;
+            }
+        } else {
 #pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = gt + i * GROUP;
-            if (live && (FULL || v < row_vecs)) m_raw[i] = ld_keep(mrow + v);
+            for (int i = 0; i < VPT; ++i) {
+                const int v = gt + i * GROUP;
+                if (live && (FULL || v < row_vecs)) m_raw[i] = ld_keep(mrow + v);
+            }
         }
 #pragma unroll
         for (int hh = 0; hh < HG; ++hh) {
@@ -101,7 +114,20 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
             const int v = gt + i * GROUP;
-            if (live && (FULL || v < row_vecs)) {
+            if (CAUSAL) {
+                // a vector lies wholly inside or outside [lo, hi] except at the two ends of the span:
+                // one uniform fill, and the per-element predicate only for those boundary vectors
+                const int k0 = v * E, k1 = k0 + (E - 1);
+                const bool all_in = k0 >= lo && k1 <= hi;
+                const bool all_out = k0 > hi || k1 < lo;
+                const float fill = all_in ? 0.0f : neg;
+#pragma unroll
+                for (int e = 0; e < E; ++e) term[i].v[e] = fill;
+                if (!all_in && !all_out) {
+#pragma unroll
+                    for (int e = 0; e < E; ++e) term[i].v[e] = (k0 + e >= lo && k0 + e <= hi) ? 0.0f : neg;
+                }
+            } else if (live && (FULL || v < row_vecs)) {
                 unpack(m_raw[i], term[i]);
 #pragma unroll
                 for (int e = 0; e < E; ++e) term[i].v[e] = (1.0f - term[i].v[e]) * neg;
@@ -170,10 +196,10 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 
 // Any k_len / alignment: one CTA per row, three scalar passes (the row is
 // re-read from L2).  Also the path for rows too long for the register kernels.
-template <typename T, int THREADS>
+template <typename T, int THREADS, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS)
 softmax_generic_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
-                       int64_t total_rows, int64_t rows_per_batch, int q_len, int64_t k_len,
+                       const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens, int64_t total_rows, int64_t rows_per_batch, int q_len, int64_t k_len,
                        float scale) {
     constexpr int kWarps = THREADS / 32;
     __shared__ float red[2][kWarps];
@@ -182,11 +208,21 @@ softmax_generic_kernel(T* __restrict__ score, const T* __restrict__ qk, const T*
         const int64_t bidx = row / rows_per_batch;
         const int64_t qi = (row - bidx * rows_per_batch) % q_len;
         const T* qrow = qk + row * k_len;
-        const T* mrow = mask + (bidx * q_len + qi) * k_len;
+        const T* mrow = CAUSAL ? nullptr : mask + (bidx * q_len + qi) * k_len;
         T* orow = score + row * k_len;
+        int64_t lo = 0, hi = -1;
+        if (CAUSAL) {
+            const int qlen = __ldg(q_lens + bidx), klen = __ldg(k_lens + bidx);
+            lo = klen - qlen;
+            hi = qi < qlen ? min(static_cast<int64_t>(klen) - 1, qi + lo) : -1;
+        }
+        // additive term (1 - mask) * (-10000) of element i
+        auto term = [&](int64_t i) -> float {
+            if (CAUSAL) return (i >= lo && i <= hi) ? 0.0f : -10000.0f;
+            return (1.0f - to_float<T>(mrow[i])) * -10000.0f;
+        };
         float mx = FLT_MIN;
-        for (int64_t i = tid; i < k_len; i += THREADS)
-            mx = fmaxf(mx, fmaf(scale, to_float<T>(qrow[i]), (1.0f - to_float<T>(mrow[i])) * -10000.0f));
+        for (int64_t i = tid; i < k_len; i += THREADS) mx = fmaxf(mx, fmaf(scale, to_float<T>(qrow[i]), term(i)));
         mx = warp_max(mx);
         if ((tid & 31) == 0) red[0][tid >> 5] = mx;
         __syncthreads();
@@ -194,7 +230,7 @@ softmax_generic_kernel(T* __restrict__ score, const T* __restrict__ qk, const T*
         for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, red[0][w]);
         float sum = 0.f;
         for (int64_t i = tid; i < k_len; i += THREADS)
-            sum += expf(fmaf(scale, to_float<T>(qrow[i]), (1.0f - to_float<T>(mrow[i])) * -10000.0f) - mx);
+            sum += expf(fmaf(scale, to_float<T>(qrow[i]), term(i)) - mx);
         sum = warp_sum(sum);
         if ((tid & 31) == 0) red[1][tid >> 5] = sum;
         __syncthreads();
@@ -203,90 +239,73 @@ softmax_generic_kernel(T* __restrict__ score, const T* __restrict__ qk, const T*
         for (int w = 0; w < kWarps; ++w) sum += red[1][w];
         const float inv = 1.0f / (sum + 1e-6f);
         for (int64_t i = tid; i < k_len; i += THREADS) {
-            const float e =
-                expf(fmaf(scale, to_float<T>(qrow[i]), (1.0f - to_float<T>(mrow[i])) * -10000.0f) - mx);
+            const float e = expf(fmaf(scale, to_float<T>(qrow[i]), term(i)) - mx);
             orow[i] = from_float<T>(e * inv);
         }
         __syncthreads();
     }
 }
 
-template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS = 1>
-int launch_groups(T* score, const T* qk, const T* mask, int64_t batch, int64_t heads, int64_t q_len,
+// Where the 0/1 mask comes from: a [batch, q_len, k_len] tensor (the reference's interface) or
+// the two length arrays it would have been built from.
+template <typename T>
+struct MaskSource {
+    const T* mask;
+    const int32_t* q_lens;
+    const int32_t* k_lens;
+};
+
+template <typename T, bool CAUSAL, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS = 1>
+int launch_groups(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch, int64_t heads, int64_t q_len,
                   int row_vecs, float scale, cudaStream_t st) {
     constexpr int kGroupsPerCta = THREADS / GROUP;
     const int64_t head_groups = ceil_div(heads, HG);
     const int64_t units = batch * q_len * head_groups;
     const int64_t ctas = ceil_div(units, kGroupsPerCta);
     const bool full = row_vecs == VPT * GROUP && heads % HG == 0;
-    auto kernel = full ? softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, true>
-                       : softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, false>;
+    auto kernel = full ? softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, true, CAUSAL>
+                       : softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, false, CAUSAL>;
     // One trip per CTA for any realistic size: the hardware scheduler hands out CTAs in
     // address order, which keeps the DRAM access front compact.
     const int grid = static_cast<int>(ctas < (1 << 30) ? ctas : (1 << 30));
-    kernel<<<grid, THREADS, 0, st>>>(score, qk, mask, static_cast<uint32_t>(units),
+    kernel<<<grid, THREADS, 0, st>>>(score, qk, ms.mask, ms.q_lens, ms.k_lens, static_cast<uint32_t>(units),
                                      static_cast<uint32_t>(head_groups), static_cast<uint32_t>(heads),
                                      static_cast<uint32_t>(q_len), row_vecs, scale);
     return check_launch("softmax_head_group_kernel");
 }
 
-template <typename T>
-int softmax_dispatch(T* score, const T* qk, const T* mask, int64_t batch, int64_t heads, int64_t q_len,
+template <typename T, bool CAUSAL>
+int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch, int64_t heads, int64_t q_len,
                      int64_t k_len, float scale, cudaStream_t st) {
-    if (batch < 0 || heads <= 0 || q_len <= 0 || k_len <= 0 || q_len > INT32_MAX)
-        return fail(ISPORE_ESHAPE, "scale_mask_softmax: bad shape [%lld,%lld,%lld,%lld]",
-                    (long long)batch, (long long)heads, (long long)q_len, (long long)k_len);
+    const char* name = CAUSAL ? "scale_causal_softmax" : "scale_mask_softmax";
+    if (batch < 0 || heads <= 0 || q_len <= 0 || k_len <= 0 || q_len > INT32_MAX || (CAUSAL && k_len > INT32_MAX))
+        return fail(ISPORE_ESHAPE, "%s: bad shape [%lld,%lld,%lld,%lld]", name, (long long)batch, (long long)heads,
+                    (long long)q_len, (long long)k_len);
     if (batch == 0) return ISPORE_OK;
-    if (!score || !qk || !mask) return fail(ISPORE_ENULL, "scale_mask_softmax: NULL buffer");
+    if (!score || !qk || (CAUSAL ? (!ms.q_lens || !ms.k_lens) : !ms.mask))
+        return fail(ISPORE_ENULL, "%s: NULL buffer", name);
     const int64_t total_rows = batch * heads * q_len;
     constexpr int E = VecTraits<T>::kElems;
-    const bool vec_ok = k_len % E == 0 && aligned16(score) && aligned16(qk) && aligned16(mask) &&
+    const bool vec_ok = k_len % E == 0 && aligned16(score) && aligned16(qk) && (CAUSAL || aligned16(ms.mask)) &&
                         total_rows < (1ll << 32) && heads < (1ll << 31);
     const int64_t vecs = k_len / E;
     if (vec_ok) {
         const int rv = static_cast<int>(vecs);
-#define ISPORE_SOFTMAX(VPT, GROUP, THREADS, HG) \
-    return launch_groups<T, VPT, GROUP, THREADS, HG>(score, qk, mask, batch, heads, q_len, rv, scale, st)
-        if (vecs <= 32) ISPORE_SOFTMAX(1, 32, 256, 4);
-        if (vecs <= 64) {
-#ifdef ISPORE_TUNING
-            switch (tune(kTuneSoftmax, 0)) {
-                case 1: return launch_groups<T, 2, 32, 256, 2, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 2: return launch_groups<T, 2, 32, 256, 1, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 3: return launch_groups<T, 2, 32, 256, 4, 3>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 4: return launch_groups<T, 2, 32, 256, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 5: return launch_groups<T, 2, 32, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 6: return launch_groups<T, 2, 32, 128, 4, 6>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 7: return launch_groups<T, 2, 32, 256, 8, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                default: break;
-            }
-#endif
-            return launch_groups<T, 2, 32, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-        }
-        if (vecs <= 128) ISPORE_SOFTMAX(4, 32, 256, 2);
-        if (vecs <= 256) ISPORE_SOFTMAX(1, 256, 256, 4);
-        if (vecs <= 512) {
-#ifdef ISPORE_TUNING
-            switch (tune(kTuneSoftmax, 0)) {
-                case 1: return launch_groups<T, 2, 256, 256, 2, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 2: return launch_groups<T, 2, 256, 256, 1, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 3: return launch_groups<T, 2, 256, 256, 4, 3>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 4: return launch_groups<T, 2, 256, 256, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 5: return launch_groups<T, 2, 256, 256, 2, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 6: return launch_groups<T, 4, 128, 128, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                case 7: return launch_groups<T, 2, 256, 256, 8, 1>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-                default: break;
-            }
-#endif
-            return launch_groups<T, 4, 128, 128, 4, 4>(score, qk, mask, batch, heads, q_len, rv, scale, st);
-        }
-        if (vecs <= 1024) ISPORE_SOFTMAX(4, 256, 256, 2);
-        if (vecs <= 2048) ISPORE_SOFTMAX(4, 512, 512, 2);
+#define ISPORE_SOFTMAX(VPT, GROUP, THREADS, HG, MINB) \
+    return launch_groups<T, CAUSAL, VPT, GROUP, THREADS, HG, MINB>(score, qk, ms, batch, heads, q_len, rv, scale, st)
+        if (vecs <= 32) ISPORE_SOFTMAX(1, 32, 256, 4, 1);
+        if (vecs <= 64) ISPORE_SOFTMAX(2, 32, 256, 2, 4);
+        if (vecs <= 128) ISPORE_SOFTMAX(4, 32, 256, 2, 1);
+        if (vecs <= 256) ISPORE_SOFTMAX(1, 256, 256, 4, 1);
+        if (vecs <= 512) ISPORE_SOFTMAX(4, 128, 128, 4, 4);
+        if (vecs <= 1024) ISPORE_SOFTMAX(4, 256, 256, 2, 1);
+        if (vecs <= 2048) ISPORE_SOFTMAX(4, 512, 512, 2, 1);
 #undef ISPORE_SOFTMAX
     }
     const int64_t rows_per_batch = heads * q_len;
-    softmax_generic_kernel<T, 256><<<persistent_grid(softmax_generic_kernel<T, 256>, 256, 0, total_rows, 8), 256, 0, st>>>(
-        score, qk, mask, total_rows, rows_per_batch, static_cast<int>(q_len), k_len, scale);
+    auto generic = softmax_generic_kernel<T, 256, CAUSAL>;
+    generic<<<persistent_grid(generic, 256, 0, total_rows, 8), 256, 0, st>>>(
+        score, qk, ms.mask, ms.q_lens, ms.k_lens, total_rows, rows_per_batch, static_cast<int>(q_len), k_len, scale);
     return check_launch("softmax_generic_kernel");
 }
 
@@ -297,15 +316,27 @@ extern "C" {
 int ispore_scale_mask_softmax_f32(float* attn_score, const float* qk, const float* mask,
                                   int64_t batch_size, int64_t head_num, int64_t q_len, int64_t k_len,
                                   float scale, ispore_stream_t stream) {
-    return ispore::softmax_dispatch<float>(attn_score, qk, mask, batch_size, head_num, q_len, k_len,
-                                           scale, static_cast<cudaStream_t>(stream));
+    return ispore::softmax_dispatch<float, false>(attn_score, qk, {mask, nullptr, nullptr}, batch_size, head_num,
+                                                  q_len, k_len, scale, static_cast<cudaStream_t>(stream));
 }
 int ispore_scale_mask_softmax_f16(void* attn_score, const void* qk, const void* mask,
                                   int64_t batch_size, int64_t head_num, int64_t q_len, int64_t k_len,
                                   float scale, ispore_stream_t stream) {
-    return ispore::softmax_dispatch<__half>(static_cast<__half*>(attn_score),
-                                            static_cast<const __half*>(qk),
-                                            static_cast<const __half*>(mask), batch_size, head_num,
-                                            q_len, k_len, scale, static_cast<cudaStream_t>(stream));
+    return ispore::softmax_dispatch<__half, false>(static_cast<__half*>(attn_score), static_cast<const __half*>(qk),
+                                                   {static_cast<const __half*>(mask), nullptr, nullptr}, batch_size,
+                                                   head_num, q_len, k_len, scale, static_cast<cudaStream_t>(stream));
+}
+int ispore_scale_causal_softmax_f32(float* attn_score, const float* qk, const int32_t* q_lens, const int32_t* k_lens,
+                                    int64_t batch_size, int64_t head_num, int64_t q_len, int64_t k_len, float scale,
+                                    ispore_stream_t stream) {
+    return ispore::softmax_dispatch<float, true>(attn_score, qk, {nullptr, q_lens, k_lens}, batch_size, head_num,
+                                                 q_len, k_len, scale, static_cast<cudaStream_t>(stream));
+}
+int ispore_scale_causal_softmax_f16(void* attn_score, const void* qk, const int32_t* q_lens, const int32_t* k_lens,
+                                    int64_t batch_size, int64_t head_num, int64_t q_len, int64_t k_len, float scale,
+                                    ispore_stream_t stream) {
+    return ispore::softmax_dispatch<__half, true>(static_cast<__half*>(attn_score), static_cast<const __half*>(qk),
+                                                  {nullptr, q_lens, k_lens}, batch_size, head_num, q_len, k_len, scale,
+                                                  static_cast<cudaStream_t>(stream));
 }
 }

@@ -147,6 +147,16 @@ def launchScaleMaskAndSoftmax(qk: torch.Tensor, mask: torch.Tensor, attn_score: 
           q_len, k_len, scale)
 
 
+def launchScaleCausalSoftmax(qk: torch.Tensor, q_lens: torch.Tensor, k_lens: torch.Tensor, attn_score: torch.Tensor,
+                             scale: float) -> None:
+    """launchBuildCausalMasks + launchScaleMaskAndSoftmax in one kernel: the mask comes from the
+    int32 length arrays q_lens, k_lens [bs] and is never materialised."""
+    _dev(qk, q_lens, k_lens, attn_score)
+    batch, heads, q_len, k_len = qk.shape
+    _call(f"ispore_scale_causal_softmax_{_suffix(qk)}", qk, _ptr(attn_score), _ptr(qk), _ptr(q_lens), _ptr(k_lens),
+          batch, heads, q_len, k_len, scale)
+
+
 def launchTopKforBeamSearch(probs: torch.Tensor, topk_ids: torch.Tensor, topk_vals: torch.Tensor,
                             final_topk_ids: torch.Tensor, final_topk_vals: torch.Tensor, index_offset: int = 0,
                             uniform: Optional[torch.Tensor] = None, temperature: float = 1.0,

@@ -373,6 +373,44 @@ def test_softmax_fully_masked_rows_are_zero_and_in_place(ops, orc, rng):
     assert np.all(host(d)[1, :, 2] == 0.0)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("case", SOFTMAX_CASES)
+def test_causal_softmax_equals_mask_then_softmax(ops, orc, rng, case, dtype):
+    # the fused call must reproduce, bit for bit, the two calls it replaces, and match the oracle
+    # run on the oracle's mask
+    batch, heads, q_len, k_len = case
+    qk = (rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32) * 3).astype(dtype)
+    ql = rng.integers(0, q_len + 1, batch)
+    kl = np.minimum(ql + rng.integers(0, k_len + 1, batch), k_len)
+    ql[0], kl[0] = min(q_len, k_len), min(q_len, k_len)
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    dqk, dql, dkl = dev(qk), _i32(ql), _i32(kl)
+    mask = torch.empty((batch, q_len, k_len), dtype=tdt, device="cuda:0")
+    two, fused = torch.empty(qk.shape, dtype=tdt, device="cuda:0"), torch.empty(qk.shape, dtype=tdt, device="cuda:0")
+    scale = 1.0 / np.sqrt(128.0)
+    ops.launchBuildCausalMasks(mask, dql, dkl)
+    ops.launchScaleMaskAndSoftmax(dqk, mask, two, scale)
+    ops.launchScaleCausalSoftmax(dqk, dql, dkl, fused, scale)
+    assert np.array_equal(host(fused).view(np.uint8), host(two).view(np.uint8))
+    want, want32 = orc.scale_mask_softmax(qk, orc.build_causal_mask(ql, kl, q_len, k_len, dtype), np.float32(scale))
+    if dtype == np.float16:
+        err, over, _ = assert_close_f16(host(fused), want32, want, "causal softmax f16")
+        assert over == 0 and err < 3e-4
+    else:
+        assert_close_f32(host(fused), want, floor=1e-30, what="causal softmax f32")
+
+
+def test_causal_softmax_in_place_and_rows_past_qlen_are_zero(ops, rng):
+    qk = rng.standard_normal((2, 3, 8, 64), dtype=np.float32)
+    d = dev(qk)
+    ops.launchScaleCausalSoftmax(d, _i32([8, 5]), _i32([8, 20]), d, 0.3)
+    got = host(d)
+    assert np.all(got[1, :, 5:] == 0.0)                      # rows q >= q_len
+    assert np.all(got[1, :, :5, :15] == 0.0)                 # history keys before k_len - q_len
+    assert np.allclose(got[0].sum(-1), 1.0, atol=1e-5) and np.allclose(got[1, :, :5].sum(-1), 1.0, atol=1e-5)
+    assert np.all(np.triu(got[0, 0], 1) == 0.0)
+
+
 # ---- top-K and sampling --------------------------------------------------------------------------------------------------------
 
 def _topk_run(ops, probs, K, slices=8, index_offset=0, uniform=None, temperature=1.0):
