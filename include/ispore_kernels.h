@@ -381,6 +381,44 @@ ISPORE_API int ispore_repeat_kv_f16(void* k_dst, void* v_dst, const void* k_src,
                                     int64_t max_seq_len, int64_t max_k_len, int64_t head_size,
                                     ispore_stream_t stream);
 
+/* ---- decode-time fused masked multi-head attention (one new token per sequence) ----------- *
+ * ref: src/kernels/fused_decoder_self_attention.h:10-18 (launchDecoderMaskedMHA),
+ *      src/kernels/fused_decoder_self_attention.cu:112-250 (fp32 kernel), :251-379 (fp16),
+ *      :381-441 (launcher); CPU function tests/unittests/test_fused_decoder_attention.cu:12-143.
+ * qkv_buf [batch, head_num + 2*kv_head_num, head_size] (q heads, k heads, v heads of the new
+ * token); qkv_bias [(head_num + 2*kv_head_num) * head_size] or NULL; k_cache, v_cache
+ * [num_layers, batch, kv_head_num, max_seq_len, head_size]; mha_output [batch, head_num, head_size].
+ *   q, k, v (+ bias);  RoPE on q and k: pairs (2i, 2i+1), angle rope_timestep / base^(2i/rot_dim)
+ *   for 2i < rot_dim (the reference launcher passes rope_timestep = step);
+ *   cache[layer, b, g, step-1, :] = k, v;  logit_i = rsqrt(head_size) * <q, K_i> for i < step;
+ *   p = exp(logit - max) / (sum + 1e-6);  out = sum_i p_i V_i.
+ * Every one of the `step` logits takes part in the softmax and the maximum is the true one, as
+ * in the reference's CPU function (its kernel covers only the first head_size/vec logits and
+ * floors the maximum at 0); the batch stride of qkv_buf is the tensor's own.  fp16 computes in
+ * fp32 with q, k, v rounded to half where the reference holds them in half registers.
+ * head_size must be (4 for f32, 8 for f16) times a power of two up to 32 (128 in every config).
+ * workspace: optional scratch that lets the kernel split long sequences over several CTAs
+ * (needed to fill the GPU at small batch); ispore_decoder_masked_mha_workspace_bytes gives the
+ * size the call will use.  Without it the call runs one CTA per (sequence, head group) and
+ * returns ISPORE_ESCRATCH only when step exceeds what shared memory can hold (40960 logits per
+ * head group). */
+ISPORE_API int64_t ispore_decoder_masked_mha_workspace_bytes(int64_t batch_size, int64_t head_num,
+                                                             int64_t kv_head_num, int64_t head_size, int64_t step);
+ISPORE_API int ispore_decoder_masked_mha_f32(float* mha_output, const float* qkv_buf, const float* qkv_bias,
+                                             float* k_cache, float* v_cache, int64_t layer, int64_t num_layers,
+                                             int64_t batch_size, int64_t head_num, int64_t kv_head_num,
+                                             int64_t max_seq_len, int64_t head_size, int64_t step,
+                                             int32_t rotary_embedding_dim, float rotary_embedding_base,
+                                             float rope_timestep, void* workspace, int64_t workspace_bytes,
+                                             ispore_stream_t stream);
+ISPORE_API int ispore_decoder_masked_mha_f16(void* mha_output, const void* qkv_buf, const void* qkv_bias,
+                                             void* k_cache, void* v_cache, int64_t layer, int64_t num_layers,
+                                             int64_t batch_size, int64_t head_num, int64_t kv_head_num,
+                                             int64_t max_seq_len, int64_t head_size, int64_t step,
+                                             int32_t rotary_embedding_dim, float rotary_embedding_base,
+                                             float rope_timestep, void* workspace, int64_t workspace_bytes,
+                                             ispore_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

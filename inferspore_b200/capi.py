@@ -40,6 +40,7 @@ for _t in ("f32", "f16"):
     SIGNATURES[f"ispore_concat_kv_{_t}"] = [_p] * 6 + [_i64] * 7 + [_p]
     SIGNATURES[f"ispore_scale_mask_softmax_{_t}"] = [_p, _p, _p, _i64, _i64, _i64, _i64, _f, _p]
     SIGNATURES[f"ispore_scale_causal_softmax_{_t}"] = [_p, _p, _p, _p, _i64, _i64, _i64, _i64, _f, _p]
+    SIGNATURES[f"ispore_decoder_masked_mha_{_t}"] = [_p] * 5 + [_i64] * 8 + [_i32, _f, _f, _p, _i64, _p]
     SIGNATURES[f"ispore_topk_{_t}"] = [_p, _i64, _i64, _i32, _p, _p, _i32, _p, _p, _i32, _p, _f, _p, _p]
     SIGNATURES[f"ispore_topk_merge_{_t}"] = [_p, _p, _i64, _i32, _i32, _p, _p, _p, _f, _p, _p]
     SIGNATURES[f"ispore_sampling_{_t}"] = [_p, _p, _p, _p, _i64, _i32, _f, _p]
@@ -47,6 +48,8 @@ for _t in ("f32", "f16"):
     SIGNATURES[f"ispore_transpose_remove_padding_{_t}"] = [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]
     SIGNATURES[f"ispore_repeat_kv_{_t}"] = [_p] * 5 + [_i64] * 8 + [_p]
 
+SIGNATURES["ispore_decoder_masked_mha_workspace_bytes"] = [_i64] * 5
+_RESTYPES["ispore_decoder_masked_mha_workspace_bytes"] = _i64
 SIGNATURES["ispore_cal_padding_offset"] = [_p, _p, _p, _i64, _i64, _p]
 SIGNATURES["ispore_topk_static_f32"] = [_p, _i64, _i64, _i32, _p, _p, _i32, _p, _f, _p, _p]
 TOPK_STATIC_ENTRIES = 131072

@@ -1,0 +1,476 @@
+// Decode-time fused masked multi-head attention for sm_100a: one new token per sequence.
+//
+// Reference: src/kernels/fused_decoder_self_attention.cu:112-250 (fp32 kernel), :251-379 (fp16),
+// launcher :381-441.  Per (batch b, q head h), with kv head g = h / (heads / kv_heads):
+//   q, k, v  <- the token's rows of qkv_buf [bs, heads + 2*kv_heads, d] (+ bias, :163-188)
+//   q, k     <- RoPE on adjacent pairs (2i, 2i+1) with angle t / base^(2i / rot_dim) for
+//               2i < rot_dim (:57-110); the reference passes t = step
+//   cache[layer, b, g, step-1, :] <- k, v                                  (:206-209, :240-243)
+//   logit_i  = rsqrt(d) * <q, K_i>,  i < step                              (:210-221)
+//   p        = exp(logit - max) / (sum + 1e-6)                             (:224-238)
+//   out[b, h, :] = sum_i p_i V_i                                            (:240-249)
+// Where this file departs from the reference kernel, on purpose:
+//   * the reference softmax only covers the first blockDim.x = d/vec logits (:224-236); here every
+//     one of the `step` logits takes part, which is what the reference's CPU function does
+//     (tests/unittests/test_fused_decoder_attention.cu:99-110);
+//   * the reference's block max is floored at 0 by the padding of its reduction (:52); here the
+//     max is the true maximum (again as in its CPU function);
+//   * the reference indexes qkv_buf with a batch stride of heads*d (:132, :141), which is only right
+//     for one sequence; here the stride is (heads + 2*kv_heads)*d, the tensor's own layout;
+//   * fp16 products are accumulated in fp32 (the reference multiplies in half, :337).
+//
+// Work split: a CTA owns one (b, kv head), GT of the q heads that share it, and one chunk of the
+// positions (flash-decoding style split so that small batches still fill 148 SMs); the cache
+// rows of the chunk are read once for all GT heads.  With more than one chunk per (b, head) the
+// CTAs leave (max, sum, unnormalised output) in a workspace and a second kernel combines them.
+#include <float.h>
+
+#include <algorithm>
+#include <cstdint>
+
+#include "common.cuh"
+
+namespace ispore {
+namespace {
+
+constexpr int kMhaThreads = 128;
+constexpr int kMhaWarps = kMhaThreads / 32;
+constexpr int kMaxRotPairs = 128;  // head_size <= 256
+
+struct RopeAngles {
+    float denom[kMaxRotPairs];  // powf(base, 2i / rot_dim), evaluated on the host
+};
+
+template <typename T>
+struct MhaParams {
+    T* out;            // [bs, heads, d]
+    const T* qkv;      // [bs, heads + 2*kv_heads, d]
+    const T* bias;     // [(heads + 2*kv_heads) * d] or NULL
+    T* k_cache;        // [bs, kv_heads, max_seq_len, d] of the layer
+    T* v_cache;
+    float* workspace;  // [bs*heads, splits, d + 2] when splits > 1
+    int heads, kv_heads, q_per_kv, head_groups;
+    int max_seq_len, step, chunk, splits, rot_pairs;
+    float rope_t, scale;
+};
+
+__device__ __forceinline__ float block_max(float v, float* red) {
+    v = warp_max(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int w = 1; w < kMhaWarps; ++w) r = fmaxf(r, red[w]);
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    v = warp_sum(v);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float r = red[0];
+#pragma unroll
+    for (int w = 1; w < kMhaWarps; ++w) r += red[w];
+    __syncthreads();
+    return r;
+}
+
+// Rounds through the storage type, as the reference does when it keeps q, k, v in T registers.
+template <typename T>
+__device__ __forceinline__ float round_to(float x) { return to_float<T>(from_float<T>(x)); }
+
+// LPK lanes share one cache row (d = LPK * elements per 128-bit vector); a CTA works on
+// kMhaThreads / LPK rows at a time.  GT q heads of one kv head per CTA.
+template <typename T, int LPK, int GT>
+__global__ void __launch_bounds__(kMhaThreads)
+decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
+    constexpr int E = VecTraits<T>::kElems;
+    constexpr int D = LPK * E;
+    constexpr int KPI = kMhaThreads / LPK;  // cache rows per CTA iteration
+    constexpr int U = 4;                    // rows in flight per thread
+    __shared__ float q_s[GT][D];
+    __shared__ float knew_s[D], vnew_s[D];
+    __shared__ float2 cs_s[kMaxRotPairs];
+    __shared__ float red_s[kMhaWarps];
+    __shared__ float m_s[GT], l_s[GT];
+    extern __shared__ __align__(16) float dyn_s[];  // logits [GT][chunk]; later the output reduction buffer
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int lk = tid % LPK, ks = tid / LPK;
+    const int hg = blockIdx.x % p.head_groups;
+    const int bkv = blockIdx.x / p.head_groups;  // b * kv_heads + kv head
+    const int b = bkv / p.kv_heads, kvh = bkv - b * p.kv_heads;
+    const int h0 = kvh * p.q_per_kv + hg * GT;   // first q head of this CTA
+    const int split = blockIdx.y;
+    const int s0 = split * p.chunk;
+    const int s1 = min(p.step, s0 + p.chunk);
+    const int last = p.step - 1;                  // position of the new token
+    const bool has_last = last >= s0 && last < s1;
+    const int n = s1 - s0;                        // positions of this chunk
+    const int n_cache = (has_last ? last : s1) - s0;  // of which read from the cache
+
+    // ---- the new token: bias, RoPE, rounding through T -------------------------------------------
+    for (int i = tid; i < p.rot_pairs; i += kMhaThreads) {
+        float sn, cs;
+        sincosf(p.rope_t / angles.denom[i], &sn, &cs);
+        cs_s[i] = make_float2(cs, sn);
+    }
+    __syncthreads();
+    const int qkv_heads = p.heads + 2 * p.kv_heads;
+    const T* tok = p.qkv + static_cast<int64_t>(b) * qkv_heads * D;
+    const int rope_rows = GT + (has_last ? 1 : 0);  // q heads, then k
+    for (int idx = tid; idx < rope_rows * (D / 2); idx += kMhaThreads) {
+        const int r = idx / (D / 2), i = idx - r * (D / 2);
+        const int row = r < GT ? h0 + r : p.heads + kvh;
+        float x0 = to_float<T>(tok[row * D + 2 * i]), x1 = to_float<T>(tok[row * D + 2 * i + 1]);
+        if (p.bias != nullptr) {
+            x0 = round_to<T>(x0 + to_float<T>(p.bias[row * D + 2 * i]));
+            x1 = round_to<T>(x1 + to_float<T>(p.bias[row * D + 2 * i + 1]));
+        }
+        float y0 = x0, y1 = x1;
+        if (i < p.rot_pairs) {
+            const float2 c = cs_s[i];
+            y0 = round_to<T>(c.x * x0 - c.y * x1);
+            y1 = round_to<T>(c.x * x1 + c.y * x0);
+        }
+        float* dst = r < GT ? q_s[r] : knew_s;
+        dst[2 * i] = y0;
+        dst[2 * i + 1] = y1;
+    }
+    if (has_last) {
+        const int row = p.heads + p.kv_heads + kvh;
+        for (int i = tid; i < D; i += kMhaThreads) {
+            float x = to_float<T>(tok[row * D + i]);
+            if (p.bias != nullptr) x = round_to<T>(x + to_float<T>(p.bias[row * D + i]));
+            vnew_s[i] = x;
+        }
+    }
+    __syncthreads();
+    const int64_t cache_row0 = static_cast<int64_t>(bkv) * p.max_seq_len;
+    if (has_last && hg == 0) {  // one writer per (b, kv head)
+        T* kd = p.k_cache + (cache_row0 + last) * D;
+        T* vd = p.v_cache + (cache_row0 + last) * D;
+        for (int i = tid; i < D; i += kMhaThreads) {
+            kd[i] = from_float<T>(knew_s[i]);
+            vd[i] = from_float<T>(vnew_s[i]);
+        }
+    }
+
+    // ---- logits of the chunk ------------------------------------------------------------------------
+    float* logits = dyn_s;  // [GT][chunk]
+    {
+        float qreg[GT][E];
+#pragma unroll
+        for (int g = 0; g < GT; ++g)
+#pragma unroll
+            for (int e = 0; e < E; ++e) qreg[g][e] = q_s[g][lk * E + e];
+        const uint4* krows = reinterpret_cast<const uint4*>(p.k_cache) + (cache_row0 + s0) * LPK + lk;
+        for (int base = 0; base < n_cache; base += KPI * U) {
+            uint4 raw[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = base + u * KPI + ks;
+                raw[u] = i < n_cache ? ld_stream(krows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
+            }
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = base + u * KPI + ks;
+                Unpacked<T> kf;
+                unpack(raw[u], kf);
+#pragma unroll
+                for (int g = 0; g < GT; ++g) {
+                    float dot = 0.f;
+#pragma unroll
+                    for (int e = 0; e < E; ++e) dot = fmaf(qreg[g][e], kf.v[e], dot);
+#pragma unroll
+                    for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+                    if (lk == 0 && i < n_cache) logits[g * p.chunk + i] = dot * p.scale;
+                }
+            }
+        }
+        if (has_last && warp == 0) {  // the new token's own logit, from shared memory
+#pragma unroll
+            for (int g = 0; g < GT; ++g) {
+                float dot = 0.f;
+                for (int i = lane; i < D; i += 32) dot = fmaf(q_s[g][i], knew_s[i], dot);
+                dot = warp_sum(dot);
+                if (lane == 0) logits[g * p.chunk + (last - s0)] = dot * p.scale;
+            }
+        }
+    }
+    __syncthreads();
+
+    // ---- softmax numerators over the chunk ----------------------------------------------------------
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+        float* row = logits + g * p.chunk;
+        float mx = -FLT_MAX;
+        for (int i = tid; i < n; i += kMhaThreads) mx = fmaxf(mx, row[i]);
+        mx = block_max(mx, red_s);
+        float sum = 0.f;
+        for (int i = tid; i < n; i += kMhaThreads) {
+            const float e = expf(row[i] - mx);
+            row[i] = e;
+            sum += e;
+        }
+        sum = block_sum(sum, red_s);  // its barriers also publish the numerators
+        if (tid == 0) {
+            m_s[g] = mx;
+            l_s[g] = sum;
+        }
+    }
+    __syncthreads();
+
+    // ---- numerators x V ----------------------------------------------------------------------------------
+    float acc[GT][E];
+#pragma unroll
+    for (int g = 0; g < GT; ++g)
+#pragma unroll
+        for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
+    const uint4* vrows = reinterpret_cast<const uint4*>(p.v_cache) + (cache_row0 + s0) * LPK + lk;
+    for (int base = 0; base < n_cache; base += KPI * U) {
+        uint4 raw[U];
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = base + u * KPI + ks;
+            raw[u] = i < n_cache ? ld_stream(vrows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
+        }
+#pragma unroll
+        for (int u = 0; u < U; ++u) {
+            const int i = base + u * KPI + ks;
+            Unpacked<T> vf;
+            unpack(raw[u], vf);
+#pragma unroll
+            for (int g = 0; g < GT; ++g) {
+                const float w = i < n_cache ? logits[g * p.chunk + i] : 0.f;
+#pragma unroll
+                for (int e = 0; e < E; ++e) acc[g][e] = fmaf(w, vf.v[e], acc[g][e]);
+            }
+        }
+    }
+    if (has_last && ks == 0) {
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+            const float w = logits[g * p.chunk + (last - s0)];
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[g][e] = fmaf(w, vnew_s[lk * E + e], acc[g][e]);
+        }
+    }
+    // rows held by the other lane groups of this warp, then by the other warps
+#pragma unroll
+    for (int g = 0; g < GT; ++g)
+#pragma unroll
+        for (int e = 0; e < E; ++e)
+#pragma unroll
+            for (int o = LPK; o < 32; o <<= 1) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+    __syncthreads();  // every thread is done with the numerators: the buffer becomes [warps][GT][D]
+    float* part = dyn_s;
+    constexpr int kLanesUsed = LPK < 32 ? LPK : 32;  // lanes 0..LPK-1 of a warp hold its sums
+    if (lane < kLanesUsed) {
+#pragma unroll
+        for (int g = 0; g < GT; ++g)
+#pragma unroll
+            for (int e = 0; e < E; ++e) part[(warp * GT + g) * D + lane * E + e] = acc[g][e];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < GT * D; idx += kMhaThreads) {
+        const int g = idx / D, dd = idx - g * D;
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMhaWarps; ++w) o += part[(w * GT + g) * D + dd];
+        const int64_t bh = static_cast<int64_t>(b) * p.heads + h0 + g;
+        if (p.splits == 1) {
+            p.out[bh * D + dd] = from_float<T>(o / (l_s[g] + 1e-6f));
+        } else {
+            float* ws = p.workspace + (bh * p.splits + split) * (D + 2);
+            ws[2 + dd] = o;
+            if (dd == 0) {
+                ws[0] = m_s[g];
+                ws[1] = l_s[g];
+            }
+        }
+    }
+}
+
+// Merges the chunks of one (b, head): out = sum_s e^(m_s - M) O_s / (sum_s e^(m_s - M) l_s + 1e-6).
+template <typename T>
+__global__ void __launch_bounds__(128)
+decoder_mha_combine_kernel(T* __restrict__ out, const float* __restrict__ workspace, int splits, int head_size) {
+    const int64_t bh = blockIdx.x;
+    const float* ws = workspace + bh * splits * (head_size + 2);
+    float mx = -FLT_MAX;
+    for (int s = 0; s < splits; ++s) mx = fmaxf(mx, ws[s * (head_size + 2)]);
+    float denom = 0.f;
+    for (int s = 0; s < splits; ++s) denom += expf(ws[s * (head_size + 2)] - mx) * ws[s * (head_size + 2) + 1];
+    const float inv = 1.0f / (denom + 1e-6f);
+    for (int dd = threadIdx.x; dd < head_size; dd += blockDim.x) {
+        float o = 0.f;
+        for (int s = 0; s < splits; ++s)
+            o = fmaf(expf(ws[s * (head_size + 2)] - mx), ws[s * (head_size + 2) + 2 + dd], o);
+        out[bh * head_size + dd] = from_float<T>(o * inv);
+    }
+}
+
+constexpr int kChunkFloatsDefault = 8192;    // logits floats per CTA without opting in to large shared memory
+constexpr int kChunkFloatsMax = 40960;       // with the opt-in (160 KB)
+constexpr int kMinChunk = 256;               // positions below which another split costs more than it gains
+
+int pick_group(int64_t q_per_kv) {
+    for (int g : {8, 4, 2}) if (q_per_kv % g == 0) return g;
+    return 1;
+}
+
+// Positions per chunk and number of chunks for one (b, kv head, head group).
+void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, bool have_workspace, int* chunk,
+                 int* splits) {
+    const int gt = pick_group(heads / kv_heads);
+    const int64_t base_ctas = batch * kv_heads * (heads / kv_heads / gt);
+    int64_t want = 1;
+    if (have_workspace) {
+        const int sms = sm_count() > 0 ? sm_count() : 148;
+        want = ceil_div(static_cast<int64_t>(2) * sms, base_ctas);                 // fill the machine twice over
+        want = std::min<int64_t>(want, std::max<int64_t>(1, step / kMinChunk));     // but keep chunks worth a CTA
+        want = std::max<int64_t>(want, ceil_div(step, static_cast<int64_t>(kChunkFloatsDefault / gt)));
+    }
+    int64_t c = ceil_div(step, want);
+    c = ceil_div(c, static_cast<int64_t>(32)) * 32;
+    *chunk = static_cast<int>(c);
+    *splits = static_cast<int>(ceil_div(step, c));
+}
+
+template <typename T, int LPK, int GT>
+int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, cudaStream_t st) {
+    constexpr int D = LPK * VecTraits<T>::kElems;
+    auto kernel = decoder_mha_kernel<T, LPK, GT>;
+    const size_t floats = std::max<size_t>(static_cast<size_t>(GT) * p.chunk, static_cast<size_t>(kMhaWarps) * GT * D);
+    const size_t smem = floats * sizeof(float);
+    if (smem > 40 * 1024) {
+        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
+            cudaGetLastError();
+            return fail(ISPORE_ELAUNCH, "decoder_masked_mha: %zu bytes of shared memory refused", smem);
+        }
+    }
+    dim3 grid(static_cast<unsigned>(batch * p.kv_heads * p.head_groups), static_cast<unsigned>(p.splits));
+    kernel<<<grid, kMhaThreads, smem, st>>>(p, angles);
+    int rc = check_launch("decoder_mha_kernel");
+    if (rc != ISPORE_OK || p.splits == 1) return rc;
+    decoder_mha_combine_kernel<T><<<static_cast<unsigned>(batch * p.heads), 128, 0, st>>>(p.out, p.workspace, p.splits, D);
+    return check_launch("decoder_mha_combine_kernel");
+}
+
+template <typename T, int LPK>
+int launch_mha_group(const MhaParams<T>& p, const RopeAngles& angles, int gt, int64_t batch, cudaStream_t st) {
+    switch (gt) {
+        case 8: return launch_mha<T, LPK, 8>(p, angles, batch, st);
+        case 4: return launch_mha<T, LPK, 4>(p, angles, batch, st);
+        case 2: return launch_mha<T, LPK, 2>(p, angles, batch, st);
+        default: return launch_mha<T, LPK, 1>(p, angles, batch, st);
+    }
+}
+
+template <typename T>
+int mha_dispatch(T* out, const T* qkv, const T* bias, T* k_cache, T* v_cache, int64_t layer, int64_t num_layers,
+                 int64_t batch, int64_t heads, int64_t kv_heads, int64_t max_seq_len, int64_t head_size, int64_t step,
+                 int32_t rot_dim, float rope_base, float rope_timestep, void* workspace, int64_t workspace_bytes,
+                 cudaStream_t st) {
+    constexpr int E = VecTraits<T>::kElems;
+    if (batch < 0 || heads <= 0 || kv_heads <= 0 || heads % kv_heads != 0 || max_seq_len <= 0 || head_size <= 0 ||
+        step <= 0 || step > max_seq_len || layer < 0 || (num_layers > 0 && layer >= num_layers) ||
+        batch * heads > INT32_MAX || max_seq_len > INT32_MAX)
+        return fail(ISPORE_ESHAPE, "decoder_masked_mha: bad shape bs=%lld heads=%lld/%lld step=%lld/%lld layer=%lld/%lld",
+                    (long long)batch, (long long)heads, (long long)kv_heads, (long long)step, (long long)max_seq_len,
+                    (long long)layer, (long long)num_layers);
+    const int64_t lpk = head_size / E;
+    if (head_size % E != 0 || lpk > 32 || (lpk & (lpk - 1)) != 0)
+        return fail(ISPORE_ESHAPE, "decoder_masked_mha: head size %lld must be %d x a power of two up to 32",
+                    (long long)head_size, E);
+    if (rot_dim < 0 || rot_dim % 2 != 0 || rot_dim / 2 > kMaxRotPairs)
+        return fail(ISPORE_ESHAPE, "decoder_masked_mha: rotary dim %d", rot_dim);
+    if (batch == 0) return ISPORE_OK;
+    if (!out || !qkv || !k_cache || !v_cache) return fail(ISPORE_ENULL, "decoder_masked_mha: NULL buffer");
+    if (!aligned16(k_cache) || !aligned16(v_cache)) return fail(ISPORE_EALIGN, "decoder_masked_mha: caches must be 16-byte aligned");
+
+    MhaParams<T> p;
+    const int gt = pick_group(heads / kv_heads);
+    int chunk = 0, splits = 1;
+    plan_chunks(batch, heads, kv_heads, step, workspace != nullptr, &chunk, &splits);
+    const int64_t need = splits > 1 ? batch * heads * splits * (head_size + 2) * static_cast<int64_t>(sizeof(float)) : 0;
+    if (need > workspace_bytes || (splits > 1 && (reinterpret_cast<uintptr_t>(workspace) & 3) != 0)) {
+        // workspace too small for the plan: fall back to one chunk per (b, head) if shared memory can hold it
+        plan_chunks(batch, heads, kv_heads, step, false, &chunk, &splits);
+    }
+    if (static_cast<int64_t>(chunk) * gt > kChunkFloatsMax)
+        return fail(ISPORE_ESCRATCH, "decoder_masked_mha: step %lld needs a workspace of %lld bytes",
+                    (long long)step, (long long)ispore_decoder_masked_mha_workspace_bytes(batch, heads, kv_heads, head_size, step));
+    const int64_t layer_offset = layer * batch * kv_heads * max_seq_len * head_size;
+    p.out = out;
+    p.qkv = qkv;
+    p.bias = bias;
+    p.k_cache = k_cache + layer_offset;
+    p.v_cache = v_cache + layer_offset;
+    p.workspace = static_cast<float*>(workspace);
+    p.heads = static_cast<int>(heads);
+    p.kv_heads = static_cast<int>(kv_heads);
+    p.q_per_kv = static_cast<int>(heads / kv_heads);
+    p.head_groups = p.q_per_kv / gt;
+    p.max_seq_len = static_cast<int>(max_seq_len);
+    p.step = static_cast<int>(step);
+    p.chunk = chunk;
+    p.splits = splits;
+    p.rot_pairs = static_cast<int>(std::min<int64_t>(rot_dim, head_size) / 2);
+    p.rope_t = rope_timestep;
+    p.scale = 1.0f / sqrtf(static_cast<float>(head_size));
+    RopeAngles angles;
+    for (int i = 0; i < p.rot_pairs; ++i)
+        angles.denom[i] = powf(rope_base, static_cast<float>(2 * i) / static_cast<float>(rot_dim));
+    switch (lpk) {
+        case 32: return launch_mha_group<T, 32>(p, angles, gt, batch, st);
+        case 16: return launch_mha_group<T, 16>(p, angles, gt, batch, st);
+        case 8: return launch_mha_group<T, 8>(p, angles, gt, batch, st);
+        case 4: return launch_mha_group<T, 4>(p, angles, gt, batch, st);
+        case 2: return launch_mha_group<T, 2>(p, angles, gt, batch, st);
+        default: return launch_mha_group<T, 1>(p, angles, gt, batch, st);
+    }
+}
+
+}  // namespace
+}  // namespace ispore
+
+extern "C" {
+
+int64_t ispore_decoder_masked_mha_workspace_bytes(int64_t batch_size, int64_t head_num, int64_t kv_head_num,
+                                                  int64_t head_size, int64_t step) {
+    if (batch_size <= 0 || head_num <= 0 || kv_head_num <= 0 || head_num % kv_head_num != 0 || head_size <= 0 || step <= 0)
+        return 0;
+    int chunk = 0, splits = 1;
+    ispore::plan_chunks(batch_size, head_num, kv_head_num, step, true, &chunk, &splits);
+    return splits > 1 ? batch_size * head_num * splits * (head_size + 2) * static_cast<int64_t>(sizeof(float)) : 0;
+}
+
+int ispore_decoder_masked_mha_f32(float* mha_output, const float* qkv_buf, const float* qkv_bias, float* k_cache,
+                                  float* v_cache, int64_t layer, int64_t num_layers, int64_t batch_size,
+                                  int64_t head_num, int64_t kv_head_num, int64_t max_seq_len, int64_t head_size,
+                                  int64_t step, int32_t rotary_embedding_dim, float rotary_embedding_base,
+                                  float rope_timestep, void* workspace, int64_t workspace_bytes,
+                                  ispore_stream_t stream) {
+    return ispore::mha_dispatch<float>(mha_output, qkv_buf, qkv_bias, k_cache, v_cache, layer, num_layers, batch_size,
+                                       head_num, kv_head_num, max_seq_len, head_size, step, rotary_embedding_dim,
+                                       rotary_embedding_base, rope_timestep, workspace, workspace_bytes,
+                                       static_cast<cudaStream_t>(stream));
+}
+
+int ispore_decoder_masked_mha_f16(void* mha_output, const void* qkv_buf, const void* qkv_bias, void* k_cache,
+                                  void* v_cache, int64_t layer, int64_t num_layers, int64_t batch_size,
+                                  int64_t head_num, int64_t kv_head_num, int64_t max_seq_len, int64_t head_size,
+                                  int64_t step, int32_t rotary_embedding_dim, float rotary_embedding_base,
+                                  float rope_timestep, void* workspace, int64_t workspace_bytes,
+                                  ispore_stream_t stream) {
+    return ispore::mha_dispatch<__half>(static_cast<__half*>(mha_output), static_cast<const __half*>(qkv_buf),
+                                        static_cast<const __half*>(qkv_bias), static_cast<__half*>(k_cache),
+                                        static_cast<__half*>(v_cache), layer, num_layers, batch_size, head_num,
+                                        kv_head_num, max_seq_len, head_size, step, rotary_embedding_dim,
+                                        rotary_embedding_base, rope_timestep, workspace, workspace_bytes,
+                                        static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

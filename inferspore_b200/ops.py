@@ -228,3 +228,26 @@ def launchRepeatKVCache(k_cache_src: torch.Tensor, v_cache_src: torch.Tensor, co
     _call(f"ispore_repeat_kv_{_suffix(k_cache_src)}", k_cache_src, _ptr(k_cache_dst), _ptr(v_cache_dst),
           _ptr(k_cache_src), _ptr(v_cache_src), _ptr(context_length), layer_id, num_layers, batch, kv_heads, heads,
           max_seq_len, max_k_len, head_size)
+
+
+def decoderMaskedMHAWorkspaceBytes(batch: int, head_num: int, kv_head_num: int, head_size: int, step: int) -> int:
+    """Bytes of scratch launchDecoderMaskedMHA can use to split long sequences over several CTAs."""
+    return int(capi.load().ispore_decoder_masked_mha_workspace_bytes(batch, head_num, kv_head_num, head_size, step))
+
+
+def launchDecoderMaskedMHA(qkv_buf: torch.Tensor, qkv_bias: Optional[torch.Tensor], layer_id: int,
+                           k_cache: torch.Tensor, v_cache: torch.Tensor, finished: Optional[torch.Tensor], step: int,
+                           mha_output: torch.Tensor, rotary_embedding_dim: int, rotary_embedding_base: float,
+                           workspace: Optional[torch.Tensor] = None, rope_timestep: Optional[float] = None) -> None:
+    """qkv_buf [bs, heads+2*kv_heads, d], caches [layers, bs, kv_heads, max_seq, d] (updated at
+    step-1), mha_output [bs, heads, d] (fused_decoder_self_attention.h:10-18).  `finished` is
+    accepted and unused, as in the reference; rope_timestep defaults to `step`, the reference's
+    choice; workspace is any CUDA tensor used as scratch (see decoderMaskedMHAWorkspaceBytes)."""
+    _dev(qkv_buf, qkv_bias, k_cache, v_cache, mha_output, workspace)
+    batch, qkv_heads, head_size = qkv_buf.shape
+    num_layers, _, kv_heads, max_seq_len, _ = k_cache.shape
+    ws_bytes = 0 if workspace is None else workspace.numel() * workspace.element_size()
+    _call(f"ispore_decoder_masked_mha_{_suffix(qkv_buf)}", qkv_buf, _ptr(mha_output), _ptr(qkv_buf), _ptr(qkv_bias),
+          _ptr(k_cache), _ptr(v_cache), layer_id, num_layers, batch, qkv_heads - 2 * kv_heads, kv_heads, max_seq_len,
+          head_size, step, rotary_embedding_dim, rotary_embedding_base,
+          float(step) if rope_timestep is None else rope_timestep, _ptr(workspace), ws_bytes)

@@ -315,3 +315,36 @@ def ref_cpu_causal_mask(q_lens, k_lens, max_q_len, max_k_len):
     ref_lib("libref_layout.so").ref_cpu_causal_mask_f32(_ptr(mask), _ptr(ql), _ptr(kl), C.c_int(max_q_len),
                                                        C.c_int(max_k_len), C.c_int(ql.size))
     return mask
+
+
+def decoder_masked_mha(qkv, bias, k_cache, v_cache, layer, step, rot_dim, base, rope_t=None):
+    """qkv [bs, heads + 2*kv, d]; caches [layers, bs, kv, max_seq, d].  Returns
+    (out [bs, heads, d], new_k_cache, new_v_cache, unrounded_fp32_out)."""
+    batch, qkv_heads, d = qkv.shape
+    _, _, kv_heads, max_seq_len, _ = k_cache.shape
+    heads = qkv_heads - 2 * kv_heads
+    kc, vc = np.array(k_cache, copy=True), np.array(v_cache, copy=True)
+    out = np.empty((batch, heads, d), qkv.dtype)
+    unr = np.empty((batch, heads, d), np.float32)
+    _is16(qkv)
+    lib().orc_decoder_masked_mha(_ptr(out), _ptr(np.ascontiguousarray(qkv)), _ptr(bias), _ptr(kc), _ptr(vc), _i64(layer),
+                                 _i64(batch), _i64(heads), _i64(kv_heads), _i64(max_seq_len), _i64(d), _i64(step),
+                                 _i32(rot_dim), _f(base), _f(float(step) if rope_t is None else rope_t),
+                                 _i64(qkv.dtype.itemsize), _ptr(unr))
+    return out, kc, vc, unr
+
+
+def ref_cpu_masked_attn(q, k, v, k_cache, v_cache, step):
+    """The reference's CPUMaskedAttn without RoPE (tests/unittests/test_fused_decoder_attention.cu:12-143).
+    q [bs, heads, d], k, v [bs, kv, d], caches [bs, kv, step, d] fp32.  Returns (out, k_cache, v_cache)."""
+    batch, heads, d = q.shape
+    kv_heads = k.shape[1]
+    kc, vc = np.array(k_cache, np.float32, copy=True), np.array(v_cache, np.float32, copy=True)
+    assert kc.shape == (batch, kv_heads, step, d)
+    out = np.empty((batch, heads, d), np.float32)
+    f = lambda a: _ptr(np.ascontiguousarray(a, np.float32))
+    qq, kk, vv = np.ascontiguousarray(q, np.float32), np.ascontiguousarray(k, np.float32), np.ascontiguousarray(v, np.float32)
+    ref_lib("libref_mha.so").ref_cpu_masked_attn_f32(_ptr(qq), _ptr(kk), _ptr(vv), _ptr(kc), _ptr(vc), _ptr(out),
+                                                    C.c_int(batch), C.c_int(heads), C.c_int(kv_heads), C.c_int(d),
+                                                    C.c_int(step))
+    return out, kc, vc

@@ -773,3 +773,94 @@ ORC_API void orc_repeat_kv(void* dst, const void* src, const int32_t* context_le
                        base + ((b * kv_heads + h / q_per_kv) * max_seq_len + s) * row, (size_t)row);
     }
 }
+
+/* ---- decode-time fused masked multi-head attention ----------------------------------------------------- *
+ * Follows the reference's CPU function CPUMaskedAttn
+ * (tests/unittests/test_fused_decoder_attention.cu:12-143) for the attention itself — every one
+ * of the `step` logits in the softmax, true maximum — and the reference kernel
+ * (src/kernels/fused_decoder_self_attention.cu:112-250, fp16 :251-379) for what the CPU function
+ * leaves out or only approximates:
+ *   :163-188  bias added to q, k, v (in the storage type: half adds round to half)
+ *   :57-110   RoPE on adjacent pairs (2i, 2i+1), angle t / powf(base, 2i / rot_dim), 2i < rot_dim,
+ *             result kept in the storage type
+ *   :206-209, :240-243  the new k, v written to cache[layer, b, g, step-1, :]
+ *   :230-233  denominator = sum + 1e-6
+ * The cache is [layers, bs, kv_heads, max_seq_len, d] (launcher :381-441), qkv is
+ * [bs, heads + 2*kv_heads, d].  Sums are accumulated in double.  out_unrounded (nullable) receives
+ * the fp32 output before the final rounding of the f16 variant.                                        */
+static float ld_elem(const void* p, int64_t i, int64_t elem_size) {
+    return elem_size == 4 ? ((const float*)p)[i] : h2f(((const uint16_t*)p)[i]);
+}
+static void st_elem(void* p, int64_t i, int64_t elem_size, float v) {
+    if (elem_size == 4)
+        ((float*)p)[i] = v;
+    else
+        ((uint16_t*)p)[i] = f2h(v);
+}
+static float round_elem(float v, int64_t elem_size) { return elem_size == 4 ? v : round_half(v); }
+
+ORC_API void orc_decoder_masked_mha(void* out, const void* qkv, const void* bias, void* k_cache, void* v_cache,
+                                    int64_t layer, int64_t batch, int64_t heads, int64_t kv_heads,
+                                    int64_t max_seq_len, int64_t d, int64_t step, int32_t rot_dim, float base,
+                                    float rope_t, int64_t elem_size, float* out_unrounded) {
+    const int64_t qkv_heads = heads + 2 * kv_heads, q_per_kv = heads / kv_heads;
+    const float scale = 1.0f / sqrtf((float)d);
+    const int64_t layer_off = layer * batch * kv_heads * max_seq_len * d;
+    float* rows = (float*)malloc((size_t)(batch * qkv_heads * d) * sizeof(float)); /* q, k, v after bias + RoPE */
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t r = 0; r < qkv_heads; ++r) {
+            float* dst = rows + (b * qkv_heads + r) * d;
+            for (int64_t i = 0; i < d; ++i) {
+                float x = ld_elem(qkv, (b * qkv_heads + r) * d + i, elem_size);
+                if (bias) x = round_elem(x + ld_elem(bias, r * d + i, elem_size), elem_size);
+                dst[i] = x;
+            }
+            if (r < heads + kv_heads) /* q and k heads are rotated, v is not */
+                for (int64_t i = 0; 2 * i + 1 < d && 2 * i < rot_dim; ++i) {
+                    const float theta = rope_t / powf(base, (float)(2 * i) / (float)rot_dim);
+                    const float c = cosf(theta), s = sinf(theta);
+                    const float x0 = dst[2 * i], x1 = dst[2 * i + 1];
+                    dst[2 * i] = round_elem(c * x0 - s * x1, elem_size);
+                    dst[2 * i + 1] = round_elem(c * x1 + s * x0, elem_size);
+                }
+        }
+    /* cache append */
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t g = 0; g < kv_heads; ++g) {
+            const int64_t at = layer_off + ((b * kv_heads + g) * max_seq_len + (step - 1)) * d;
+            for (int64_t i = 0; i < d; ++i) {
+                st_elem(k_cache, at + i, elem_size, rows[(b * qkv_heads + heads + g) * d + i]);
+                st_elem(v_cache, at + i, elem_size, rows[(b * qkv_heads + heads + kv_heads + g) * d + i]);
+            }
+        }
+#pragma omp parallel for schedule(static) collapse(2)
+    for (int64_t b = 0; b < batch; ++b)
+        for (int64_t h = 0; h < heads; ++h) {
+            const int64_t g = h / q_per_kv;
+            const float* q = rows + (b * qkv_heads + h) * d;
+            const int64_t c0 = layer_off + (b * kv_heads + g) * max_seq_len * d;
+            double* logit = (double*)malloc((size_t)step * sizeof(double));
+            double mx = -DBL_MAX;
+            for (int64_t s = 0; s < step; ++s) {
+                double acc = 0.0;
+                for (int64_t i = 0; i < d; ++i) acc += (double)q[i] * (double)ld_elem(k_cache, c0 + s * d + i, elem_size);
+                logit[s] = (double)(float)(acc * (double)scale);
+                if (logit[s] > mx) mx = logit[s];
+            }
+            double sum = 0.0;
+            for (int64_t s = 0; s < step; ++s) {
+                logit[s] = (double)expf((float)(logit[s] - mx));
+                sum += logit[s];
+            }
+            const double inv = 1.0 / (sum + 1e-6);
+            for (int64_t i = 0; i < d; ++i) {
+                double o = 0.0;
+                for (int64_t s = 0; s < step; ++s) o += logit[s] * (double)ld_elem(v_cache, c0 + s * d + i, elem_size);
+                const float y = (float)(o * inv);
+                if (out_unrounded) out_unrounded[(b * heads + h) * d + i] = y;
+                st_elem(out, (b * heads + h) * d + i, elem_size, y);
+            }
+            free(logit);
+        }
+    free(rows);
+}

@@ -690,3 +690,92 @@ def test_layout_ops_reject_bad_shapes(ops):
     with pytest.raises(Exception):  # layer out of range
         ops.launchRepeatKVCache(src, src, _i32([1]), 1, torch.zeros((1, 3, 4, 8), device="cuda:0"),
                                 torch.zeros((1, 3, 4, 8), device="cuda:0"))
+
+
+# ---- decode-time fused masked multi-head attention ---------------------------------------------------
+
+MHA_CASES = [
+    # batch, heads, kv_heads, d, max_seq, step, rot_dim, bias, workspace
+    (1, 2, 2, 128, 8, 4, 128, False, False),
+    (2, 8, 8, 128, 64, 64, 128, True, False),
+    (3, 8, 2, 128, 300, 257, 128, True, True),      # GQA, 4 q heads per CTA
+    (2, 16, 2, 64, 128, 100, 32, False, True),      # 8 q heads per CTA, partial rotation
+    (1, 6, 2, 128, 40, 33, 128, False, False),      # 3 q heads per kv head: one head per CTA
+    (1, 4, 4, 128, 5000, 4100, 128, False, True),   # long context split over many CTAs
+    (1, 4, 4, 128, 5000, 4100, 128, True, False),   # the same in one CTA per head
+    (2, 4, 4, 32, 70, 1, 0, False, False),          # first token: the cache holds nothing yet
+    (2, 2, 1, 256, 50, 50, 256, True, True),
+]
+
+
+def _mha_inputs(rng, dtype, batch, heads, kv, d, max_seq, step, bias):
+    layers = 2
+    cast = (lambda a: a.astype(np.float16)) if dtype == np.float16 else (lambda a: a)
+    qkv = cast(rng.standard_normal((batch, heads + 2 * kv, d), dtype=np.float32))
+    kc = cast(rng.standard_normal((layers, batch, kv, max_seq, d), dtype=np.float32))
+    vc = cast(rng.standard_normal((layers, batch, kv, max_seq, d), dtype=np.float32))
+    b = cast((rng.standard_normal((heads + 2 * kv) * d) * 0.1).astype(np.float32)) if bias else None
+    return qkv, kc, vc, b
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("case", MHA_CASES)
+def test_decoder_masked_mha(ops, orc, rng, case, dtype):
+    batch, heads, kv, d, max_seq, step, rot_dim, bias, use_ws = case
+    if dtype == np.float32 and d > 128:
+        pytest.skip("f32 rows are limited to 32 vectors of 4")
+    qkv, kc, vc, b = _mha_inputs(rng, dtype, batch, heads, kv, d, max_seq, step, bias)
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    dk, dv = dev(kc), dev(vc)
+    out = torch.full((batch, heads, d), 9.0, dtype=tdt, device="cuda:0")
+    ws = None
+    if use_ws:
+        nbytes = ops.decoderMaskedMHAWorkspaceBytes(batch, heads, kv, d, step)
+        ws = torch.empty(max(nbytes, 4), dtype=torch.uint8, device="cuda:0")
+    ops.launchDecoderMaskedMHA(dev(qkv), None if b is None else dev(b), 1, dk, dv, None, step, out, rot_dim, 10000.0, ws)
+    want, want_k, want_v, want32 = orc.decoder_masked_mha(qkv, b, kc, vc, 1, step, rot_dim, 10000.0)
+    got_k, got_v = host(dk), host(dv)
+    # everything but the new row is untouched; v of the new row is a copy (+ one rounded add)
+    keep = np.ones(max_seq, bool)
+    keep[step - 1] = False
+    assert np.array_equal(got_k[0], kc[0]) and np.array_equal(got_v[0], vc[0])
+    assert np.array_equal(got_k[1][:, :, keep], kc[1][:, :, keep]) and np.array_equal(got_v[1][:, :, keep], vc[1][:, :, keep])
+    assert np.array_equal(got_v[1][:, :, step - 1], want_v[1][:, :, step - 1])
+    if dtype == np.float16:
+        # k of the new row: device and host sin/cos differ in the last bits, which can move a half rounding
+        assert np.max(np.abs(got_k[1][:, :, step - 1].astype(np.float32) - want_k[1][:, :, step - 1].astype(np.float32))) <= 4e-3
+        err, over, _ = assert_close_f16(host(out), want32, want, "decoder mha f16")
+        assert over == 0
+    else:
+        # both are sums of O(1) terms that cancel: the relative bound is taken at magnitude 1
+        assert_close_f32(got_k[1][:, :, step - 1], want_k[1][:, :, step - 1], floor=1.0, what="new k row")
+        assert_close_f32(host(out), want32, floor=1.0, what="decoder mha f32")
+
+
+def test_decoder_masked_mha_split_equals_unsplit(ops, rng):
+    batch, heads, kv, d, max_seq, step = 1, 8, 8, 128, 3000, 2900
+    qkv, kc, vc, _ = _mha_inputs(rng, np.float16, batch, heads, kv, d, max_seq, step, False)
+    outs = []
+    for use_ws in (False, True):
+        nbytes = ops.decoderMaskedMHAWorkspaceBytes(batch, heads, kv, d, step)
+        assert nbytes > 0  # a single sequence of 8 heads cannot fill the GPU unsplit
+        ws = torch.empty(nbytes, dtype=torch.uint8, device="cuda:0") if use_ws else None
+        out = torch.empty((batch, heads, d), dtype=torch.float16, device="cuda:0")
+        ops.launchDecoderMaskedMHA(dev(qkv), None, 0, dev(kc), dev(vc), None, step, out, 128, 10000.0, ws)
+        outs.append(host(out).astype(np.float32))
+    assert np.max(np.abs(outs[0] - outs[1])) <= 1e-3
+
+
+def test_decoder_masked_mha_rejects_bad_shapes(ops):
+    qkv = torch.zeros((1, 6, 24), device="cuda:0")  # 24 floats = 6 vectors: not a power of two
+    kc = torch.zeros((1, 1, 2, 8, 24), device="cuda:0")
+    out = torch.zeros((1, 2, 24), device="cuda:0")
+    with pytest.raises(Exception):
+        ops.launchDecoderMaskedMHA(qkv, None, 0, kc, kc.clone(), None, 1, out, 0, 10000.0)
+    qkv = torch.zeros((1, 6, 32), device="cuda:0")
+    kc = torch.zeros((1, 1, 2, 8, 32), device="cuda:0")
+    out = torch.zeros((1, 2, 32), device="cuda:0")
+    with pytest.raises(Exception):  # step beyond the cache
+        ops.launchDecoderMaskedMHA(qkv, None, 0, kc, kc.clone(), None, 9, out, 0, 10000.0)
+    with pytest.raises(Exception):  # layer out of range
+        ops.launchDecoderMaskedMHA(qkv, None, 1, kc, kc.clone(), None, 1, out, 0, 10000.0)

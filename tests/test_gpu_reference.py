@@ -41,12 +41,12 @@ def _p(t):
 
 # ---- the reference's unit tests, unmodified, linked against this library ----------------------------
 
-def _run(name, *args):
+def _run(name, *args, ok_codes=(0,)):
     exe = DROPIN / name
     if not exe.exists():
         pytest.skip("oracle/_ref/dropin was not built (reference tree absent at build time)")
     proc = subprocess.run([str(exe), *args], capture_output=True, text=True, timeout=300)
-    assert proc.returncode == 0, proc.stdout[-2000:] + proc.stderr[-2000:]
+    assert proc.returncode in ok_codes, proc.stdout[-2000:] + proc.stderr[-2000:]
     return proc.stdout
 
 
@@ -135,6 +135,16 @@ def test_dropin_repeat_kv(cuda):
     out = _run("test_repeat_kv")
     vals = [float(l.split("=")[-1]) for l in out.splitlines() if l.startswith("k trans[")]
     assert vals == [0, 1, 2, 3, 8, 9, 10, 11]
+
+
+def test_dropin_fused_decoder_attention(cuda):
+    # Compile, link and launch only.  The test's own verdict is not usable: its V pointer starts
+    # past the end of the host qkv buffer (test_fused_decoder_attention.cu:226, 8 + 16 = 24 = the
+    # buffer's size), and its CPU RoPE is marked approximate and differs from its kernel's, so
+    # it prints FAILED for any implementation; numeric parity for this op comes from the
+    # oracle (pinned on the same CPU function without RoPE) and from the reference kernel below.
+    out = _run("test_fused_decoder_attention", ok_codes=(0, 1))
+    assert "GPU kernel execution failed" not in out and ("TEST PASSED" in out or "TEST FAILED" in out)
 
 
 # ---- this library vs the reference's GPU kernels on random data -----------------------------------------
@@ -308,3 +318,38 @@ def test_vs_reference_gpu_repeat_kv(ops, orc, rng, half):
               max_seq, max_k, d) == 0
     torch.cuda.synchronize()
     assert np.array_equal(host(kd), host(rkd)) and np.array_equal(host(vd), host(rvd))
+
+
+@pytest.mark.parametrize("half", [False, True])
+@pytest.mark.parametrize("heads,kv,step,bias", [(4, 4, 32, False), (8, 2, 20, True), (2, 2, 1, False)])
+def test_vs_reference_gpu_decoder_masked_mha(ops, orc, rng, half, heads, kv, step, bias):
+    # One sequence, head size 128, step within the reference kernel's softmax coverage
+    # (32 threads for fp32, 64 for fp16); the logits are kept positive at their maximum so that
+    # the reference's 0-floored maximum coincides with the true one.  This pins the RoPE pairing
+    # and angle, the bias rows, the cache append and the GQA head mapping on the reference kernel.
+    lib = _ref(orc, "libref_mha.so")
+    d, max_seq, layers = 128, 40, 2
+    npdt, tdt = (np.float16, torch.float16) if half else (np.float32, torch.float32)
+    qkv32 = rng.standard_normal((1, heads + 2 * kv, d), dtype=np.float32) * 0.5
+    u = rng.standard_normal(d).astype(np.float32) * 0.5
+    qkv32[0, :heads] = u + 0.1 * qkv32[0, :heads]  # every q head close to u, every new k equal to u:
+    qkv32[0, heads:heads + kv] = u                 # the new token's own logit is about |u|^2 / sqrt(d) > 0
+    qkv = qkv32.astype(npdt)
+    kc = (rng.standard_normal((layers, 1, kv, max_seq, d), dtype=np.float32) * 0.5).astype(npdt)
+    vc = rng.standard_normal((layers, 1, kv, max_seq, d), dtype=np.float32).astype(npdt)
+    b = (rng.standard_normal((heads + 2 * kv) * d) * 0.1).astype(npdt) if bias else None
+    dq, db = dev(qkv), None if b is None else dev(b)
+    ok, ov, rk, rv = dev(kc), dev(vc), dev(kc), dev(vc)
+    ours = torch.zeros((1, heads, d), dtype=tdt, device="cuda:0")
+    ref = torch.zeros((1, heads, d), dtype=tdt, device="cuda:0")
+    ops.launchDecoderMaskedMHA(dq, db, 1, ok, ov, None, step, ours, 128, 10000.0)
+    fn = lib.ref_gpu_masked_mha_f16 if half else lib.ref_gpu_masked_mha_f32
+    assert fn(_p(dq), None if db is None else _p(db), 1, _p(rk), _p(rv), _p(ref), layers, 1, heads, kv, max_seq, d, step,
+              128, C.c_float(10000.0)) == 0
+    torch.cuda.synchronize()
+    tol = 4e-3 if half else 2e-5
+    assert np.array_equal(host(ov), host(rv))
+    assert np.max(np.abs(host(ok).astype(np.float64) - host(rk).astype(np.float64))) <= tol
+    # the reference multiplies q*k*scale in the storage type (half products for fp16): 1e-3 is
+    # its own test's tolerance and what half products allow; fp32 agrees far closer
+    assert np.max(np.abs(host(ours).astype(np.float64) - host(ref).astype(np.float64))) <= (5e-3 if half else 5e-5)
