@@ -320,6 +320,106 @@ class GpuChain:
             events[8].record()
 
 
+NEXT_KERNELS = ["build_causal_mask", "scale_causal_softmax", "cal_padding_offset", "transpose_remove_padding",
+                "repeat_kv", "decoder_masked_mha"]
+
+
+class NextRows:
+    """The kernels either side of the chain (mask build, mask-free softmax, padding offsets,
+    transpose + remove padding, repeat-KV, decode-time fused attention), each at a Llama-2-7B shape
+    derived from `tokens` (prefill: tokens/512 sequences of 512) and `decode_batch` sequences with
+    `context` cached positions.  Timed one by one, outside the step the headline metric counts."""
+
+    def __init__(self, tokens: int, device, seed: int = 77, decode_batch: int = 64, context: int = 4096):
+        import torch
+
+        from inferspore_b200 import ops
+
+        self.torch, self.ops, self.dev = torch, ops, device
+        self.tokens, self.batch, self.decode_batch, self.context = tokens, tokens // SEQ, decode_batch, context
+        self.g = torch.Generator(device=device)
+        self.g.manual_seed(seed)
+        self._bufs = {}
+
+    def _randn(self, *shape, scale=1.0):
+        t = self.torch
+        return (t.randn(*shape, generator=self.g, device=self.dev, dtype=t.float32) * scale).to(t.float16)
+
+    def _i32(self, values):
+        return self.torch.tensor(values, dtype=self.torch.int32, device=self.dev)
+
+    def prepare(self, name: str):
+        """Allocates the kernel's buffers; returns (launch closure, algorithmic bytes, workload text)."""
+        t, o, h = self.torch, self.ops, self.torch.float16
+        B, T, dev = self.batch, self.tokens, self.dev
+        if name == "build_causal_mask":
+            mask = t.empty((B, SEQ, SEQ), dtype=h, device=dev)
+            ql = self._i32([SEQ] * B)
+            return (lambda: o.launchBuildCausalMasks(mask, ql, ql)), mask.numel() * 2, f"mask [{B}, {SEQ}, {SEQ}] f16"
+        if name == "scale_causal_softmax":
+            qk = self._randn(B, HEADS, SEQ, SEQ, scale=3.0)
+            out = t.empty_like(qk)
+            ql = self._i32([SEQ] * B)
+            return ((lambda: o.launchScaleCausalSoftmax(qk, ql, ql, out, 1.0 / float(np.sqrt(HEAD_SIZE)))),
+                    2 * qk.numel() * 2, f"qk [{B}, {HEADS}, {SEQ}, {SEQ}] f16, no mask tensor")
+        if name == "cal_padding_offset":
+            lens = self._i32([SEQ] * B)
+            po = t.empty((B, SEQ), dtype=t.int32, device=dev)
+            cum = t.empty(B + 1, dtype=t.int32, device=dev)
+            return (lambda: o.launchCalPaddingoffset(po, cum, lens)), B * SEQ * 4 + (2 * B + 1) * 4, f"{B} sequences of {SEQ}"
+        if name == "transpose_remove_padding":
+            x = self._randn(B, HEADS, SEQ, HEAD_SIZE)
+            out = t.empty((T, HEADS, HEAD_SIZE), dtype=h, device=dev)
+            po = t.zeros(T, dtype=t.int32, device=dev)
+            return ((lambda: o.launchTransposeOutRemovePadding(x, po, out)), 2 * x.numel() * 2 + T * 4,
+                    f"[{B}, {HEADS}, {SEQ}, {HEAD_SIZE}] f16 -> [{T}, {HEADS}, {HEAD_SIZE}]")
+        if name == "repeat_kv":  # a grouped-query shape: 8 kv heads under the 32 q heads
+            bs, kvh, ctx = 16, 8, 2048
+            ks, vs = self._randn(1, bs, kvh, 2 * ctx, HEAD_SIZE), self._randn(1, bs, kvh, 2 * ctx, HEAD_SIZE)
+            kd = t.empty((bs, HEADS, ctx, HEAD_SIZE), dtype=h, device=dev)
+            vd = t.empty_like(kd)
+            cl = self._i32([ctx] * bs)
+            nbytes = 2 * kd.numel() * 2 + 2 * bs * kvh * ctx * HEAD_SIZE * 2
+            return ((lambda: o.launchRepeatKVCache(ks, vs, cl, 0, kd, vd)), nbytes,
+                    f"{bs} sequences, {kvh} -> {HEADS} heads, context {ctx}, f16")
+        if name == "decoder_masked_mha":
+            bs, ctx = self.decode_batch, self.context
+            qkv = self._randn(bs, 3 * HEADS, HEAD_SIZE)
+            kc, vc = self._randn(1, bs, KV_HEADS, ctx, HEAD_SIZE), self._randn(1, bs, KV_HEADS, ctx, HEAD_SIZE)
+            out = t.empty((bs, HEADS, HEAD_SIZE), dtype=h, device=dev)
+            nb = o.decoderMaskedMHAWorkspaceBytes(bs, HEADS, KV_HEADS, HEAD_SIZE, ctx)
+            ws = t.empty(max(nb, 4), dtype=t.uint8, device=dev)
+            nbytes = 2 * bs * KV_HEADS * ctx * HEAD_SIZE * 2 + qkv.numel() * 2 + out.numel() * 2
+            return ((lambda: o.launchDecoderMaskedMHA(qkv, None, 0, kc, vc, None, ctx, out, ROT_DIM, ROT_BASE, ws)), nbytes,
+                    f"{bs} sequences, {HEADS} heads, step {ctx}, f16 caches ({nb >> 10} KiB split workspace)")
+        raise KeyError(name)
+
+    def time_one(self, name: str, steps: int, warmup: int):
+        t = self.torch
+        launch, nbytes, workload = self.prepare(name)
+        for _ in range(max(3, warmup)):
+            launch()
+        t.cuda.synchronize()
+        s, e = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(steps):
+            launch()
+        e.record()
+        t.cuda.synchronize()
+        return s.elapsed_time(e) / steps, nbytes, workload
+
+    def measure(self, steps: int = 20, warmup: int = 3) -> dict:
+        peak, _ = measured_peak_gbs()
+        out = {}
+        for name in NEXT_KERNELS:
+            ms, nbytes, workload = self.time_one(name, steps, warmup)
+            gbs = nbytes / (ms * 1e-3) / 1e9
+            out[name] = {"ms": round(ms, 5), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
+                         "bytes": nbytes, "workload": workload}
+            self.torch.cuda.empty_cache()
+        return out
+
+
 class HostDrivenChain:
     """The same chain for a caller whose data lives in host memory: every step copies the step's
     inputs from pinned host buffers to the GPU, runs the kernels and copies every output back."""
@@ -453,6 +553,10 @@ def run_ours(args) -> dict:
         "gpu_launches": K * LAUNCHES_PER_STEP,
         "device_status": status,
     }
+    if world == 1 and not args.no_next_rows:
+        del chain, e2e_chain, hd
+        torch.cuda.empty_cache()
+        out["next_rows"] = NextRows(tokens, device).measure()
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         rps, dt, cpu = time_cpu_chain(args.cpu_tokens, threads, steps=3, warmup=1, budget_s=40.0)
@@ -468,6 +572,13 @@ def run_only(args) -> dict:
 
     torch.cuda.set_device(0)
     device = torch.device("cuda", 0)
+    if args.only in NEXT_KERNELS:
+        ms, nbytes, workload = NextRows(args.tokens, device, decode_batch=max(1, args.tokens // 1024)).time_one(
+            args.only, args.steps, args.warmup)
+        peak, kind = measured_peak_gbs()
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"kernel": args.only, "workload": workload, "ms": round(ms, 5), "bytes": nbytes, "gbs": round(gbs, 1),
+                "frac_of_peak": round(gbs / peak, 4), "peak": peak, "peak_kind": kind, "steps": args.steps}
     chain = GpuChain(args.tokens, device, seed=1000)
     launch = dict(chain.launchers())[args.only]
     for _ in range(args.warmup):
@@ -517,7 +628,9 @@ def main() -> int:
     ap.add_argument("--e2e-steps", type=int, default=10)
     ap.add_argument("--cpu-tokens", type=int, default=4096, help="tokens per step of the CPU chain sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--only", choices=KERNELS, default=None,
+    ap.add_argument("--no-next-rows", action="store_true",
+                    help="skip the separately timed kernels either side of the chain (`next_rows`)")
+    ap.add_argument("--only", choices=KERNELS + NEXT_KERNELS, default=None,
                     help="run one kernel of the chain alone at --tokens (small cases for profiler captures)")
     ap.add_argument("--traffic", type=float, default=None,
                     help="override: DRAM bytes per launch of the roofline kernel from a fresh ncu capture")

@@ -79,15 +79,46 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
 template <typename T>
 __device__ __forceinline__ float round_to(float x) { return to_float<T>(from_float<T>(x)); }
 
+// Sums N per-lane values across the LPK lanes of a group with a halving butterfly: at each
+// level a lane keeps one half of its values and hands the other half to its partner, so N
+// values cost about N shuffles in total instead of N * log2(LPK).  On return the lane holds
+// max(1, N / LPK) finished sums, v[0..], for the value indices base, base + 1, ...; when
+// LPK > N the lanes that differ only in their lowest log2(LPK / N) bits hold duplicates.
+template <int N, int O>
+struct GroupReduce {
+    template <int NMAX>
+    static __device__ __forceinline__ void run(float (&v)[NMAX], int lk, int& base) {
+        if (N > 1) {
+            constexpr int kHalf = N > 1 ? N / 2 : 1;
+            const bool upper = (lk & O) != 0;
+#pragma unroll
+            for (int i = 0; i < kHalf; ++i) {
+                const float send = upper ? v[i] : v[i + kHalf];
+                const float keep = upper ? v[i + kHalf] : v[i];
+                v[i] = keep + __shfl_xor_sync(0xffffffffu, send, O);
+            }
+            if (upper) base += kHalf;
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], O);
+        }
+        GroupReduce<(N > 1 ? N / 2 : 1), O / 2>::run(v, lk, base);
+    }
+};
+template <int N>
+struct GroupReduce<N, 0> {
+    template <int NMAX>
+    static __device__ __forceinline__ void run(float (&)[NMAX], int, int&) {}
+};
+
 // LPK lanes share one cache row (d = LPK * elements per 128-bit vector); a CTA works on
 // kMhaThreads / LPK rows at a time.  GT q heads of one kv head per CTA.
-template <typename T, int LPK, int GT>
+template <typename T, int LPK, int GT, int U>
 __global__ void __launch_bounds__(kMhaThreads)
 decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int D = LPK * E;
     constexpr int KPI = kMhaThreads / LPK;  // cache rows per CTA iteration
-    constexpr int U = 4;                    // rows in flight per thread
+    constexpr int N = GT * U;               // dot products per thread per iteration (U rows in flight)
     __shared__ float q_s[GT][D];
     __shared__ float knew_s[D], vnew_s[D];
     __shared__ float2 cs_s[kMaxRotPairs];
@@ -172,9 +203,9 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
                 const int i = base + u * KPI + ks;
                 raw[u] = i < n_cache ? ld_stream(krows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
             }
+            float dots[N];  // index g * U + u
 #pragma unroll
             for (int u = 0; u < U; ++u) {
-                const int i = base + u * KPI + ks;
                 Unpacked<T> kf;
                 unpack(raw[u], kf);
 #pragma unroll
@@ -182,9 +213,19 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
                     float dot = 0.f;
 #pragma unroll
                     for (int e = 0; e < E; ++e) dot = fmaf(qreg[g][e], kf.v[e], dot);
+                    dots[g * U + u] = dot;
+                }
+            }
+            int first = 0;
+            GroupReduce<N, LPK / 2>::run(dots, lk, first);
+            constexpr int kHeld = N > LPK ? N / LPK : 1;   // finished sums per lane
+            constexpr int kDup = LPK > N ? LPK / N : 1;    // lanes holding the same sum
+            if ((lk & (kDup - 1)) == 0) {
 #pragma unroll
-                    for (int o = LPK / 2; o > 0; o >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-                    if (lk == 0 && i < n_cache) logits[g * p.chunk + i] = dot * p.scale;
+                for (int j = 0; j < kHeld; ++j) {
+                    const int idx = first + j, g = idx / U, u = idx % U;
+                    const int i = base + u * KPI + ks;
+                    if (i < n_cache) logits[g * p.chunk + i] = dots[j] * p.scale;
                 }
             }
         }
@@ -313,10 +354,10 @@ decoder_mha_combine_kernel(T* __restrict__ out, const float* __restrict__ worksp
 
 constexpr int kChunkFloatsDefault = 8192;    // logits floats per CTA without opting in to large shared memory
 constexpr int kChunkFloatsMax = 40960;       // with the opt-in (160 KB)
-constexpr int kMinChunk = 256;               // positions below which another split costs more than it gains
 
 int pick_group(int64_t q_per_kv) {
-    for (int g : {8, 4, 2}) if (q_per_kv % g == 0) return g;
+    const int cap = tune(kTuneAct, 4);
+    for (int g : {4, 2}) if (g <= cap && q_per_kv % g == 0) return g;
     return 1;
 }
 
@@ -327,9 +368,15 @@ void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, b
     const int64_t base_ctas = batch * kv_heads * (heads / kv_heads / gt);
     int64_t want = 1;
     if (have_workspace) {
+        // Many more CTAs than fit at once (the tail of the last wave then costs little), each
+        // still reading enough rows to pay for preparing q: 512 positions per CTA when that
+        // already gives 8 CTAs per SM; otherwise as many chunks as reach 16 per SM, down to 128
+        // positions each.
         const int sms = sm_count() > 0 ? sm_count() : 148;
-        want = ceil_div(static_cast<int64_t>(2) * sms, base_ctas);                 // fill the machine twice over
-        want = std::min<int64_t>(want, std::max<int64_t>(1, step / kMinChunk));     // but keep chunks worth a CTA
+        const int64_t enough = static_cast<int64_t>(tune(kTuneConcat, 8)) * sms;
+        const int64_t big = tune(kTuneSoftmax, 512), small = 128;
+        want = ceil_div(step, big);
+        if (base_ctas * want < enough) want = std::min(ceil_div(2 * enough, base_ctas), std::max<int64_t>(1, step / small));
         want = std::max<int64_t>(want, ceil_div(step, static_cast<int64_t>(kChunkFloatsDefault / gt)));
     }
     int64_t c = ceil_div(step, want);
@@ -338,10 +385,10 @@ void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, b
     *splits = static_cast<int>(ceil_div(step, c));
 }
 
-template <typename T, int LPK, int GT>
+template <typename T, int LPK, int GT, int U>
 int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, cudaStream_t st) {
     constexpr int D = LPK * VecTraits<T>::kElems;
-    auto kernel = decoder_mha_kernel<T, LPK, GT>;
+    auto kernel = decoder_mha_kernel<T, LPK, GT, U>;
     const size_t floats = std::max<size_t>(static_cast<size_t>(GT) * p.chunk, static_cast<size_t>(kMhaWarps) * GT * D);
     const size_t smem = floats * sizeof(float);
     if (smem > 40 * 1024) {
@@ -361,10 +408,9 @@ int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, c
 template <typename T, int LPK>
 int launch_mha_group(const MhaParams<T>& p, const RopeAngles& angles, int gt, int64_t batch, cudaStream_t st) {
     switch (gt) {
-        case 8: return launch_mha<T, LPK, 8>(p, angles, batch, st);
-        case 4: return launch_mha<T, LPK, 4>(p, angles, batch, st);
-        case 2: return launch_mha<T, LPK, 2>(p, angles, batch, st);
-        default: return launch_mha<T, LPK, 1>(p, angles, batch, st);
+        case 4: return launch_mha<T, LPK, 4, 4>(p, angles, batch, st);
+        case 2: return launch_mha<T, LPK, 2, 8>(p, angles, batch, st);
+        default: return launch_mha<T, LPK, 1, 8>(p, angles, batch, st);
     }
 }
 
