@@ -637,10 +637,20 @@ def main() -> int:
     args = ap.parse_args()
     if args.tokens % SEQ or args.e2e_tokens % SEQ or args.tokens <= 0:
         ap.error("--tokens and --e2e-tokens must be positive multiples of 512")
-    if args.only:
-        out = run_only(args)
-    else:
-        out = run_reference(args) if args.impl == "reference" else run_ours(args)
+    # stdout carries exactly one JSON line: anything a library prints there during the run (NCCL's
+    # version banner, for one) is sent to stderr instead, and the line is written to the real stdout.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+    try:
+        if args.only:
+            out = run_only(args)
+        else:
+            out = run_reference(args) if args.impl == "reference" else run_ours(args)
+        sys.stdout.flush()
+    finally:
+        os.dup2(real_stdout, 1)
+        os.close(real_stdout)
     if out:
         print(json.dumps(out), flush=True)
     return 0
