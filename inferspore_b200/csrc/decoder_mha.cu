@@ -356,7 +356,7 @@ constexpr int kChunkFloatsDefault = 8192;    // logits floats per CTA without op
 constexpr int kChunkFloatsMax = 40960;       // with the opt-in (160 KB)
 
 int pick_group(int64_t q_per_kv) {
-    const int cap = tune(kTuneAct, 4);
+    const int cap = tune(kTuneMhaGroup, 4);
     for (int g : {4, 2}) if (g <= cap && q_per_kv % g == 0) return g;
     return 1;
 }
@@ -373,8 +373,8 @@ void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, b
         // already gives 8 CTAs per SM; otherwise as many chunks as reach 16 per SM, down to 128
         // positions each.
         const int sms = sm_count() > 0 ? sm_count() : 148;
-        const int64_t enough = static_cast<int64_t>(tune(kTuneConcat, 8)) * sms;
-        const int64_t big = tune(kTuneSoftmax, 512), small = 128;
+        const int64_t enough = static_cast<int64_t>(tune(kTuneMhaCtasPerSm, 8)) * sms;
+        const int64_t big = tune(kTuneMhaChunk, 512), small = 128;
         want = ceil_div(step, big);
         if (base_ctas * want < enough) want = std::min(ceil_div(2 * enough, base_ctas), std::max<int64_t>(1, step / small));
         want = std::max<int64_t>(want, ceil_div(step, static_cast<int64_t>(kChunkFloatsDefault / gt)));

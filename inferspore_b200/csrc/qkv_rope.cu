@@ -17,6 +17,7 @@
 #include <math.h>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace ispore {
 namespace {
@@ -187,6 +188,117 @@ qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
     }
 }
 
+// The same work with the token staged through shared memory: a token's q, k and v heads are one
+// contiguous span of QKV (24 KB for Llama-2-7B in fp16), so one thread starts TMA bulk copies of
+// the whole span and the CTA looks up the position and evaluates cos/sin while they fly.  No
+// registers are tied up holding loads in flight, which lets eight CTAs (and their 8 x 24 KB of
+// outstanding reads) share an SM.  Full rotation (rotary_dim == HEAD_SIZE) only.
+constexpr int kTmaPiece = 8192;
+
+template <typename T, int THREADS, int HEAD_SIZE, bool HAS_BIAS>
+__global__ void __launch_bounds__(THREADS)
+qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* __restrict__ v_buf,
+                              const T* __restrict__ QKV, const T* __restrict__ bias,
+                              const int32_t* __restrict__ padding_offset,
+                              const int32_t* __restrict__ history_length, int64_t batch_size,
+                              int64_t seq_len, int head_num, int kv_head_num, const RopeDenominators freq,
+                              unsigned* __restrict__ status) {
+    constexpr int E = VecTraits<T>::kElems;
+    constexpr int kHeadVecs = HEAD_SIZE / E, kHalfVecs = kHeadVecs / 2, kRotHalf = HEAD_SIZE / 2;
+    extern __shared__ __align__(128) unsigned char token_raw[];
+    __shared__ float2 cos_sin[kRotHalf];
+    __shared__ __align__(8) uint64_t bar;
+    const int tid = threadIdx.x;
+    const int qkv_heads = head_num + 2 * kv_head_num;
+    const int64_t token = blockIdx.x;
+    const uint32_t bytes = static_cast<uint32_t>(qkv_heads) * HEAD_SIZE * sizeof(T);
+    if (tid == 0) {
+        tma::mbar_init(&bar, 1);
+        tma::fence_mbar_init();
+        tma::mbar_arrive_expect_tx(&bar, bytes);
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(QKV) + token * bytes;
+        for (uint32_t off = 0; off < bytes; off += kTmaPiece)
+            tma::load(token_raw + off, src + off, min(static_cast<uint32_t>(kTmaPiece), bytes - off), &bar);
+    }
+    const int64_t dst_token = token + __ldg(padding_offset + token);
+    const bool bad = dst_token < 0 || dst_token >= batch_size * seq_len;
+    int64_t b = 0, s = 0;
+    if (!bad) {
+        if (dst_token < (1ll << 31) && seq_len < (1ll << 31)) {
+            const uint32_t bq = static_cast<uint32_t>(dst_token) / static_cast<uint32_t>(seq_len);
+            b = bq;
+            s = static_cast<uint32_t>(dst_token) - bq * static_cast<uint32_t>(seq_len);
+        } else {
+            b = dst_token / seq_len;
+            s = dst_token - b * seq_len;
+        }
+        const float m = static_cast<float>(__ldg(history_length + b) + static_cast<int>(s));
+        for (int j = tid; j < kRotHalf; j += THREADS) {
+            float sn, cs;
+            sincosf(m / freq.d[j], &sn, &cs);
+            cos_sin[j] = make_float2(cs, sn);
+        }
+    }
+    __syncthreads();  // cos/sin written; the barrier's initialisation is visible to every waiter
+    // The copies land in this CTA's shared memory: wait for them even when the token is skipped.
+    if (!tma::mbar_wait(&bar, 0)) {
+        if (tid == 0) atomicOr(status, ISPORE_DEV_TIMEOUT);
+        return;
+    }
+    if (bad) {
+        if (tid == 0) atomicOr(status, ISPORE_DEV_BAD_PADDING);
+        return;
+    }
+    const uint4* tok = reinterpret_cast<const uint4*>(token_raw);
+    const uint4* bias_v = reinterpret_cast<const uint4*>(bias);
+    const int64_t head_stride = seq_len * kHeadVecs;
+    uint4* q_row = reinterpret_cast<uint4*>(q_buf) + (b * head_num * seq_len + s) * kHeadVecs;
+    uint4* k_row = reinterpret_cast<uint4*>(k_buf) + (b * kv_head_num * seq_len + s) * kHeadVecs;
+    uint4* v_row = reinterpret_cast<uint4*>(v_buf) + (b * kv_head_num * seq_len + s) * kHeadVecs;
+    const int rope_tasks = (head_num + kv_head_num) * kHalfVecs;
+    const int v_tasks = kv_head_num * kHeadVecs;
+    for (int task = tid; task < rope_tasks; task += THREADS) {
+        const int hh = task / kHalfVecs, c = task % kHalfVecs;
+        Unpacked<T> lo, hi;
+        unpack(tok[hh * kHeadVecs + c], lo);
+        unpack(tok[hh * kHeadVecs + kHalfVecs + c], hi);
+        if (HAS_BIAS) {
+            Unpacked<T> blo, bhi;
+            unpack(ld_keep(bias_v + hh * kHeadVecs + c), blo);
+            unpack(ld_keep(bias_v + hh * kHeadVecs + kHalfVecs + c), bhi);
+#pragma unroll
+            for (int e = 0; e < E; ++e) {
+                lo.v[e] += blo.v[e];
+                hi.v[e] += bhi.v[e];
+            }
+        }
+#pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float2 cs = cos_sin[c * E + e];
+            const float x0 = lo.v[e], x1 = hi.v[e];
+            lo.v[e] = cs.x * x0 - cs.y * x1;
+            hi.v[e] = cs.x * x1 + cs.y * x0;
+        }
+        uint4* dst = hh < head_num ? q_row + hh * head_stride : k_row + (hh - head_num) * head_stride;
+        st_stream(dst + c, pack(lo));
+        st_stream(dst + kHalfVecs + c, pack(hi));
+    }
+    const uint4* vtok = tok + (head_num + kv_head_num) * kHeadVecs;
+    for (int task = tid; task < v_tasks; task += THREADS) {
+        const int h = task / kHeadVecs, c = task % kHeadVecs;
+        uint4 raw = vtok[task];
+        if (HAS_BIAS) {
+            Unpacked<T> x, bb;
+            unpack(raw, x);
+            unpack(ld_keep(bias_v + (head_num + kv_head_num) * kHeadVecs + task), bb);
+#pragma unroll
+            for (int e = 0; e < E; ++e) x.v[e] += bb.v[e];
+            raw = pack(x);
+        }
+        st_stream(v_row + h * head_stride + c, raw);
+    }
+}
+
 // Any head size / alignment (head_size even): one thread per rotation pair.
 template <typename T, int THREADS>
 __global__ void __launch_bounds__(THREADS)
@@ -314,26 +426,33 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
             token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);     \
         return check_launch("qkv_rope_transpose_vec_kernel");                                           \
     } while (0)
-#ifdef ISPORE_TUNING
-        if (head_size == 128 && full_rot && has_bias && tune(kTuneQkv, 0) == 1) {
-            qkv_rope_transpose_vec_kernel<T, TH, 128, true, true, 1><<<grid, TH, 0, st>>>(
-                q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
-                token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
-            return check_launch("qkv");
+        // Full rotation at a compile-time head size: the shared-memory staged kernel.
+        const int64_t token_bytes = (head_num + 2 * kv_head_num) * head_size * static_cast<int64_t>(sizeof(T));
+        if (full_rot && (head_size == 128 || head_size == 64) && token_bytes <= 96 * 1024 && token_num < (1ll << 31) &&
+            tune(kTuneQkv, 0) != 1) {
+#define ISPORE_QKV_TMA(HS, HB)                                                                              \
+    do {                                                                                                    \
+        constexpr int TH = 128; /* measured: 64 and 256 threads are 3-6 % slower */                         \
+        auto kernel = qkv_rope_transpose_tma_kernel<T, TH, HS, HB>;                                         \
+        if (token_bytes > 40 * 1024 &&                                                                      \
+            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)token_bytes) != cudaSuccess) { \
+            cudaGetLastError();                                                                             \
+            break;                                                                                          \
+        }                                                                                                   \
+        kernel<<<static_cast<unsigned>(token_num), TH, static_cast<size_t>(token_bytes), st>>>(             \
+            q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,           \
+            (int)head_num, (int)kv_head_num, freq, status);                                                 \
+        return check_launch("qkv_rope_transpose_tma_kernel");                                               \
+    } while (0)
+            if (head_size == 128) {
+                if (has_bias) ISPORE_QKV_TMA(128, true);
+                else ISPORE_QKV_TMA(128, false);
+            } else {
+                if (has_bias) ISPORE_QKV_TMA(64, true);
+                else ISPORE_QKV_TMA(64, false);
+            }
+#undef ISPORE_QKV_TMA
         }
-        if (head_size == 128 && full_rot && has_bias && tune(kTuneQkv, 0) == 2) {
-            qkv_rope_transpose_vec_kernel<T, 256, 128, true, true, 0><<<grid, 256, 0, st>>>(
-                q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
-                token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
-            return check_launch("qkv");
-        }
-        if (head_size == 128 && full_rot && has_bias && tune(kTuneQkv, 0) == 3) {
-            qkv_rope_transpose_vec_kernel<T, 64, 128, true, true, 0><<<grid, 64, 0, st>>>(
-                q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,
-                token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);
-            return check_launch("qkv");
-        }
-#endif
         if (head_size == 128 && full_rot) {
             if (has_bias) ISPORE_QKV(128, true, true);
             ISPORE_QKV(128, true, false);
