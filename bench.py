@@ -422,25 +422,64 @@ class NextRows:
 
 class HostDrivenChain:
     """The same chain for a caller whose data lives in host memory: every step copies the step's
-    inputs from pinned host buffers to the GPU, runs the kernels and copies every output back."""
+    inputs from pinned host buffers to the GPU, runs the kernels and copies every output back.
 
-    def __init__(self, chain: GpuChain):
-        torch = chain.torch
-        self.c = chain
-        c = chain
-        self.inputs = [c.ids, c.qkv, c.qk, c.attn_out, c.act_in, c.logits[0], c.u]
-        self.outputs = [c.x, c.res, c.q, c.k, c.v, c.score, c.attn_out, c.act_out, c.top_i, c.top_v, c.picked]
-        self.h_in = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in self.inputs]
-        self.h_out = [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in self.outputs]
-        self.h2d = sum(t.numel() * t.element_size() for t in self.inputs)
-        self.d2h = sum(t.numel() * t.element_size() for t in self.outputs)
+    The three phases of a step run on three streams (copy in, kernels, copy out) and consecutive
+    steps alternate between two sets of device buffers, so step i's copy out and step i+1's copy
+    in use the two directions of the PCIe link at the same time.  Every step still moves all of its
+    inputs and outputs; events order the phases of a step and the reuse of a buffer set."""
+
+    def __init__(self, chains):
+        torch = chains[0].torch
+        self.torch, self.chains = torch, chains
+        dev = chains[0].dev
+        self.s_in, self.s_run, self.s_out = (torch.cuda.Stream(dev) for _ in range(3))
+        self.sets = []
+        for c in chains:
+            inputs = [c.ids, c.qkv, c.qk, c.attn_out, c.act_in, c.logits[0], c.u]
+            outputs = [c.x, c.res, c.q, c.k, c.v, c.score, c.attn_out, c.act_out, c.top_i, c.top_v, c.picked]
+            self.sets.append({
+                "chain": c, "inputs": inputs, "outputs": outputs,
+                "h_in": [torch.empty(t.shape, dtype=t.dtype, pin_memory=True).copy_(t) for t in inputs],
+                "h_out": [torch.empty(t.shape, dtype=t.dtype, pin_memory=True) for t in outputs],
+                "in_ready": torch.cuda.Event(), "ran": torch.cuda.Event(), "out_done": torch.cuda.Event(),
+            })
+        first = self.sets[0]
+        self.h2d = sum(t.numel() * t.element_size() for t in first["inputs"])
+        self.d2h = sum(t.numel() * t.element_size() for t in first["outputs"])
+        self.n = 0
+
+    def begin(self) -> None:
+        """The three streams start after everything already queued on the current stream."""
+        cur = self.torch.cuda.current_stream()
+        for st in (self.s_in, self.s_run, self.s_out):
+            st.wait_stream(cur)
+        for b in self.sets:
+            b["out_done"].record(self.s_out)
 
     def step(self) -> None:
-        for h, d in zip(self.h_in, self.inputs):
-            d.copy_(h, non_blocking=True)
-        self.c.step()
-        for h, d in zip(self.h_out, self.outputs):
-            h.copy_(d, non_blocking=True)
+        torch, b = self.torch, self.sets[self.n % len(self.sets)]
+        self.n += 1
+        with torch.cuda.stream(self.s_in):
+            self.s_in.wait_event(b["out_done"])  # the previous user of this buffer set has been read out
+            for h, d in zip(b["h_in"], b["inputs"]):
+                d.copy_(h, non_blocking=True)
+            b["in_ready"].record(self.s_in)
+        with torch.cuda.stream(self.s_run):
+            self.s_run.wait_event(b["in_ready"])
+            b["chain"].step()
+            b["ran"].record(self.s_run)
+        with torch.cuda.stream(self.s_out):
+            self.s_out.wait_event(b["ran"])
+            for h, d in zip(b["h_out"], b["outputs"]):
+                h.copy_(d, non_blocking=True)
+            b["out_done"].record(self.s_out)
+
+    def end(self) -> None:
+        """The current stream continues after the three streams have drained."""
+        cur = self.torch.cuda.current_stream()
+        for st in (self.s_in, self.s_run, self.s_out):
+            cur.wait_stream(st)
 
 
 def run_ours(args) -> dict:
@@ -488,16 +527,20 @@ def run_ours(args) -> dict:
     ms_per_step = total_ms / K
 
     # end to end from host buffers, smaller batch (rows/s is size-normalised)
-    e2e_chain = GpuChain(args.e2e_tokens, device, seed=2000 + rank, topk_buffers=1)
-    hd = HostDrivenChain(e2e_chain)
+    e2e_chains = [GpuChain(args.e2e_tokens, device, seed=2000 + 10 * rank + i, topk_buffers=1) for i in range(2)]
+    hd = HostDrivenChain(e2e_chains)
     e2e_steps = max(3, min(K, args.e2e_steps))
+    hd.begin()
     for _ in range(3):
         hd.step()
+    hd.end()
     barrier()
     s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s.record()
+    hd.begin()
     for _ in range(e2e_steps):
         hd.step()
+    hd.end()
     e.record()
     barrier()
     t2 = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=device)
@@ -554,7 +597,7 @@ def run_ours(args) -> dict:
         "device_status": status,
     }
     if world == 1 and not args.no_next_rows:
-        del chain, e2e_chain, hd
+        del chain, e2e_chains, hd
         torch.cuda.empty_cache()
         out["next_rows"] = NextRows(tokens, device).measure()
     if world == 1 and not args.no_cpu_baseline:
@@ -625,7 +668,7 @@ def main() -> int:
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--tokens", type=int, default=65536, help="tokens per GPU per step (multiple of 512)")
     ap.add_argument("--e2e-tokens", type=int, default=8192, help="tokens per step of the host-driven leg")
-    ap.add_argument("--e2e-steps", type=int, default=10)
+    ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-tokens", type=int, default=4096, help="tokens per step of the CPU chain sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-next-rows", action="store_true",
