@@ -47,9 +47,9 @@ KERNELS = ["input_embedding", "rmsnorm", "qkv_bias_rope_transpose", "concat_kv",
 LAUNCHES_PER_STEP = 9  # one per kernel, two for top-K (slice round + merge round)
 # DRAM traffic of the roofline kernel (SiLU*up) from the ncu capture summarised in
 # profiles/silu_mul_16384tok.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch at 16,384
-# tokens (1,036.1 MB) over that launch's algorithmic bytes (1,082.1 MB).  The kernel is a flat
+# tokens (1,037.6 MB) over that launch's algorithmic bytes (1,082.1 MB).  The kernel is a flat
 # streaming pass, so traffic grows in proportion to the rows; a full-size launch is scaled by it.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1036.1 / 1082.13
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1037.6 / 1082.13
 
 
 def algorithmic_bytes(tokens: int, topk_rows: int) -> dict:
