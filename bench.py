@@ -44,7 +44,7 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 KERNELS = ["input_embedding", "rmsnorm", "qkv_bias_rope_transpose", "concat_kv", "scale_mask_softmax",
            "add_residual_rmsnorm", "silu_mul", "topk_sampling"]
-LAUNCHES_PER_STEP = 9  # one per kernel, two for top-K (slice round + merge round)
+LAUNCHES_PER_STEP = 8  # one per kernel (at 256 rows top-K runs one slice per row and samples in the same launch)
 # DRAM traffic of the roofline kernel (SiLU*up) from the ncu capture summarised in
 # profiles/silu_mul_16384tok.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch at 16,384
 # tokens (1,037.6 MB) over that launch's algorithmic bytes (1,082.1 MB).  The kernel is a flat

@@ -254,11 +254,46 @@ __device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int
 // tile t is being thresholded and ranked; the registers are filled from shared memory.  Needs
 // the vector-load conditions (16-byte aligned rows, slice length a multiple of the vector).
 // Without TMA the tile is loaded straight into registers.
+// exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.
+// One warp: lanes evaluate the exponentials, lane 0 accumulates sequentially.
+template <typename T>
+__device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, int K, float u,
+                                           float temperature, float* p_smem, int32_t* out) {
+    const int lane = threadIdx.x & 31;
+    const float v0 = to_float<T>(vals[0]);
+    for (int i = lane; i < K; i += 32)
+        p_smem[i] = ids[i] < 0 ? 0.f : expf((to_float<T>(vals[i]) - v0) / temperature);
+    __syncwarp();
+    if (lane == 0) {
+        float total = 0.f;
+        int last = -1;
+        for (int i = 0; i < K; ++i) {
+            if (ids[i] >= 0) {
+                total += p_smem[i];
+                last = i;
+            }
+        }
+        const float target = u * total;
+        float cum = 0.f;
+        int pick = last;
+        for (int i = 0; i < K; ++i) {
+            if (ids[i] < 0) continue;
+            cum += p_smem[i];
+            if (cum >= target) {
+                pick = i;
+                break;
+            }
+        }
+        *out = pick >= 0 ? ids[pick] : -1;
+    }
+}
+
 template <typename T, int MIN_BLOCKS, bool TMA>
 __global__ void __launch_bounds__(kTopkThreads, MIN_BLOCKS)
 topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int slices, int K,
                   int32_t* __restrict__ out_ids_base, T* __restrict__ out_vals_base, int out_lists,
-                  int32_t index_offset, int vec_loads, unsigned* __restrict__ status) {
+                  int32_t index_offset, int vec_loads, unsigned* __restrict__ status,
+                  const float* __restrict__ uniform, float temperature, int32_t* __restrict__ sampled_ids) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int kVecs = kElemsPerThread / E;
     extern __shared__ __align__(128) unsigned char stage_raw[];  // TMA: [2][kTileElems * sizeof(T)]
@@ -423,39 +458,13 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             out_vals[s] = neg_inf<T>();
         }
     }
-}
-
-// exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.
-// One warp: lanes evaluate the exponentials, lane 0 accumulates sequentially.
-template <typename T>
-__device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, int K, float u,
-                                           float temperature, float* p_smem, int32_t* out) {
-    const int lane = threadIdx.x & 31;
-    const float v0 = to_float<T>(vals[0]);
-    for (int i = lane; i < K; i += 32)
-        p_smem[i] = ids[i] < 0 ? 0.f : expf((to_float<T>(vals[i]) - v0) / temperature);
-    __syncwarp();
-    if (lane == 0) {
-        float total = 0.f;
-        int last = -1;
-        for (int i = 0; i < K; ++i) {
-            if (ids[i] >= 0) {
-                total += p_smem[i];
-                last = i;
-            }
-        }
-        const float target = u * total;
-        float cum = 0.f;
-        int pick = last;
-        for (int i = 0; i < K; ++i) {
-            if (ids[i] < 0) continue;
-            cum += p_smem[i];
-            if (cum >= target) {
-                pick = i;
-                break;
-            }
-        }
-        *out = pick >= 0 ? ids[pick] : -1;
+    // With one slice per row the list just written is the final one: sample from it here
+    // instead of in a launch of its own (uniform is NULL whenever there are several slices).
+    if (uniform != nullptr) {
+        __syncthreads();  // the list written above is visible to warp 0
+        if (tid < 32)
+            sample_row<T>(out_ids, out_vals, K, uniform[row], temperature, reinterpret_cast<float*>(hist),
+                          sampled_ids + row);
     }
 }
 
@@ -627,14 +636,12 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
         // The slice kernel's sorted list is already the answer.
         kernel<<<static_cast<int>(rows), kTopkThreads, smem, st>>>(probs, vocab, static_cast<int>(slice_len), 1, K,
                                                                    final_ids, final_vals, 1, index_offset, vec_loads,
-                                                                   status);
-        if (int rc = check_launch("topk_slice_kernel")) return rc;
-        if (uniform == nullptr) return ISPORE_OK;
-        return sampling_dispatch<T>(final_ids, final_vals, uniform, sampled_ids, rows, K, temperature, st);
+                                                                   status, uniform, temperature, sampled_ids);
+        return check_launch("topk_slice_kernel");
     }
     kernel<<<static_cast<int>(rows * slices), kTopkThreads, smem, st>>>(
         probs, vocab, static_cast<int>(slice_len), static_cast<int>(slices), K, scratch_ids, scratch_vals,
-        scratch_slices, index_offset, vec_loads, status);
+        scratch_slices, index_offset, vec_loads, status, nullptr, 1.0f, nullptr);
     if (int rc = check_launch("topk_slice_kernel")) return rc;
     return merge_dispatch<T>(scratch_ids, scratch_vals, rows, static_cast<int32_t>(slices), scratch_slices, K,
                              final_ids, final_vals, uniform, temperature, sampled_ids, st);
