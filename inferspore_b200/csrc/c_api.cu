@@ -54,7 +54,7 @@ unsigned* device_status_ptr() {
 }
 
 #ifdef ISPORE_TUNING
-static int g_tune[kTuneKeys] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1};
+static int g_tune[kTuneKeys] = {-1, -1, -1, -1, -1, -1, -1, -1, -1, -1, -1};
 int tune(int key, int dflt) { return (key >= 0 && key < kTuneKeys && g_tune[key] >= 0) ? g_tune[key] : dflt; }
 #endif
 

@@ -24,7 +24,7 @@ int resident_ctas(const void* kernel, int threads, size_t dynamic_smem);
 // Launch-shape experiments: a build with -DISPORE_TUNING exports ispore_tune(key, value)
 // and dispatchers consult tune(key, default); the shipped build compiles this to the default.
 enum TuneKey { kTuneRmsnorm = 0, kTuneSoftmax, kTuneAct, kTuneEmbedding, kTuneQkv, kTuneConcat, kTuneTopk,
-               kTuneMhaChunk, kTuneMhaCtasPerSm, kTuneMhaGroup, kTuneKeys };
+               kTuneMhaChunk, kTuneMhaCtasPerSm, kTuneMhaGroup, kTuneMhaStaged, kTuneKeys };
 #ifdef ISPORE_TUNING
 int tune(int key, int dflt);
 #else

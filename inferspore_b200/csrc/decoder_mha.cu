@@ -19,16 +19,23 @@
 //     for one sequence; here the stride is (heads + 2*kv_heads)*d, the tensor's own layout;
 //   * fp16 products are accumulated in fp32 (the reference multiplies in half, :337).
 //
-// Work split: a CTA owns one (b, kv head), GT of the q heads that share it, and one chunk of the
-// positions (flash-decoding style split so that small batches still fill 148 SMs); the cache
-// rows of the chunk are read once for all GT heads.  With more than one chunk per (b, head) the
-// CTAs leave (max, sum, unnormalised output) in a workspace and a second kernel combines them.
+// Work split: a CTA owns one (b, kv head), up to four of the q heads that share it, and one chunk
+// of the positions (flash-decoding style split so that small batches still fill 148 SMs); the
+// cache rows of the chunk are read once for all heads of the group.  The rows reach the CTA
+// through a three-deep ring of 16 KB shared-memory tiles filled by TMA bulk copies (K tiles, then
+// V tiles, issued three ahead).  With several q heads on half-precision rows of 128 the q.K
+// products run on the tensor cores (mma m16n8k16, a cache tile as the A operand without any
+// shuffling); otherwise 16 lanes share a row and a halving butterfly sums the partial products.
+// With more than one chunk per (b, head) the CTAs leave (max, sum, unnormalised output) in a
+// workspace and a second kernel combines them.
 #include <float.h>
 
 #include <algorithm>
 #include <cstdint>
+#include <type_traits>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace ispore {
 namespace {
@@ -110,21 +117,52 @@ struct GroupReduce<N, 0> {
     static __device__ __forceinline__ void run(float (&)[NMAX], int, int&) {}
 };
 
+// D += A * B for one m16n8k16 tile: A 16x16 row-major fp16 (four registers of two halves), B 16x8
+// column-major fp16 (two registers), fp32 accumulators.  Lane (g = lane / 4, t = lane % 4) holds
+//   a0 = A[g][2t, 2t+1], a1 = A[g+8][2t, 2t+1], a2 = A[g][2t+8, 2t+9], a3 = A[g+8][2t+8, 2t+9],
+//   b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g],  d0, d1 = D[g][2t, 2t+1], d2, d3 = D[g+8][2t, 2t+1].
+__device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                            uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&h);
+}
+
 // LPK lanes share one cache row (d = LPK * elements per 128-bit vector); a CTA works on
 // kMhaThreads / LPK rows at a time.  GT q heads of one kv head per CTA.
-template <typename T, int LPK, int GT, int U>
+// STAGED: the cache rows of the chunk do not go from global memory into registers but through a
+// ring of kStages shared-memory tiles of kStageRows rows (16 KB), filled by TMA bulk copies that
+// one thread issues kStages tiles ahead — first all K tiles, then all V tiles, so V is already
+// arriving while the softmax numerators are computed.  The bytes in flight then do not depend on
+// registers or on how many CTAs fit, which is what the wider head groups (more registers, fewer
+// CTAs per SM) need to reach the memory roofline.
+constexpr int kStages = 3;
+
+template <typename T, int LPK, int GT, int U, bool STAGED>
 __global__ void __launch_bounds__(kMhaThreads)
-decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
+decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __restrict__ status) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int D = LPK * E;
     constexpr int KPI = kMhaThreads / LPK;  // cache rows per CTA iteration
     constexpr int N = GT * U;               // dot products per thread per iteration (U rows in flight)
+    constexpr int kStageRows = KPI * U;     // rows per pass of the CTA = rows per shared-memory tile
+    constexpr int kStageBytes = kStageRows * D * static_cast<int>(sizeof(T));
+    static_assert(!STAGED || kStageBytes == 16384, "a staged tile is one pass of eight rows per thread");
     __shared__ float q_s[GT][D];
     __shared__ float knew_s[D], vnew_s[D];
     __shared__ float2 cs_s[kMaxRotPairs];
     __shared__ float red_s[kMhaWarps];
     __shared__ float m_s[GT], l_s[GT];
-    extern __shared__ __align__(16) float dyn_s[];  // logits [GT][chunk]; later the output reduction buffer
+    __shared__ __align__(8) uint64_t full[kStages];
+    extern __shared__ __align__(128) unsigned char dyn_raw[];  // [tiles when STAGED][logits / output reduction buffer]
+    unsigned char* const stage_base = dyn_raw;
+    float* const dyn_s = reinterpret_cast<float*>(dyn_raw + (STAGED ? kStages * kStageBytes : 0));
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lk = tid % LPK, ks = tid / LPK;
@@ -139,6 +177,45 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
     const bool has_last = last >= s0 && last < s1;
     const int n = s1 - s0;                        // positions of this chunk
     const int n_cache = (has_last ? last : s1) - s0;  // of which read from the cache
+    const int64_t cache_row0 = static_cast<int64_t>(bkv) * p.max_seq_len;
+
+    // Tiles 0 .. nt-1 are K rows, nt .. 2nt-1 the same rows of V.
+    const int nt = (n_cache + kStageRows - 1) / kStageRows;
+    auto issue_tile = [&](int tile) {
+        const bool is_v = tile >= nt;
+        const int first_row = (is_v ? tile - nt : tile) * kStageRows;
+        const int rows = min(kStageRows, n_cache - first_row);
+        const uint32_t bytes = static_cast<uint32_t>(rows) * D * sizeof(T);
+        const T* src = (is_v ? p.v_cache : p.k_cache) + (cache_row0 + s0 + first_row) * D;
+        uint64_t* bar = &full[tile % kStages];
+        tma::mbar_arrive_expect_tx(bar, bytes);
+        tma::load(stage_base + (tile % kStages) * kStageBytes, src, bytes, bar);
+    };
+    if (STAGED && tid == 0) {
+#pragma unroll
+        for (int st = 0; st < kStages; ++st) tma::mbar_init(&full[st], 1);
+        tma::fence_mbar_init();
+        for (int tile = 0; tile < kStages && tile < 2 * nt; ++tile) issue_tile(tile);
+    }
+    // Waits for tile `tile`; false when the copy did not land in time (reported at release).
+    auto acquire_tile = [&](int tile) -> bool {
+        return !STAGED || tma::mbar_wait(&full[tile % kStages], (tile / kStages) & 1);
+    };
+    // Every thread is done with tile `tile`: its stage is refilled with tile + kStages.  Returns
+    // false (for the whole CTA) when a copy was lost; the caller leaves the kernel.
+    auto release_tile = [&](int tile, bool landed) -> bool {
+        if (!STAGED) return true;
+        if (__syncthreads_or(!landed)) {
+            if (tid == 0) {
+                atomicOr(status, ISPORE_DEV_TIMEOUT);
+                for (int t2 = tile; t2 < tile + kStages && t2 < 2 * nt; ++t2)  // once more for the copies in flight
+                    tma::mbar_wait(&full[t2 % kStages], (t2 / kStages) & 1);
+            }
+            return false;
+        }
+        if (tid == 0 && tile + kStages < 2 * nt) issue_tile(tile + kStages);
+        return true;
+    };
 
     // ---- the new token: bias, RoPE, rounding through T -------------------------------------------
     for (int i = tid; i < p.rot_pairs; i += kMhaThreads) {
@@ -177,7 +254,6 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
         }
     }
     __syncthreads();
-    const int64_t cache_row0 = static_cast<int64_t>(bkv) * p.max_seq_len;
     if (has_last && hg == 0) {  // one writer per (b, kv head)
         T* kd = p.k_cache + (cache_row0 + last) * D;
         T* vd = p.v_cache + (cache_row0 + last) * D;
@@ -189,20 +265,84 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
 
     // ---- logits of the chunk ------------------------------------------------------------------------
     float* logits = dyn_s;  // [GT][chunk]
-    {
+    // Several q heads on half-precision rows of 128: the dot products go through the tensor cores.
+    // A warp takes 16 cache rows as the A tile; the 16-byte chunk a lane loads from rows g and
+    // g + 8 already is its A fragment for two k-steps, because the order in which the 128
+    // elements of a row are visited is free as long as q is visited in the same order:
+    // k-slot (2t, 2t+1) of step (j, s) stands for elements 8(t+4j) + 4s + (0, 1), slot
+    // (2t+8, 2t+9) for elements 8(t+4j) + 4s + (2, 3).  q (already rounded to half) is the B
+    // tile, one head per column; columns GT..7 are zero.
+    constexpr bool kMmaQK = std::is_same<T, __half>::value && LPK == 16 && GT >= 2;
+    if constexpr (kMmaQK) {
+        const int g = lane >> 2, t = lane & 3;
+        uint32_t bq[4][2][2];  // [j][s][low / high k half]
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+#pragma unroll
+            for (int sft = 0; sft < 2; ++sft) {
+                const int d0 = 8 * (t + 4 * j) + 4 * sft;
+                const float* qrow = q_s[g < GT ? g : 0];
+                bq[j][sft][0] = g < GT ? pack_half2(qrow[d0], qrow[d0 + 1]) : 0u;
+                bq[j][sft][1] = g < GT ? pack_half2(qrow[d0 + 2], qrow[d0 + 3]) : 0u;
+            }
+        const uint4* kbase = reinterpret_cast<const uint4*>(p.k_cache) + (cache_row0 + s0) * LPK;
+        static_assert(!STAGED || kStageRows == kMhaWarps * 16, "one staged tile is 16 rows per warp");
+        constexpr int kRowsPerIter = kMhaWarps * 16;
+        for (int tile_row = 0, tile = 0; tile_row < n_cache; tile_row += kRowsPerIter, ++tile) {
+            const bool landed = acquire_tile(tile);
+            const int l0 = warp * 16 + g, l1 = l0 + 8;  // rows inside the tile
+            const int r0 = tile_row + l0, r1 = tile_row + l1;
+            const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + (tile % kStages) * kStageBytes);
+            uint4 a_lo[4], a_hi[4];  // rows g and g + 8 of this warp's 16, chunks t + 4j
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (STAGED) {
+                    a_lo[j] = r0 < n_cache ? stage_v[l0 * LPK + t + 4 * j] : make_uint4(0, 0, 0, 0);
+                    a_hi[j] = r1 < n_cache ? stage_v[l1 * LPK + t + 4 * j] : make_uint4(0, 0, 0, 0);
+                } else {
+                    a_lo[j] = r0 < n_cache ? ld_stream(kbase + static_cast<int64_t>(r0) * LPK + t + 4 * j) : make_uint4(0, 0, 0, 0);
+                    a_hi[j] = r1 < n_cache ? ld_stream(kbase + static_cast<int64_t>(r1) * LPK + t + 4 * j) : make_uint4(0, 0, 0, 0);
+                }
+            }
+            if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                mma_16x8x16(acc, a_lo[j].x, a_hi[j].x, a_lo[j].y, a_hi[j].y, bq[j][0][0], bq[j][0][1]);
+                mma_16x8x16(acc, a_lo[j].z, a_hi[j].z, a_lo[j].w, a_hi[j].w, bq[j][1][0], bq[j][1][1]);
+            }
+            // acc[0], acc[1]: row g, heads 2t, 2t+1; acc[2], acc[3]: row g + 8
+            if (2 * t < GT) {
+                if (r0 < n_cache) {
+                    logits[(2 * t) * p.chunk + r0] = acc[0] * p.scale;
+                    if (2 * t + 1 < GT) logits[(2 * t + 1) * p.chunk + r0] = acc[1] * p.scale;
+                }
+                if (r1 < n_cache) {
+                    logits[(2 * t) * p.chunk + r1] = acc[2] * p.scale;
+                    if (2 * t + 1 < GT) logits[(2 * t + 1) * p.chunk + r1] = acc[3] * p.scale;
+                }
+            }
+        }
+    } else {
         float qreg[GT][E];
 #pragma unroll
         for (int g = 0; g < GT; ++g)
 #pragma unroll
             for (int e = 0; e < E; ++e) qreg[g][e] = q_s[g][lk * E + e];
         const uint4* krows = reinterpret_cast<const uint4*>(p.k_cache) + (cache_row0 + s0) * LPK + lk;
-        for (int base = 0; base < n_cache; base += KPI * U) {
+        for (int base = 0, tile = 0; base < n_cache; base += KPI * U, ++tile) {
+            const bool landed = acquire_tile(tile);
+            const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + (tile % kStages) * kStageBytes);
             uint4 raw[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
                 const int i = base + u * KPI + ks;
-                raw[u] = i < n_cache ? ld_stream(krows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
+                if (STAGED)
+                    raw[u] = i < n_cache ? stage_v[(u * KPI + ks) * LPK + lk] : make_uint4(0, 0, 0, 0);
+                else
+                    raw[u] = i < n_cache ? ld_stream(krows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
             }
+            if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
             float dots[N];  // index g * U + u
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -229,14 +369,14 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
                 }
             }
         }
-        if (has_last && warp == 0) {  // the new token's own logit, from shared memory
+    }
+    if (has_last && warp == 0) {  // the new token's own logit, from shared memory
 #pragma unroll
-            for (int g = 0; g < GT; ++g) {
-                float dot = 0.f;
-                for (int i = lane; i < D; i += 32) dot = fmaf(q_s[g][i], knew_s[i], dot);
-                dot = warp_sum(dot);
-                if (lane == 0) logits[g * p.chunk + (last - s0)] = dot * p.scale;
-            }
+        for (int g = 0; g < GT; ++g) {
+            float dot = 0.f;
+            for (int i = lane; i < D; i += 32) dot = fmaf(q_s[g][i], knew_s[i], dot);
+            dot = warp_sum(dot);
+            if (lane == 0) logits[g * p.chunk + (last - s0)] = dot * p.scale;
         }
     }
     __syncthreads();
@@ -269,13 +409,19 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles) {
 #pragma unroll
         for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
     const uint4* vrows = reinterpret_cast<const uint4*>(p.v_cache) + (cache_row0 + s0) * LPK + lk;
-    for (int base = 0; base < n_cache; base += KPI * U) {
+    for (int base = 0, tile = nt; base < n_cache; base += KPI * U, ++tile) {
+        const bool landed = acquire_tile(tile);
+        const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + (tile % kStages) * kStageBytes);
         uint4 raw[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int i = base + u * KPI + ks;
-            raw[u] = i < n_cache ? ld_stream(vrows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
+            if (STAGED)
+                raw[u] = i < n_cache ? stage_v[(u * KPI + ks) * LPK + lk] : make_uint4(0, 0, 0, 0);
+            else
+                raw[u] = i < n_cache ? ld_stream(vrows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
         }
+        if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
 #pragma unroll
         for (int u = 0; u < U; ++u) {
             const int i = base + u * KPI + ks;
@@ -368,13 +514,12 @@ void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, b
     const int64_t base_ctas = batch * kv_heads * (heads / kv_heads / gt);
     int64_t want = 1;
     if (have_workspace) {
-        // Many more CTAs than fit at once (the tail of the last wave then costs little), each
-        // still reading enough rows to pay for preparing q: 512 positions per CTA when that
-        // already gives 8 CTAs per SM; otherwise as many chunks as reach 16 per SM, down to 128
-        // positions each.
+        // The tile ring keeps every CTA's reads in flight on its own, so a CTA takes a long chunk
+        // (1024 positions) whenever that still gives every SM one; smaller batches get as many
+        // chunks as reach two CTAs per SM, down to 128 positions each.
         const int sms = sm_count() > 0 ? sm_count() : 148;
-        const int64_t enough = static_cast<int64_t>(tune(kTuneMhaCtasPerSm, 8)) * sms;
-        const int64_t big = tune(kTuneMhaChunk, 512), small = 128;
+        const int64_t enough = static_cast<int64_t>(tune(kTuneMhaCtasPerSm, 1)) * sms;
+        const int64_t big = tune(kTuneMhaChunk, 1024), small = 128;
         want = ceil_div(step, big);
         if (base_ctas * want < enough) want = std::min(ceil_div(2 * enough, base_ctas), std::max<int64_t>(1, step / small));
         want = std::max<int64_t>(want, ceil_div(step, static_cast<int64_t>(kChunkFloatsDefault / gt)));
@@ -385,20 +530,22 @@ void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, b
     *splits = static_cast<int>(ceil_div(step, c));
 }
 
-template <typename T, int LPK, int GT, int U>
+template <typename T, int LPK, int GT, int U, bool STAGED>
 int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, cudaStream_t st) {
     constexpr int D = LPK * VecTraits<T>::kElems;
-    auto kernel = decoder_mha_kernel<T, LPK, GT, U>;
+    auto kernel = decoder_mha_kernel<T, LPK, GT, U, STAGED>;
     const size_t floats = std::max<size_t>(static_cast<size_t>(GT) * p.chunk, static_cast<size_t>(kMhaWarps) * GT * D);
-    const size_t smem = floats * sizeof(float);
+    const size_t smem = floats * sizeof(float) + (STAGED ? static_cast<size_t>(kStages) * 16384 : 0);
     if (smem > 40 * 1024) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
             cudaGetLastError();
             return fail(ISPORE_ELAUNCH, "decoder_masked_mha: %zu bytes of shared memory refused", smem);
         }
     }
+    unsigned* status = device_status_ptr();
+    if (status == nullptr) return fail(ISPORE_ELAUNCH, "decoder_masked_mha: no device status word");
     dim3 grid(static_cast<unsigned>(batch * p.kv_heads * p.head_groups), static_cast<unsigned>(p.splits));
-    kernel<<<grid, kMhaThreads, smem, st>>>(p, angles);
+    kernel<<<grid, kMhaThreads, smem, st>>>(p, angles, status);
     int rc = check_launch("decoder_mha_kernel");
     if (rc != ISPORE_OK || p.splits == 1) return rc;
     decoder_mha_combine_kernel<T><<<static_cast<unsigned>(batch * p.heads), 128, 0, st>>>(p.out, p.workspace, p.splits, D);
@@ -407,10 +554,19 @@ int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, c
 
 template <typename T, int LPK>
 int launch_mha_group(const MhaParams<T>& p, const RopeAngles& angles, int gt, int64_t batch, cudaStream_t st) {
+#ifdef ISPORE_TUNING
+    if (tune(kTuneMhaStaged, 1) == 0) {  // the register-staged variant, kept for comparison
+        switch (gt) {
+            case 4: return launch_mha<T, LPK, 4, 8, false>(p, angles, batch, st);
+            case 2: return launch_mha<T, LPK, 2, 8, false>(p, angles, batch, st);
+            default: return launch_mha<T, LPK, 1, 8, false>(p, angles, batch, st);
+        }
+    }
+#endif
     switch (gt) {
-        case 4: return launch_mha<T, LPK, 4, 4>(p, angles, batch, st);
-        case 2: return launch_mha<T, LPK, 2, 8>(p, angles, batch, st);
-        default: return launch_mha<T, LPK, 1, 8>(p, angles, batch, st);
+        case 4: return launch_mha<T, LPK, 4, 8, true>(p, angles, batch, st);
+        case 2: return launch_mha<T, LPK, 2, 8, true>(p, angles, batch, st);
+        default: return launch_mha<T, LPK, 1, 8, true>(p, angles, batch, st);
     }
 }
 
