@@ -1,7 +1,7 @@
 """Builds the checker side: the C oracle and, when the reference tree is present,
 the reference's own code.
 
-    python oracle/build.py [--ref-root /root/reference] [--force]
+    python oracle/build.py [--ref-root <reference checkout>] [--force]
 
 TEST INFRASTRUCTURE ONLY — nothing under inferspore_b200/ imports this.
 
@@ -11,7 +11,7 @@ TEST INFRASTRUCTURE ONLY — nothing under inferspore_b200/ imports this.
       from where they lie in the reference tree, -> oracle/_ref/libref_*.so.
       These export the reference's CPU functions (from its unit tests) and its
       GPU launchers through a C ABI.
-   b. the reference's six hot-path unit tests, unmodified, compiled against
+   b. eleven of the reference's unit tests (DROPIN_TESTS), unmodified, compiled against
       inferspore_b200/compat (the drop-in headers) and linked to
       libispore_kernels.so -> oracle/_ref/dropin/test_*.  They are the
       acceptance check that the reference's callers build and run against the
