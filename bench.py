@@ -408,6 +408,49 @@ class NextRows:
         t.cuda.synchronize()
         return s.elapsed_time(e) / steps, nbytes, workload
 
+    def decode_small_kernels(self, iters: int = 50) -> dict:
+        """The launch-bound kernels of one decode step at `decode_batch` sequences (plain RMSNorm,
+        residual add + RMSNorm, SiLU*up, top-K + sampling): time per step launched one by one and
+        replayed from a CUDA graph (the C ABI is capturable after one warm-up call)."""
+        t, o, h, dev, bs = self.torch, self.ops, self.torch.float16, self.dev, self.decode_batch
+        x, res = self._randn(bs, HIDDEN), self._randn(bs, HIDDEN)
+        gamma = (t.rand(HIDDEN, generator=self.g, device=dev) + 0.5).to(h)
+        act, act_out = self._randn(bs, 2, INTER), t.empty((bs, INTER), dtype=h, device=dev)
+        logits = (t.randn(bs, VOCAB, generator=self.g, device=dev) * 2.0)
+        u = t.rand(bs, generator=self.g, device=dev)
+        sc_i = t.empty((bs, 8, TOPK_K), dtype=t.int32, device=dev)
+        sc_v = t.empty((bs, 8, TOPK_K), device=dev)
+        top_i, top_v = t.empty((bs, TOPK_K), dtype=t.int32, device=dev), t.empty((bs, TOPK_K), device=dev)
+        picked = t.empty(bs, dtype=t.int32, device=dev)
+
+        def step():
+            o.launchRMSNorm(x, res, gamma, EPS)
+            o.launchFusedAddBiasResidualRMSNorm(res, x, None, gamma, EPS)
+            o.launchAct(act, act_out)
+            o.launchTopKforBeamSearch(logits, sc_i, sc_v, top_i, top_v, 0, u, 1.0, picked)
+
+        def timed(fn):
+            for _ in range(3):
+                fn()
+            t.cuda.synchronize()
+            s, e = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            s.record()
+            for _ in range(iters):
+                fn()
+            e.record()
+            t.cuda.synchronize()
+            return s.elapsed_time(e) / iters * 1e3
+
+        eager_us = timed(step)
+        graph, side = t.cuda.CUDAGraph(), t.cuda.Stream(dev)
+        with t.cuda.stream(side):
+            with t.cuda.graph(graph, stream=side):
+                step()
+        graph_us = timed(graph.replay)
+        return {"eager_us": round(eager_us, 2), "graph_us": round(graph_us, 2), "launches_per_step": 4,
+                "workload": f"{bs} sequences: RMSNorm, residual+RMSNorm [{bs}, {HIDDEN}], SiLU*up [{bs}, {INTER}], "
+                            f"top-K({TOPK_K})+sampling [{bs}, {VOCAB}]"}
+
     def measure(self, steps: int = 20, warmup: int = 3) -> dict:
         peak, _ = measured_peak_gbs()
         out = {}
@@ -417,6 +460,7 @@ class NextRows:
             out[name] = {"ms": round(ms, 5), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4),
                          "bytes": nbytes, "workload": workload}
             self.torch.cuda.empty_cache()
+        out["decode_small_kernels"] = self.decode_small_kernels()
         return out
 
 

@@ -779,3 +779,62 @@ def test_decoder_masked_mha_rejects_bad_shapes(ops):
         ops.launchDecoderMaskedMHA(qkv, None, 0, kc, kc.clone(), None, 9, out, 0, 10000.0)
     with pytest.raises(Exception):  # layer out of range
         ops.launchDecoderMaskedMHA(qkv, None, 1, kc, kc.clone(), None, 1, out, 0, 10000.0)
+
+
+# ---- stream capture: a decode step replayed from a CUDA graph ------------------------------------------
+
+def test_decode_step_in_a_cuda_graph(ops, rng):
+    """Every launcher of a decode step is captured into one CUDA graph (after one eager warm-up
+    call, which performs the per-kernel attribute calls) and replayed on fresh inputs; the replay
+    must reproduce the eager results bit for bit."""
+    batch, heads, d, hidden, inter, step, max_seq, K = 8, 8, 128, 1024, 2816, 200, 256, 20
+    g = torch.Generator(device="cuda:0")
+    g.manual_seed(3)
+    rnd = lambda *s, sc=1.0: (torch.randn(*s, generator=g, device="cuda:0") * sc).half()
+    x0, gamma = rnd(batch, hidden), (torch.rand(hidden, generator=g, device="cuda:0") + 0.5).half()
+    qkv0 = rnd(batch, 3 * heads, d)
+    kc0, vc0 = rnd(1, batch, heads, max_seq, d), rnd(1, batch, heads, max_seq, d)
+    act0 = rnd(batch, 2, inter)
+    logits0 = rnd(batch, 32000, sc=2.0).float()
+    u = torch.rand(batch, generator=g, device="cuda:0")
+    # working buffers the graph owns
+    x, res, qkv, kc, vc, act = (t.clone() for t in (x0, x0, qkv0, kc0, vc0, act0))
+    attn = torch.empty((batch, heads, d), dtype=torch.float16, device="cuda:0")
+    act_out = torch.empty((batch, inter), dtype=torch.float16, device="cuda:0")
+    ws = torch.empty(max(4, ops.decoderMaskedMHAWorkspaceBytes(batch, heads, heads, d, step)), dtype=torch.uint8,
+                     device="cuda:0")
+    top_i = torch.empty((batch, K), dtype=torch.int32, device="cuda:0")
+    top_v = torch.empty((batch, K), device="cuda:0")
+    sc_i = torch.empty((batch, 8, K), dtype=torch.int32, device="cuda:0")
+    sc_v = torch.empty((batch, 8, K), device="cuda:0")
+    picked = torch.empty(batch, dtype=torch.int32, device="cuda:0")
+
+    def reset():
+        for dst, src in ((x, x0), (qkv, qkv0), (kc, kc0), (vc, vc0), (act, act0)):
+            dst.copy_(src)
+
+    def decode_step():
+        ops.launchRMSNorm(x, res, gamma, 1e-6)
+        ops.launchDecoderMaskedMHA(qkv, None, 0, kc, vc, None, step, attn, d, 10000.0, ws)
+        ops.launchFusedAddBiasResidualRMSNorm(res, x, None, gamma, 1e-6)
+        ops.launchAct(act, act_out)
+        ops.launchTopKforBeamSearch(logits0, sc_i, sc_v, top_i, top_v, 0, u, 1.0, picked)
+
+    outputs = lambda: [t.clone() for t in (x, res, kc, vc, attn, act_out, top_i, top_v, picked)]
+    reset()
+    decode_step()
+    torch.cuda.synchronize()
+    eager = outputs()
+    graph = torch.cuda.CUDAGraph()
+    side = torch.cuda.Stream()
+    reset()
+    torch.cuda.synchronize()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            decode_step()
+    for _ in range(2):
+        reset()
+        graph.replay()
+        torch.cuda.synchronize()
+        for got, want in zip(outputs(), eager):
+            assert torch.equal(got, want)
