@@ -592,6 +592,33 @@ def run_ours(args) -> dict:
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     e2e_ms_per_step = float(t2.item()) / e2e_steps
 
+    # The path's one real exchange, timed on its own when there are ranks to exchange with: top-K
+    # over logits whose vocabulary axis is split across the ranks (local top-K with global ids, one
+    # NCCL all-gather of the candidate lists, merge + sampling on every rank).
+    sharded_topk = None
+    if world > 1:
+        from inferspore_b200.sharding import vocab_shard, vocab_sharded_topk
+
+        shard = vocab_shard(VOCAB, world, rank)
+        g = torch.Generator(device=device)
+        g.manual_seed(4000)  # the same logits on every rank; each keeps its own columns
+        full = torch.randn(TOPK_ROWS, VOCAB, generator=g, device=device) * 2.0
+        local = full[:, shard.start:shard.stop].contiguous()
+        uni = torch.rand(TOPK_ROWS, generator=g, device=device)
+        for _ in range(3):
+            vocab_sharded_topk(local, shard, TOPK_K, uniform=uni)
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(20):
+            vocab_sharded_topk(local, shard, TOPK_K, uniform=uni)
+        e.record()
+        barrier()
+        t3 = torch.tensor([s.elapsed_time(e) / 20], dtype=torch.float64, device=device)
+        dist.all_reduce(t3, op=dist.ReduceOp.MAX)
+        sharded_topk = {"ms": round(float(t3.item()), 4), "rows": TOPK_ROWS, "vocab_per_rank": shard.size,
+                        "gathered_bytes_per_rank": TOPK_ROWS * TOPK_K * 8 * world}
+
     from inferspore_b200 import capi
 
     status = capi.device_status(clear=True)
@@ -640,6 +667,8 @@ def run_ours(args) -> dict:
         "gpu_launches": K * LAUNCHES_PER_STEP,
         "device_status": status,
     }
+    if sharded_topk is not None:
+        out["vocab_sharded_topk"] = sharded_topk
     if world == 1 and not args.no_next_rows:
         del chain, e2e_chains, hd
         torch.cuda.empty_cache()

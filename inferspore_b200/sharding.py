@@ -72,25 +72,60 @@ def gather_candidates(local_ids: torch.Tensor, local_vals: torch.Tensor,
             vals.view(world, rows, K).permute(1, 0, 2).contiguous())
 
 
+class VocabShardedTopK:
+    """Top-K (and optional sampling) over logits whose vocab axis is split across ranks, with
+    every buffer allocated once: local top-K with global ids, ONE all-gather of the packed
+    (ids | values) candidate lists, merge (+ sampling) on every rank."""
+
+    def __init__(self, rows: int, K: int, dtype: torch.dtype, device: torch.device,
+                 group: Optional[dist.ProcessGroup] = None, slices: int = 8):
+        self.rows, self.K, self.group = rows, K, group
+        self.world = dist.get_world_size(group)
+        esize = torch.empty((), dtype=dtype).element_size()
+        ids_bytes, vals_bytes = rows * K * 4, rows * K * esize
+        self.packed = torch.empty(ids_bytes + vals_bytes, dtype=torch.uint8, device=device)
+        self.loc_i = self.packed[:ids_bytes].view(torch.int32).view(rows, K)
+        self.loc_v = self.packed[ids_bytes:].view(dtype).view(rows, K)
+        self.gathered = torch.empty((self.world, ids_bytes + vals_bytes), dtype=torch.uint8, device=device)
+        self.all_i = self.gathered[:, :ids_bytes].view(torch.int32).view(self.world, rows, K)  # strided views
+        self.all_v = self.gathered[:, ids_bytes:].view(dtype).view(self.world, rows, K)
+        self.cand_i = torch.empty((rows, self.world, K), dtype=torch.int32, device=device)
+        self.cand_v = torch.empty((rows, self.world, K), dtype=dtype, device=device)
+        self.sc_i = torch.empty((rows, slices, K), dtype=torch.int32, device=device)
+        self.sc_v = torch.empty((rows, slices, K), dtype=dtype, device=device)
+        self.out_i = torch.empty((rows, K), dtype=torch.int32, device=device)
+        self.out_v = torch.empty((rows, K), dtype=dtype, device=device)
+        self.picked = torch.empty((rows,), dtype=torch.int32, device=device)
+
+    def __call__(self, local_logits: torch.Tensor, shard: Shard, uniform: Optional[torch.Tensor] = None,
+                 temperature: float = 1.0):
+        from . import ops
+
+        if local_logits.shape != (self.rows, shard.size):
+            raise ValueError("local logits must be [rows, shard.size]")
+        ops.launchTopKforBeamSearch(local_logits, self.sc_i, self.sc_v, self.loc_i, self.loc_v,
+                                    index_offset=shard.start)
+        dist.all_gather_into_tensor(self.gathered.view(-1), self.packed, group=self.group)
+        self.cand_i.copy_(self.all_i.permute(1, 0, 2))  # rank-major -> the merge kernel's [rows, lists, K]
+        self.cand_v.copy_(self.all_v.permute(1, 0, 2))
+        picked = self.picked if uniform is not None else None
+        ops.launchTopKMerge(self.cand_i, self.cand_v, self.out_i, self.out_v, uniform, temperature, picked)
+        return self.out_i, self.out_v, picked
+
+
+_SHARDED_TOPK_CACHE: dict = {}
+
+
 def vocab_sharded_topk(local_logits: torch.Tensor, shard: Shard, K: int,
                        uniform: Optional[torch.Tensor] = None, temperature: float = 1.0,
                        group: Optional[dist.ProcessGroup] = None):
     """Top-K (and optional sampling) over logits whose vocab axis is split across ranks.
     local_logits [rows, shard.size] on this rank's GPU.  Returns (ids [rows, K], vals [rows, K],
-    sampled [rows] or None), identical on every rank."""
-    from . import ops
-
-    rows = local_logits.shape[0]
-    dev, dt = local_logits.device, local_logits.dtype
-    slices = 8
-    sc_i = torch.empty((rows, slices, K), dtype=torch.int32, device=dev)
-    sc_v = torch.empty((rows, slices, K), dtype=dt, device=dev)
-    loc_i = torch.empty((rows, K), dtype=torch.int32, device=dev)
-    loc_v = torch.empty((rows, K), dtype=dt, device=dev)
-    ops.launchTopKforBeamSearch(local_logits, sc_i, sc_v, loc_i, loc_v, index_offset=shard.start)
-    cand_i, cand_v = gather_candidates(loc_i, loc_v, group)
-    out_i = torch.empty((rows, K), dtype=torch.int32, device=dev)
-    out_v = torch.empty((rows, K), dtype=dt, device=dev)
-    picked = torch.empty((rows,), dtype=torch.int32, device=dev) if uniform is not None else None
-    ops.launchTopKMerge(cand_i, cand_v, out_i, out_v, uniform, temperature, picked)
-    return out_i, out_v, picked
+    sampled [rows] or None), identical on every rank; the returned tensors are reused by the next
+    call of the same shape."""
+    key = (local_logits.shape[0], K, local_logits.dtype, local_logits.device, id(group))
+    op = _SHARDED_TOPK_CACHE.get(key)
+    if op is None:
+        op = _SHARDED_TOPK_CACHE[key] = VocabShardedTopK(local_logits.shape[0], K, local_logits.dtype,
+                                                         local_logits.device, group)
+    return op(local_logits, shard, uniform, temperature)
