@@ -382,22 +382,41 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     __syncthreads();
 
     // ---- softmax numerators over the chunk ----------------------------------------------------------
-#pragma unroll
-    for (int g = 0; g < GT; ++g) {
-        float* row = logits + g * p.chunk;
+    if constexpr (GT == kMhaWarps) {
+        // one warp per head: warp reductions only, no block barrier until all heads are done
+        float* row = logits + warp * p.chunk;
         float mx = -FLT_MAX;
-        for (int i = tid; i < n; i += kMhaThreads) mx = fmaxf(mx, row[i]);
-        mx = block_max(mx, red_s);
+        for (int i = lane; i < n; i += 32) mx = fmaxf(mx, row[i]);
+        mx = warp_max(mx);
         float sum = 0.f;
-        for (int i = tid; i < n; i += kMhaThreads) {
+        for (int i = lane; i < n; i += 32) {
             const float e = expf(row[i] - mx);
             row[i] = e;
             sum += e;
         }
-        sum = block_sum(sum, red_s);  // its barriers also publish the numerators
-        if (tid == 0) {
-            m_s[g] = mx;
-            l_s[g] = sum;
+        sum = warp_sum(sum);
+        if (lane == 0) {
+            m_s[warp] = mx;
+            l_s[warp] = sum;
+        }
+    } else {
+#pragma unroll
+        for (int g = 0; g < GT; ++g) {
+            float* row = logits + g * p.chunk;
+            float mx = -FLT_MAX;
+            for (int i = tid; i < n; i += kMhaThreads) mx = fmaxf(mx, row[i]);
+            mx = block_max(mx, red_s);
+            float sum = 0.f;
+            for (int i = tid; i < n; i += kMhaThreads) {
+                const float e = expf(row[i] - mx);
+                row[i] = e;
+                sum += e;
+            }
+            sum = block_sum(sum, red_s);  // its barriers also publish the numerators
+            if (tid == 0) {
+                m_s[g] = mx;
+                l_s[g] = sum;
+            }
         }
     }
     __syncthreads();
