@@ -130,7 +130,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
             } else if (live && (FULL || v < row_vecs)) {
                 unpack(m_raw[i], term[i]);
 #pragma unroll
-                for (int e = 0; e < E; ++e) term[i].v[e] = (1.0f - term[i].v[e]) * neg;
+                for (int e = 0; e < E; ++e) term[i].v[e] = fmaf(term[i].v[e], -neg, neg);  // (1 - mask) * neg in one rounding
             }
         }
 
