@@ -52,7 +52,7 @@ __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
                           const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
                           uint32_t units /* batch*q_len*head_groups */, uint32_t head_groups,
-                          uint32_t heads, uint32_t q_len, int row_vecs, float scale) {
+                          uint32_t heads, uint32_t q_len, int row_vecs, float scale, int q_shift, int hg_shift) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int kGroupsPerCta = THREADS / GROUP;
     constexpr int kWarpsPerGroup = GROUP / 32;
@@ -72,10 +72,23 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
         const uint32_t u = u0 + g;
         const bool live = u < units;  // with several groups per CTA there are no block barriers below
         // q index fastest: neighbouring groups work on neighbouring rows of the same heads.
-        const uint32_t qi = live ? u % q_len : 0;
-        const uint32_t t = live ? u / q_len : 0;
-        const uint32_t hg = t % head_groups;
-        const uint32_t b = t / head_groups;
+        // q_shift / hg_shift: log2 of q_len / head_groups when those are powers of two (the usual
+        // case), else -1: a run-time division costs as much as the arithmetic of two elements.
+        uint32_t qi, t, hg, b;
+        if (q_shift >= 0) {
+            qi = live ? u & (q_len - 1) : 0;
+            t = live ? u >> q_shift : 0;
+        } else {
+            qi = live ? u % q_len : 0;
+            t = live ? u / q_len : 0;
+        }
+        if (hg_shift >= 0) {
+            hg = t & (head_groups - 1);
+            b = t >> hg_shift;
+        } else {
+            hg = t % head_groups;
+            b = t / head_groups;
+        }
         const uint32_t h0 = hg * HG;
         const int nh = FULL ? (live ? HG : 0) : (live ? static_cast<int>(min(static_cast<uint32_t>(HG), heads - h0)) : 0);
 
@@ -255,6 +268,13 @@ struct MaskSource {
     const int32_t* k_lens;
 };
 
+inline int log2_or_minus1(int64_t v) {
+    if (v <= 0 || (v & (v - 1)) != 0) return -1;
+    int s = 0;
+    while ((int64_t{1} << s) < v) ++s;
+    return s;
+}
+
 template <typename T, bool CAUSAL, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS = 1>
 int launch_groups(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch, int64_t heads, int64_t q_len,
                   int row_vecs, float scale, cudaStream_t st) {
@@ -270,7 +290,8 @@ int launch_groups(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch,
     const int grid = static_cast<int>(ctas < (1 << 30) ? ctas : (1 << 30));
     kernel<<<grid, THREADS, 0, st>>>(score, qk, ms.mask, ms.q_lens, ms.k_lens, static_cast<uint32_t>(units),
                                      static_cast<uint32_t>(head_groups), static_cast<uint32_t>(heads),
-                                     static_cast<uint32_t>(q_len), row_vecs, scale);
+                                     static_cast<uint32_t>(q_len), row_vecs, scale, log2_or_minus1(q_len),
+                                     log2_or_minus1(head_groups));
     return check_launch("softmax_head_group_kernel");
 }
 
