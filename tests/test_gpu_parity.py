@@ -840,12 +840,12 @@ def test_decode_step_in_a_cuda_graph(ops, rng):
             assert torch.equal(got, want)
 
 
-def test_softmax_more_sequences_than_a_grid_axis_holds(ops, orc, rng):
-    # batch > 65535: the kernel takes the flat grid instead of the (q, head group, batch) one
+def test_softmax_many_short_sequences(ops, orc, rng):
+    # 70,000 sequences of one 8-key row: more units than any single grid axis but x could index
     batch, heads, q_len, k_len = 70000, 2, 1, 8
     qk = rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32)
     mask = (rng.random((batch, q_len, k_len)) < 0.7).astype(np.float32)
     out = torch.empty(qk.shape, device="cuda:0")
     ops.launchScaleMaskAndSoftmax(dev(qk), dev(mask), out, 0.5)
     want, _ = orc.scale_mask_softmax(qk, mask, np.float32(0.5))
-    assert_close_f32(host(out), want, floor=1e-30, what="softmax, flat grid")
+    assert_close_f32(host(out), want, floor=1e-30, what="softmax, many short sequences")
