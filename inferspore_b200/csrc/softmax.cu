@@ -42,12 +42,15 @@ struct ExpPolicy<__half> {
 // THREADS/GROUP groups.  Each thread keeps VPT 128-bit vectors of a row and the
 // matching slice of the additive mask term.  A group works on HG heads of one
 // (b, q) pair per trip.
-// FULL: every row is exactly VPT*GROUP vectors long and heads is a multiple of HG, so the
-// per-vector and per-head guards (and the branches they cost) disappear.
+// MODE 0 (full): every row is exactly VPT*GROUP vectors long and heads is a multiple of HG, so the
+// per-vector and per-head guards (and the branches they cost) disappear.  MODE 1 (tail): rows are
+// longer than (VPT-1)*GROUP vectors, so only a thread's last vector needs its guard.  MODE 2: any
+// row length and head count.
 // CAUSAL: there is no mask tensor; the 0/1 mask row is derived from q_lens[b] and k_lens[b] with
 // the predicate of the reference's mask builder (src/kernels/build_casual_mask.cu:36), so the
 // result is bit-identical to building the mask first and the [bs, q, k] tensor is never read.
-template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS, bool FULL, bool CAUSAL>
+#define ISPORE_IN_ROW(i, v) (MODE == 0 || (MODE == 1 && (i) < VPT - 1) || (v) < row_vecs)
+template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS, int MODE, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
                           const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
@@ -90,7 +93,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
             b = t / head_groups;
         }
         const uint32_t h0 = hg * HG;
-        const int nh = FULL ? (live ? HG : 0) : (live ? static_cast<int>(min(static_cast<uint32_t>(HG), heads - h0)) : 0);
+        const int nh = MODE != 2 ? (live ? HG : 0) : (live ? static_cast<int>(min(static_cast<uint32_t>(HG), heads - h0)) : 0);
 
         const uint4* mrow = reinterpret_cast<const uint4*>(mask) + (static_cast<int64_t>(b) * q_len + qi) * row_vecs;
         const int64_t row0 = (static_cast<int64_t>(b) * heads + h0) * q_len + qi;  // row of head h0
@@ -111,7 +114,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = gt + i * GROUP;
-                if (live && (FULL || v < row_vecs)) m_raw[i] = ld_keep(mrow + v);
+                if (live && ISPORE_IN_ROW(i, v)) m_raw[i] = ld_keep(mrow + v);
             }
         }
 #pragma unroll
@@ -119,7 +122,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
             for (int i = 0; i < VPT; ++i) {
                 const int v = gt + i * GROUP;
-                if (hh < nh && (FULL || v < row_vecs)) q_raw[hh][i] = ld_stream(qrow0 + hh * head_stride_vecs + v);
+                if (hh < nh && ISPORE_IN_ROW(i, v)) q_raw[hh][i] = ld_stream(qrow0 + hh * head_stride_vecs + v);
             }
         }
         // Additive mask term (1 - mask) * (-10000), prescaled; -inf-like filler beyond the row.
@@ -140,7 +143,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
                     for (int e = 0; e < E; ++e) term[i].v[e] = (k0 + e >= lo && k0 + e <= hi) ? 0.0f : neg;
                 }
-            } else if (live && (FULL || v < row_vecs)) {
+            } else if (live && ISPORE_IN_ROW(i, v)) {
                 unpack(m_raw[i], term[i]);
 #pragma unroll
                 for (int e = 0; e < E; ++e) term[i].v[e] = fmaf(term[i].v[e], -neg, neg);  // (1 - mask) * neg in one rounding
@@ -155,7 +158,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int v = gt + i * GROUP;
-                    if (FULL || v < row_vecs) {
+                    if (ISPORE_IN_ROW(i, v)) {
                         unpack(q_raw[hh][i], z[i]);
 #pragma unroll
                         for (int e = 0; e < E; ++e) {
@@ -175,7 +178,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int v = gt + i * GROUP;
-                    if (FULL || v < row_vecs) {
+                    if (ISPORE_IN_ROW(i, v)) {
 #pragma unroll
                         for (int e = 0; e < E; ++e) {
                             z[i].v[e] = Exp::exp_diff(z[i].v[e], mx);
@@ -195,7 +198,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 #pragma unroll
                 for (int i = 0; i < VPT; ++i) {
                     const int v = gt + i * GROUP;
-                    if (FULL || v < row_vecs) {
+                    if (ISPORE_IN_ROW(i, v)) {
 #pragma unroll
                         for (int e = 0; e < E; ++e) z[i].v[e] *= inv;
                         st_stream(orow0 + hh * head_stride_vecs + v, pack(z[i]));
@@ -206,6 +209,8 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
         }
     }
 }
+
+#undef ISPORE_IN_ROW
 
 // Any k_len / alignment: one CTA per row, three scalar passes (the row is
 // re-read from L2).  Also the path for rows too long for the register kernels.
@@ -259,6 +264,70 @@ softmax_generic_kernel(T* __restrict__ score, const T* __restrict__ qk, const T*
     }
 }
 
+// Rows that cannot be moved as 128-bit vectors (k_len not a multiple of the vector, unaligned
+// views) but fit a CTA's registers: one CTA per row, EPT scalar elements per thread, the row read
+// once and written once.
+template <typename T, int THREADS, int EPT, bool CAUSAL>
+__global__ void __launch_bounds__(THREADS)
+softmax_row_scalar_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
+                          const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
+                          int64_t total_rows, int64_t rows_per_batch, int q_len, int k_len, float scale) {
+    constexpr int kWarps = THREADS / 32;
+    __shared__ float red[2][kWarps];
+    const int tid = threadIdx.x;
+    for (int64_t row = blockIdx.x; row < total_rows; row += gridDim.x) {
+        const int64_t bidx = row / rows_per_batch;
+        const int qi = static_cast<int>((row - bidx * rows_per_batch) % q_len);
+        const T* qrow = qk + row * k_len;
+        const T* mrow = CAUSAL ? nullptr : mask + (bidx * q_len + qi) * k_len;
+        T* orow = score + row * k_len;
+        int lo = 0, hi = -1;
+        if (CAUSAL) {
+            const int qlen = __ldg(q_lens + bidx), klen = __ldg(k_lens + bidx);
+            lo = klen - qlen;
+            hi = qi < qlen ? min(klen - 1, qi + lo) : -1;
+        }
+        float z[EPT];
+        float mx = FLT_MIN;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int i = tid + j * THREADS;
+            if (i < k_len) {
+                const float term = CAUSAL ? ((i >= lo && i <= hi) ? 0.0f : -10000.0f)
+                                          : (1.0f - to_float<T>(mrow[i])) * -10000.0f;
+                z[j] = fmaf(scale, to_float<T>(qrow[i]), term);
+                mx = fmaxf(mx, z[j]);
+            }
+        }
+        mx = warp_max(mx);
+        if ((tid & 31) == 0) red[0][tid >> 5] = mx;
+        __syncthreads();
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, red[0][w]);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            if (tid + j * THREADS < k_len) {
+                z[j] = expf(z[j] - mx);
+                sum += z[j];
+            }
+        }
+        sum = warp_sum(sum);
+        if ((tid & 31) == 0) red[1][tid >> 5] = sum;
+        __syncthreads();
+        sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) sum += red[1][w];
+        const float inv = 1.0f / (sum + 1e-6f);
+#pragma unroll
+        for (int j = 0; j < EPT; ++j) {
+            const int i = tid + j * THREADS;
+            if (i < k_len) orow[i] = from_float<T>(z[j] * inv);
+        }
+        __syncthreads();  // red[] is rewritten by the next row
+    }
+}
+
 // Where the 0/1 mask comes from: a [batch, q_len, k_len] tensor (the reference's interface) or
 // the two length arrays it would have been built from.
 template <typename T>
@@ -282,9 +351,12 @@ int launch_groups(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch,
     const int64_t head_groups = ceil_div(heads, HG);
     const int64_t units = batch * q_len * head_groups;
     const int64_t ctas = ceil_div(units, kGroupsPerCta);
-    const bool full = row_vecs == VPT * GROUP && heads % HG == 0;
-    auto kernel = full ? softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, true, CAUSAL>
-                       : softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, false, CAUSAL>;
+    const bool whole_groups = heads % HG == 0;
+    auto kernel = softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, 2, CAUSAL>;
+    if (whole_groups && row_vecs == VPT * GROUP)
+        kernel = softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, 0, CAUSAL>;
+    else if (whole_groups && row_vecs > (VPT - 1) * GROUP)
+        kernel = softmax_head_group_kernel<T, VPT, GROUP, THREADS, HG, MIN_BLOCKS, 1, CAUSAL>;
     // One trip per CTA for any realistic size: the hardware scheduler hands out CTAs in
     // address order, which keeps the DRAM access front compact.
     const int grid = static_cast<int>(ctas < (1 << 30) ? ctas : (1 << 30));
@@ -316,14 +388,38 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
     return launch_groups<T, CAUSAL, VPT, GROUP, THREADS, HG, MINB>(score, qk, ms, batch, heads, q_len, rv, scale, st)
         if (vecs <= 32) ISPORE_SOFTMAX(1, 32, 256, 4, 1);
         if (vecs <= 64) ISPORE_SOFTMAX(2, 32, 256, 2, 4);
-        if (vecs <= 128) ISPORE_SOFTMAX(4, 32, 256, 2, 1);
-        if (vecs <= 256) ISPORE_SOFTMAX(1, 256, 256, 4, 1);
+        // (launch shapes below were picked by measurement on B200, fp16 and fp32, full and ragged rows)
+        if (vecs <= 128) {
+            if (vecs == 128 && heads % 2 == 0) ISPORE_SOFTMAX(4, 32, 256, 2, 1);
+            ISPORE_SOFTMAX(1, 128, 128, 4, 1);  // ragged rows: one vector per thread, no idle trips
+        }
+        if (vecs <= 256) ISPORE_SOFTMAX(4, 64, 64, 2, 1);
         if (vecs <= 512) ISPORE_SOFTMAX(4, 128, 128, 4, 4);
-        if (vecs <= 1024) ISPORE_SOFTMAX(4, 256, 256, 2, 1);
-        if (vecs <= 2048) ISPORE_SOFTMAX(4, 512, 512, 2, 1);
+        if (vecs <= 1024) ISPORE_SOFTMAX(4, 256, 256, 1, 1);
+        if (vecs <= 2048) {
+            if (sizeof(T) == 4) ISPORE_SOFTMAX(4, 512, 512, 1, 1);
+            ISPORE_SOFTMAX(4, 512, 512, 2, 1);
+        }
+        if (vecs <= 4096) ISPORE_SOFTMAX(8, 512, 512, 1, 1);
 #undef ISPORE_SOFTMAX
     }
     const int64_t rows_per_batch = heads * q_len;
+    if (k_len <= 256 * 16) {
+        const unsigned grid = static_cast<unsigned>(total_rows < (1ll << 30) ? total_rows : (1ll << 30));
+        if (k_len <= 128 * 4)
+            softmax_row_scalar_kernel<T, 128, 4, CAUSAL><<<grid, 128, 0, st>>>(
+                score, qk, ms.mask, ms.q_lens, ms.k_lens, total_rows, rows_per_batch, static_cast<int>(q_len),
+                static_cast<int>(k_len), scale);
+        else if (k_len <= 256 * 8)
+            softmax_row_scalar_kernel<T, 256, 8, CAUSAL><<<grid, 256, 0, st>>>(
+                score, qk, ms.mask, ms.q_lens, ms.k_lens, total_rows, rows_per_batch, static_cast<int>(q_len),
+                static_cast<int>(k_len), scale);
+        else
+            softmax_row_scalar_kernel<T, 256, 16, CAUSAL><<<grid, 256, 0, st>>>(
+                score, qk, ms.mask, ms.q_lens, ms.k_lens, total_rows, rows_per_batch, static_cast<int>(q_len),
+                static_cast<int>(k_len), scale);
+        return check_launch("softmax_row_scalar_kernel");
+    }
     auto generic = softmax_generic_kernel<T, 256, CAUSAL>;
     generic<<<persistent_grid(generic, 256, 0, total_rows, 8), 256, 0, st>>>(
         score, qk, ms.mask, ms.q_lens, ms.k_lens, total_rows, rows_per_batch, static_cast<int>(q_len), k_len, scale);
