@@ -8,6 +8,8 @@
 // r each cross HBM once in and once out.  gamma is loaded once per CTA and
 // reused over all rows the CTA visits (grid-stride over rows, grid sized in
 // multiples of the SM count).
+#include <stdint.h>
+
 #include "common.cuh"
 
 namespace ispore {
@@ -27,7 +29,10 @@ enum class ResidualMode : int {
 // every row) instead of occupying registers.
 // MODE is the ResidualMode; FAST means the row is exactly VPT*THREADS vectors long and there is
 // no bias, so no per-vector guard (each costs a branch) and no bias test remain in the loop.
-template <typename T, int VPT, int THREADS, int MIN_BLOCKS, int MODE, bool FAST>
+// RT: the CTA size is the launch's (any multiple of 32 up to THREADS) instead of THREADS itself, so a
+// row of VPT * blockDim.x vectors fits exactly (hidden sizes such as 5120, 2560, 6144) and runs the
+// guard-free FAST code.
+template <typename T, int VPT, int THREADS, int MIN_BLOCKS, int MODE, bool FAST, bool RT = false>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
 rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __restrict__ bias_arg,
                            const T* __restrict__ gamma, float eps, int64_t num_tokens,
@@ -35,7 +40,8 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
     constexpr int kWarps = THREADS / 32;
     constexpr int E = VecTraits<T>::kElems;
     constexpr ResidualMode mode = static_cast<ResidualMode>(MODE);
-    const int hidden_vecs = FAST ? VPT * THREADS : hidden_vecs_arg;
+    const int nthreads = RT ? static_cast<int>(blockDim.x) : THREADS;
+    const int hidden_vecs = FAST ? VPT * nthreads : hidden_vecs_arg;
     const T* bias = FAST ? nullptr : bias_arg;
     const int tid = threadIdx.x;
     const int lane = tid & 31, warp = tid >> 5;
@@ -51,7 +57,7 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
         uint4 s_raw[VPT], r_raw[VPT];
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int v = tid + i * THREADS;
+            const int v = tid + i * nthreads;
             if (FAST || v < hidden_vecs) {
                 s_raw[i] = ld_stream(xrow + v);
                 if (mode == ResidualMode::kAdd) r_raw[i] = ld_stream(rrow + v);
@@ -61,7 +67,7 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
         float acc = 0.f;
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int v = tid + i * THREADS;
+            const int v = tid + i * nthreads;
             if (FAST || v < hidden_vecs) {
                 Unpacked<T> s;
                 unpack(s_raw[i], s);
@@ -93,13 +99,17 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
         if (lane == 0) partial[parity][warp] = acc;
         __syncthreads();
         float total = 0.f;
+        if (RT) {
+            for (int w = 0; w < nthreads / 32; ++w) total += partial[parity][w];
+        } else {
 #pragma unroll
-        for (int w = 0; w < kWarps; ++w) total += partial[parity][w];
+            for (int w = 0; w < kWarps; ++w) total += partial[parity][w];
+        }
         const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
 
 #pragma unroll
         for (int i = 0; i < VPT; ++i) {
-            const int v = tid + i * THREADS;
+            const int v = tid + i * nthreads;
             if (FAST || v < hidden_vecs) {
                 Unpacked<T> s, g;
                 unpack(s_raw[i], s);
@@ -166,6 +176,36 @@ int launch_regs_as(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t
     return check_launch("rmsnorm_row_in_regs_kernel");
 }
 
+template <typename T, int VPT, int MAXT, int MIN_BLOCKS, bool FAST>
+int launch_rt_as(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens, int64_t hidden,
+                 ResidualMode mode, int threads, cudaStream_t st) {
+    const int hidden_vecs = static_cast<int>(hidden / VecTraits<T>::kElems);
+    const int grid = static_cast<int>(tokens < (1ll << 30) ? tokens : (1ll << 30));
+    switch (mode) {
+        case ResidualMode::kAdd:
+            rmsnorm_row_in_regs_kernel<T, VPT, MAXT, MIN_BLOCKS, 1, FAST, true><<<grid, threads, 0, st>>>(
+                x, r, bias, gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden));
+            break;
+        case ResidualMode::kCopyOut:
+            rmsnorm_row_in_regs_kernel<T, VPT, MAXT, MIN_BLOCKS, 2, FAST, true><<<grid, threads, 0, st>>>(
+                x, r, bias, gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden));
+            break;
+        default:
+            rmsnorm_row_in_regs_kernel<T, VPT, MAXT, MIN_BLOCKS, 0, FAST, true><<<grid, threads, 0, st>>>(
+                x, r, bias, gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden));
+    }
+    return check_launch("rmsnorm_row_in_regs_kernel");
+}
+
+// CTA of `threads` threads (a multiple of 32) holding VPT vectors each; `exact` when the row fills
+// every slot and there is no bias (the guard-free code).
+template <typename T, int VPT, int MAXT, int MIN_BLOCKS>
+int launch_rt(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens, int64_t hidden, ResidualMode mode,
+              int threads, bool exact, cudaStream_t st) {
+    return exact ? launch_rt_as<T, VPT, MAXT, MIN_BLOCKS, true>(x, r, bias, gamma, eps, tokens, hidden, mode, threads, st)
+                 : launch_rt_as<T, VPT, MAXT, MIN_BLOCKS, false>(x, r, bias, gamma, eps, tokens, hidden, mode, threads, st);
+}
+
 template <typename T, int VPT, int THREADS, int MIN_BLOCKS>
 int launch_regs(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens, int64_t hidden,
                 ResidualMode mode, cudaStream_t st) {
@@ -203,6 +243,47 @@ int rmsnorm_dispatch(T* x, T* r, const T* bias, const T* gamma, float eps, int64
     const bool one_stream = mode == ResidualMode::kNone;
 #define ISPORE_NORM(VPT, THREADS, BLOCKS) \
     return launch_regs<T, VPT, THREADS, BLOCKS>(x, r, bias, gamma, eps, tokens, hidden, mode, st)
+    // Rows that match none of the fixed shapes below exactly (5120, 2560, 6144, 7168, 4104 ... at
+    // fp16): a CTA just large enough, ceil(vecs / VPT) threads rounded up to whole warps; when the row
+    // fills every slot (and there is no bias) the guard-free code runs.
+    const bool fixed_fit = vecs == 128 || vecs == 256 || vecs == 512 || vecs == 1024 || vecs == 2048 || vecs == 4096;
+    if (vec_ok && !fixed_fit && vecs > 64 && vecs <= 4096) {
+        const bool four_first = one_stream || vecs > 640;  // measured: two input streams like 2 vectors per thread up to 5120 halves
+        const int prefer[3] = {four_first ? 4 : 2, four_first ? 2 : 4, 1};
+        int best_vpt = 0;
+        int64_t best_idle = INT64_MAX;
+        for (int vpt : prefer) {  // the first preferred count that idles at most an eighth of its slots, else the fewest idle
+            const int64_t threads = ceil_div(ceil_div(vecs, static_cast<int64_t>(vpt)), 32) * 32;
+            if (threads > 1024) continue;
+            const int64_t idle = threads * vpt - vecs;
+            if (idle * 8 <= threads * vpt) {
+                best_idle = idle;
+                best_vpt = vpt;
+                break;
+            }
+            if (idle < best_idle) {
+                best_idle = idle;
+                best_vpt = vpt;
+            }
+        }
+        if (best_vpt != 0) {
+            const int th = static_cast<int>(ceil_div(ceil_div(vecs, static_cast<int64_t>(best_vpt)), 32) * 32);
+            const bool exact = best_idle == 0 && bias == nullptr;
+#define ISPORE_NORM_RT(VPT, MAXT, BLOCKS) \
+    return launch_rt<T, VPT, MAXT, BLOCKS>(x, r, bias, gamma, eps, tokens, hidden, mode, th, exact, st)
+            if (best_vpt == 4) {
+                if (th <= 256) ISPORE_NORM_RT(4, 256, 4);
+                ISPORE_NORM_RT(4, 1024, 1);
+            }
+            if (best_vpt == 2) {
+                if (th <= 512) ISPORE_NORM_RT(2, 512, 2);
+                ISPORE_NORM_RT(2, 1024, 1);
+            }
+            if (th <= 512) ISPORE_NORM_RT(1, 512, 2);
+            ISPORE_NORM_RT(1, 1024, 1);
+#undef ISPORE_NORM_RT
+        }
+    }
     if (vec_ok && vecs <= 128) ISPORE_NORM(1, 128, 8);
     if (vec_ok && vecs <= 256) ISPORE_NORM(2, 128, 8);
     if (vec_ok && vecs <= 512) {
