@@ -192,26 +192,30 @@ qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
 // contiguous span of QKV (24 KB for Llama-2-7B in fp16), so one thread starts TMA bulk copies of
 // the whole span and the CTA looks up the position and evaluates cos/sin while they fly.  No
 // registers are tied up holding loads in flight, which lets eight CTAs (and their 8 x 24 KB of
-// outstanding reads) share an SM.  Full rotation (rotary_dim == HEAD_SIZE) only.
+// outstanding reads) share an SM.  HEAD_SIZE == 0 and FULL_ROT == false cover any head size (a
+// multiple of two vectors) and partial rotation at the price of run-time index divisions.
 constexpr int kTmaPiece = 8192;
 
-template <typename T, int THREADS, int HEAD_SIZE, bool HAS_BIAS>
+template <typename T, int THREADS, int HEAD_SIZE, bool FULL_ROT, bool HAS_BIAS>
 __global__ void __launch_bounds__(THREADS)
 qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* __restrict__ v_buf,
                               const T* __restrict__ QKV, const T* __restrict__ bias,
                               const int32_t* __restrict__ padding_offset,
                               const int32_t* __restrict__ history_length, int64_t batch_size,
-                              int64_t seq_len, int head_num, int kv_head_num, const RopeDenominators freq,
-                              unsigned* __restrict__ status) {
+                              int64_t seq_len, int head_num, int kv_head_num, int head_size_arg, int rot_half_arg,
+                              const RopeDenominators freq, unsigned* __restrict__ status) {
     constexpr int E = VecTraits<T>::kElems;
-    constexpr int kHeadVecs = HEAD_SIZE / E, kHalfVecs = kHeadVecs / 2, kRotHalf = HEAD_SIZE / 2;
+    // compile-time head size: the task -> (head, vector) split is shifts; 0: taken from the argument
+    const int head_size = HEAD_SIZE > 0 ? HEAD_SIZE : head_size_arg;
+    const int kHeadVecs = head_size / E, kHalfVecs = kHeadVecs / 2;
+    const int kRotHalf = FULL_ROT ? head_size / 2 : rot_half_arg;
     extern __shared__ __align__(128) unsigned char token_raw[];
-    __shared__ float2 cos_sin[kRotHalf];
+    __shared__ float2 cos_sin[HEAD_SIZE > 0 ? HEAD_SIZE / 2 : kMaxRotHalf];
     __shared__ __align__(8) uint64_t bar;
     const int tid = threadIdx.x;
     const int qkv_heads = head_num + 2 * kv_head_num;
     const int64_t token = blockIdx.x;
-    const uint32_t bytes = static_cast<uint32_t>(qkv_heads) * HEAD_SIZE * sizeof(T);
+    const uint32_t bytes = static_cast<uint32_t>(qkv_heads) * head_size * sizeof(T);
     if (tid == 0) {
         tma::mbar_init(&bar, 1);
         tma::fence_mbar_init();
@@ -274,10 +278,12 @@ qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
         }
 #pragma unroll
         for (int e = 0; e < E; ++e) {
-            const float2 cs = cos_sin[c * E + e];
-            const float x0 = lo.v[e], x1 = hi.v[e];
-            lo.v[e] = cs.x * x0 - cs.y * x1;
-            hi.v[e] = cs.x * x1 + cs.y * x0;
+            if (FULL_ROT || c * E + e < kRotHalf) {
+                const float2 cs = cos_sin[c * E + e];
+                const float x0 = lo.v[e], x1 = hi.v[e];
+                lo.v[e] = cs.x * x0 - cs.y * x1;
+                hi.v[e] = cs.x * x1 + cs.y * x0;
+            }
         }
         uint4* dst = hh < head_num ? q_row + hh * head_stride : k_row + (hh - head_num) * head_stride;
         st_stream(dst + c, pack(lo));
@@ -426,14 +432,14 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
             token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);     \
         return check_launch("qkv_rope_transpose_vec_kernel");                                           \
     } while (0)
-        // Full rotation at a compile-time head size: the shared-memory staged kernel.
+        // The shared-memory staged kernel: compile-time head size and full rotation for the usual
+        // shapes, run-time head size / partial rotation otherwise.
         const int64_t token_bytes = (head_num + 2 * kv_head_num) * head_size * static_cast<int64_t>(sizeof(T));
-        if (full_rot && (head_size == 128 || head_size == 64) && token_bytes <= 96 * 1024 && token_num < (1ll << 31) &&
-            tune(kTuneQkv, 0) != 1) {
-#define ISPORE_QKV_TMA(HS, HB)                                                                              \
+        if (token_bytes <= 96 * 1024 && token_num < (1ll << 31) && head_size <= 2 * kMaxRotHalf && tune(kTuneQkv, 0) != 1) {
+#define ISPORE_QKV_TMA(HS, FR, HB)                                                                          \
     do {                                                                                                    \
         constexpr int TH = 128; /* measured: 64 and 256 threads are 3-6 % slower */                         \
-        auto kernel = qkv_rope_transpose_tma_kernel<T, TH, HS, HB>;                                         \
+        auto kernel = qkv_rope_transpose_tma_kernel<T, TH, HS, FR, HB>;                                     \
         if (token_bytes > 40 * 1024 &&                                                                      \
             cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)token_bytes) != cudaSuccess) { \
             cudaGetLastError();                                                                             \
@@ -441,15 +447,21 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
         }                                                                                                   \
         kernel<<<static_cast<unsigned>(token_num), TH, static_cast<size_t>(token_bytes), st>>>(             \
             q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,           \
-            (int)head_num, (int)kv_head_num, freq, status);                                                 \
+            (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);                    \
         return check_launch("qkv_rope_transpose_tma_kernel");                                               \
     } while (0)
-            if (head_size == 128) {
-                if (has_bias) ISPORE_QKV_TMA(128, true);
-                else ISPORE_QKV_TMA(128, false);
+            if (full_rot && head_size == 128) {
+                if (has_bias) ISPORE_QKV_TMA(128, true, true);
+                else ISPORE_QKV_TMA(128, true, false);
+            } else if (full_rot && head_size == 64) {
+                if (has_bias) ISPORE_QKV_TMA(64, true, true);
+                else ISPORE_QKV_TMA(64, true, false);
+            } else if (full_rot) {
+                if (has_bias) ISPORE_QKV_TMA(0, true, true);
+                else ISPORE_QKV_TMA(0, true, false);
             } else {
-                if (has_bias) ISPORE_QKV_TMA(64, true);
-                else ISPORE_QKV_TMA(64, false);
+                if (has_bias) ISPORE_QKV_TMA(0, false, true);
+                else ISPORE_QKV_TMA(0, false, false);
             }
 #undef ISPORE_QKV_TMA
         }
