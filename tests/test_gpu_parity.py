@@ -849,3 +849,21 @@ def test_softmax_many_short_sequences(ops, orc, rng):
     ops.launchScaleMaskAndSoftmax(dev(qk), dev(mask), out, 0.5)
     want, _ = orc.scale_mask_softmax(qk, mask, np.float32(0.5))
     assert_close_f32(host(out), want, floor=1e-30, what="softmax, many short sequences")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("case", [(2, 5, 7, 777), (1, 3, 2, 4099), (3, 4, 5, 37), (1, 2, 3, 1001)])
+def test_softmax_rows_not_16_byte_aligned_in_place(ops, orc, rng, case, dtype):
+    # k_len is not a multiple of the 128-bit vector: rows start at arbitrary offsets inside aligned
+    # vectors, neighbouring rows share a vector, and attn_score aliases qk
+    batch, heads, q_len, k_len = case
+    qk = (rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32) * 3).astype(dtype)
+    mask = _causal_mask(rng, batch, q_len, k_len, dtype)
+    d = dev(qk)
+    ops.launchScaleMaskAndSoftmax(d, dev(mask), d, 0.25)
+    want, want32 = orc.scale_mask_softmax(qk, mask, np.float32(0.25))
+    if dtype == np.float16:
+        err, over, _ = assert_close_f16(host(d), want32, want, "unaligned softmax f16")
+        assert over == 0
+    else:
+        assert_close_f32(host(d), want, floor=1e-30, what="unaligned softmax f32")
