@@ -1,11 +1,11 @@
 """The CUDA library against the REFERENCE's own GPU kernels and unit tests, on the same GPU.
 
 oracle/_ref/ holds the reference's kernel sources compiled for sm_100a (from where they lie in the
-reference tree, see oracle/build.py) behind a small C ABI, and the reference's six hot-path unit
+reference tree, see oracle/build.py) behind a small C ABI, and eleven of the reference's unit
 tests compiled unmodified against the drop-in headers.  Only reference kernels that are functional
 are run, and only on shapes they are safe for (the wrappers in oracle/ref_wrap/ refuse the rest):
 fp32 residual+RMSNorm, embedding, fp32 QKV+RoPE (the reference applies no bias), SiLU*up, KV concat,
-softmax.  Marked gpu.
+softmax, causal mask, padding offsets, repeat-KV, decode attention.  Marked gpu.
 """
 import ctypes as C
 import subprocess
