@@ -1,5 +1,3 @@
-// Embedding table [vocab, hidden] (reference: src/weights/llama/embedding_weights.h).
+// Same include path as the reference tree; the definitions live in llama_weights.h.
 #pragma once
-#include "src/weights/base_weights.h"
-template <typename T>
-struct EmbeddingWeight : public BaseWeight<T> {};
+#include "src/weights/llama/llama_weights.h"

@@ -1,10 +1,3 @@
-// Feed-forward weights (reference: src/weights/llama/ffn_weights.h).
+// Same include path as the reference tree; the definitions live in llama_weights.h.
 #pragma once
-#include "src/weights/base_weights.h"
-template <typename T>
-struct LLaMAFFNWeights {
-    BaseWeight<T> gate;
-    BaseWeight<T> up;
-    BaseWeight<T> down;
-    BaseWeight<T> gateAndup;
-};
+#include "src/weights/llama/llama_weights.h"

@@ -1,6 +1,3 @@
-// RMSNorm weight (reference: src/weights/llama/norm_weights.h).
+// Same include path as the reference tree; the definitions live in llama_weights.h.
 #pragma once
-template <typename T>
-struct LayerNormWeight {
-    T* gamma;
-};
+#include "src/weights/llama/llama_weights.h"
