@@ -353,3 +353,88 @@ def test_vs_reference_gpu_decoder_masked_mha(ops, orc, rng, half, heads, kv, ste
     # the reference multiplies q*k*scale in the storage type (half products for fp16): 1e-3 is
     # its own test's tolerance and what half products allow; fp32 agrees far closer
     assert np.max(np.abs(host(ours).astype(np.float64) - host(ref).astype(np.float64))) <= (5e-3 if half else 5e-5)
+
+
+# ---- a C++ caller of the drop-in templates beyond the reference's own (tiny) test shapes -----------
+
+CPP_DECODE_ATTENTION = r"""
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <vector>
+#include "src/kernels/fused_decoder_self_attention.h"
+
+#define CUDA_OK(x) do { if ((x) != cudaSuccess) { std::printf("cuda error line %d\n", __LINE__); return 1; } } while (0)
+
+int main() {
+    const int batch = 2, heads = 32, kv = 32, d = 128, max_seq = 3000;
+    int step = 2900, layer = 0;
+    const size_t n_qkv = size_t(batch) * (heads + 2 * kv) * d, n_cache = size_t(batch) * kv * max_seq * d;
+    const size_t n_out = size_t(batch) * heads * d;
+    std::vector<half> h_qkv(n_qkv), h_cache(n_cache);
+    std::srand(5);
+    auto rnd = [] { return __float2half((std::rand() % 2001 - 1000) / 1000.0f); };
+    for (auto& x : h_qkv) x = rnd();
+    for (auto& x : h_cache) x = rnd();
+    half *d_qkv, *d_k, *d_v, *d_k2, *d_v2, *d_out, *d_out2;
+    CUDA_OK(cudaMalloc(&d_qkv, n_qkv * 2));
+    CUDA_OK(cudaMalloc(&d_k, n_cache * 2)); CUDA_OK(cudaMalloc(&d_v, n_cache * 2));
+    CUDA_OK(cudaMalloc(&d_k2, n_cache * 2)); CUDA_OK(cudaMalloc(&d_v2, n_cache * 2));
+    CUDA_OK(cudaMalloc(&d_out, n_out * 2)); CUDA_OK(cudaMalloc(&d_out2, n_out * 2));
+    CUDA_OK(cudaMemcpy(d_qkv, h_qkv.data(), n_qkv * 2, cudaMemcpyHostToDevice));
+    for (half* p : {d_k, d_v, d_k2, d_v2}) CUDA_OK(cudaMemcpy(p, h_cache.data(), n_cache * 2, cudaMemcpyHostToDevice));
+
+    // 1. through the reference's launcher signature: the template sizes and keeps its own workspace
+    TensorWrapper<half> qkv(GPU, FP16, {batch, heads + 2 * kv, d}, d_qkv);
+    TensorWrapper<half> kc(GPU, FP16, {1, batch, kv, max_seq, d}, d_k), vc(GPU, FP16, {1, batch, kv, max_seq, d}, d_v);
+    TensorWrapper<half> out(GPU, FP16, {batch, heads, d}, d_out);
+    TensorWrapper<int> st(CPU, INT32, {1}, &step), lid(CPU, INT32, {1}, &layer);
+    TensorWrapper<bool> fin(GPU, BOOL, {batch}, nullptr);
+    BaseWeight<half> w;  // no bias
+    LLaMAAttentionStaticParams params;
+    params.rotary_embedding_dim = 128;
+    params.rotary_embedding_base = 10000.0f;
+    params.max_position_embeddings = 4096;
+    params.use_dynamic_ntk = false;
+    if (ispore_decoder_masked_mha_workspace_bytes(batch, heads, kv, d, step) <= 0) { std::printf("expected a split plan\n"); return 1; }
+    for (int rep = 0; rep < 2; ++rep)  // the second call reuses the buffer
+        launchDecoderMaskedMHA(&qkv, w, &lid, &kc, &vc, &fin, &st, &out, params);
+    // 2. the C ABI without a workspace: one CTA per (sequence, head)
+    if (ispore_decoder_masked_mha_f16(d_out2, d_qkv, nullptr, d_k2, d_v2, 0, 1, batch, heads, kv, max_seq, d, step, 128,
+                                      10000.0f, float(step), nullptr, 0, nullptr) != ISPORE_OK) {
+        std::printf("C ABI call failed: %s\n", ispore_last_error_string());
+        return 1;
+    }
+    CUDA_OK(cudaDeviceSynchronize());
+    std::vector<half> a(n_out), b(n_out), ka(n_cache), kb(n_cache);
+    CUDA_OK(cudaMemcpy(a.data(), d_out, n_out * 2, cudaMemcpyDeviceToHost));
+    CUDA_OK(cudaMemcpy(b.data(), d_out2, n_out * 2, cudaMemcpyDeviceToHost));
+    CUDA_OK(cudaMemcpy(ka.data(), d_k, n_cache * 2, cudaMemcpyDeviceToHost));
+    CUDA_OK(cudaMemcpy(kb.data(), d_k2, n_cache * 2, cudaMemcpyDeviceToHost));
+    float worst = 0.f;
+    for (size_t i = 0; i < n_out; ++i) worst = std::fmax(worst, std::fabs(__half2float(a[i]) - __half2float(b[i])));
+    size_t cache_diff = 0;
+    for (size_t i = 0; i < n_cache; ++i) cache_diff += __half2float(ka[i]) != __half2float(kb[i]);
+    std::printf("worst %g cache_diff %zu\n", worst, cache_diff);
+    if (worst > 1e-3f || cache_diff != 0) return 1;
+    std::printf("decode attention through the template ok\n");
+    return 0;
+}
+"""
+
+
+def test_cpp_caller_decoder_attention_with_template_workspace(cuda, tmp_path):
+    import shutil
+
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    src = tmp_path / "mha_caller.cu"
+    src.write_text(CPP_DECODE_ATTENTION)
+    exe = tmp_path / "mha_caller"
+    lib_dir = ROOT / "inferspore_b200" / "lib"
+    cmd = [nvcc, "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-w",
+           f"-I{ROOT / 'inferspore_b200' / 'compat'}", f"-I{ROOT / 'include'}", str(src), "-o", str(exe),
+           f"-L{lib_dir}", "-lispore_kernels", "-Xlinker", "-rpath", "-Xlinker", str(lib_dir)]
+    build = subprocess.run(cmd, capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-3000:]
+    run = subprocess.run([str(exe)], capture_output=True, text=True, timeout=300)
+    assert run.returncode == 0 and "through the template ok" in run.stdout, run.stdout + run.stderr
