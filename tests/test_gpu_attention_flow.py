@@ -93,3 +93,38 @@ def test_context_attention_flow(ops, rng, lens, heads, kv_heads, d):
             want = p @ vv[:, h // group]
             assert np.allclose(got[start:start + n, h], want, rtol=2e-4, atol=2e-5), (n, h)
         start += n
+
+
+def test_decode_steps_build_the_cache_they_read(ops, rng):
+    """Six decode steps from an empty cache: step s appends at position s-1 and attends to
+    positions < s, so every step's output depends on every earlier append being where the later
+    steps look for it.  Adjacent-pair RoPE at position `step`, as the reference's decode kernel."""
+    dev = "cuda:0"
+    batch, heads, kv_heads, d, max_seq, base = 2, 4, 2, 16, 8, 10000.0
+    group = heads // kv_heads
+    kc = torch.zeros((1, batch, kv_heads, max_seq, d), device=dev)
+    vc = torch.zeros_like(kc)
+    out = torch.empty((batch, heads, d), device=dev)
+    hist_k = np.zeros((batch, kv_heads, 0, d))
+    hist_v = np.zeros((batch, kv_heads, 0, d))
+    i = np.arange(d // 2)
+    for step in range(1, 7):
+        qkv = rng.standard_normal((batch, heads + 2 * kv_heads, d), dtype=np.float32)
+        ops.launchDecoderMaskedMHA(torch.from_numpy(qkv).to(dev), None, 0, kc, vc, None, step, out, d, base)
+        x = qkv.astype(np.float64)
+        theta = step / base ** (2.0 * i / d)
+        c, s = np.cos(theta), np.sin(theta)
+        rot = x.copy()
+        rot[:, :heads + kv_heads, 0::2] = c * x[:, :heads + kv_heads, 0::2] - s * x[:, :heads + kv_heads, 1::2]
+        rot[:, :heads + kv_heads, 1::2] = c * x[:, :heads + kv_heads, 1::2] + s * x[:, :heads + kv_heads, 0::2]
+        hist_k = np.concatenate([hist_k, rot[:, heads:heads + kv_heads, None]], 2)
+        hist_v = np.concatenate([hist_v, rot[:, heads + kv_heads:, None]], 2)
+        got = out.cpu().numpy().astype(np.float64)
+        for b in range(batch):
+            for h in range(heads):
+                logits = hist_k[b, h // group] @ rot[b, h] / np.sqrt(d)
+                p = np.exp(logits - logits.max())
+                want = (p / (p.sum() + 1e-6)) @ hist_v[b, h // group]
+                assert np.allclose(got[b, h], want, rtol=1e-4, atol=1e-5), (step, b, h)
+    assert np.allclose(kc[0, :, :, :6].cpu().numpy(), hist_k, rtol=1e-5, atol=1e-6)
+    assert not kc[0, :, :, 6:].any()
