@@ -82,6 +82,11 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
     return r;
 }
 
+// e^x for the softmax numerators: the library function for fp32 rows, the hardware exp2 for half
+// rows (its error, about 2^-21 relative, is far below a half's spacing).
+template <typename T>
+__device__ __forceinline__ float exp_for(float x) { return std::is_same<T, float>::value ? expf(x) : __expf(x); }
+
 // Rounds through the storage type, as the reference does when it keeps q, k, v in T registers.
 template <typename T>
 __device__ __forceinline__ float round_to(float x) { return to_float<T>(from_float<T>(x)); }
@@ -123,10 +128,18 @@ struct GroupReduce<N, 0> {
 //   b0 = B[2t, 2t+1][g], b1 = B[2t+8, 2t+9][g],  d0, d1 = D[g][2t, 2t+1], d2, d3 = D[g+8][2t, 2t+1].
 __device__ __forceinline__ void mma_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                             uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
         : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Four 8x8 fp16 matrices from shared memory, transposed on the way: lane l gives the address of
+// row l % 8 of matrix l / 8; lane (g, t) receives M_i[2t][g], M_i[2t+1][g] in r_i.
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* smem_row) {
+    const uint32_t addr = static_cast<uint32_t>(__cvta_generic_to_shared(smem_row));
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+                 : "r"(addr));
 }
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
@@ -143,6 +156,10 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 // registers or on how many CTAs fit, which is what the wider head groups (more registers, fewer
 // CTAs per SM) need to reach the memory roofline.
 constexpr int kStages = 3;
+#ifndef ISPORE_MHA_PV_MIN_GROUP
+#define ISPORE_MHA_PV_MIN_GROUP 8
+#endif
+constexpr int kPvTensorMinGroup = ISPORE_MHA_PV_MIN_GROUP;  // q heads per CTA from which numerators x V runs on the tensor cores
 
 template <typename T, int LPK, int GT, int U, bool STAGED>
 __global__ void __launch_bounds__(kMhaThreads)
@@ -154,6 +171,18 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     constexpr int kStageRows = KPI * U;     // rows per pass of the CTA = rows per shared-memory tile
     constexpr int kStageBytes = kStageRows * D * static_cast<int>(sizeof(T));
     static_assert(!STAGED || kStageBytes == 16384, "a staged tile is one pass of eight rows per thread");
+    // Tensor-core paths: q.K needs several heads on half rows of 128; numerators x V needs the V
+    // tile in shared memory as well, with every row padded by 16 bytes so that the eight row
+    // addresses of one ldmatrix phase fall into different banks.
+    constexpr bool kMmaQK = std::is_same<T, __half>::value && LPK == 16 && GT >= 2;
+    constexpr bool kMmaPV = kMmaQK && STAGED && GT >= kPvTensorMinGroup;
+    constexpr int kRowBytes = D * static_cast<int>(sizeof(T));
+    // A V tile of the tensor-core path lands as eight groups of eight rows, each group 16 bytes
+    // further along than rows alone would put it: the eight rows one ldmatrix phase reads are taken
+    // one from each group, so they fall into different banks.
+    constexpr int kGroupRows = 8;
+    constexpr int kGroupBytes = kGroupRows * kRowBytes + (kMmaPV ? 16 : 0);
+    constexpr int kStageStride = kMmaPV ? (kStageRows / kGroupRows) * kGroupBytes : kStageBytes;
     __shared__ float q_s[GT][D];
     __shared__ float knew_s[D], vnew_s[D];
     __shared__ float2 cs_s[kMaxRotPairs];
@@ -162,7 +191,8 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     __shared__ __align__(8) uint64_t full[kStages];
     extern __shared__ __align__(128) unsigned char dyn_raw[];  // [tiles when STAGED][logits / output reduction buffer]
     unsigned char* const stage_base = dyn_raw;
-    float* const dyn_s = reinterpret_cast<float*>(dyn_raw + (STAGED ? kStages * kStageBytes : 0));
+    float* const dyn_s = reinterpret_cast<float*>(dyn_raw + (STAGED ? kStages * kStageStride : 0));
+    const int lstride = p.chunk + (kMmaPV ? 8 : 0);  // floats between two heads' logits (bank spread)
 
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int lk = tid % LPK, ks = tid / LPK;
@@ -181,25 +211,42 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
 
     // Tiles 0 .. nt-1 are K rows, nt .. 2nt-1 the same rows of V.
     const int nt = (n_cache + kStageRows - 1) / kStageRows;
-    auto issue_tile = [&](int tile) {
+    // Called by every thread.  K tiles (and V tiles of the FMA path) are one contiguous copy issued
+    // by thread 0; a V tile of the tensor-core path is one copy per group of rows, each issued by
+    // its own thread.
+    int ring_slot = 0;         // stage of the tile consumed next
+    uint32_t ring_phase = 0;   // parity its barrier completes with
+    auto issue_tile = [&](int tile, int slot) {
         const bool is_v = tile >= nt;
         const int first_row = (is_v ? tile - nt : tile) * kStageRows;
         const int rows = min(kStageRows, n_cache - first_row);
-        const uint32_t bytes = static_cast<uint32_t>(rows) * D * sizeof(T);
+        const uint32_t bytes = static_cast<uint32_t>(rows) * kRowBytes;
         const T* src = (is_v ? p.v_cache : p.k_cache) + (cache_row0 + s0 + first_row) * D;
-        uint64_t* bar = &full[tile % kStages];
-        tma::mbar_arrive_expect_tx(bar, bytes);
-        tma::load(stage_base + (tile % kStages) * kStageBytes, src, bytes, bar);
+        uint64_t* bar = &full[slot];
+        unsigned char* dst = stage_base + slot * kStageStride;
+        if (tid == 0) tma::mbar_arrive_expect_tx(bar, bytes);
+        if (kMmaPV && is_v) {
+            const int group_rows = min(kGroupRows, rows - tid * kGroupRows);
+            if (group_rows > 0)
+                tma::load(dst + tid * kGroupBytes, src + tid * kGroupRows * D, group_rows * kRowBytes, bar);
+        } else if (tid == 0) {
+            tma::load(dst, src, bytes, bar);
+        }
     };
-    if (STAGED && tid == 0) {
+    if (STAGED) {
+        if (tid == 0) {
 #pragma unroll
-        for (int st = 0; st < kStages; ++st) tma::mbar_init(&full[st], 1);
-        tma::fence_mbar_init();
-        for (int tile = 0; tile < kStages && tile < 2 * nt; ++tile) issue_tile(tile);
+            for (int st = 0; st < kStages; ++st) tma::mbar_init(&full[st], 1);
+            tma::fence_mbar_init();
+        }
+        if (kMmaPV) __syncthreads();  // other threads issue copies on these barriers too
+        if (kMmaPV || tid == 0)
+            for (int tile = 0; tile < kStages && tile < 2 * nt; ++tile) issue_tile(tile, tile);
     }
     // Waits for tile `tile`; false when the copy did not land in time (reported at release).
     auto acquire_tile = [&](int tile) -> bool {
-        return !STAGED || tma::mbar_wait(&full[tile % kStages], (tile / kStages) & 1);
+        (void)tile;
+        return !STAGED || tma::mbar_wait(&full[ring_slot], ring_phase);
     };
     // Every thread is done with tile `tile`: its stage is refilled with tile + kStages.  Returns
     // false (for the whole CTA) when a copy was lost; the caller leaves the kernel.
@@ -213,7 +260,11 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
             }
             return false;
         }
-        if (tid == 0 && tile + kStages < 2 * nt) issue_tile(tile + kStages);
+        if ((kMmaPV || tid == 0) && tile + kStages < 2 * nt) issue_tile(tile + kStages, ring_slot);
+        if (++ring_slot == kStages) {
+            ring_slot = 0;
+            ring_phase ^= 1u;
+        }
         return true;
     };
 
@@ -272,7 +323,6 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     // k-slot (2t, 2t+1) of step (j, s) stands for elements 8(t+4j) + 4s + (0, 1), slot
     // (2t+8, 2t+9) for elements 8(t+4j) + 4s + (2, 3).  q (already rounded to half) is the B
     // tile, one head per column; columns GT..7 are zero.
-    constexpr bool kMmaQK = std::is_same<T, __half>::value && LPK == 16 && GT >= 2;
     if constexpr (kMmaQK) {
         const int g = lane >> 2, t = lane & 3;
         uint32_t bq[4][2][2];  // [j][s][low / high k half]
@@ -292,7 +342,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
             const bool landed = acquire_tile(tile);
             const int l0 = warp * 16 + g, l1 = l0 + 8;  // rows inside the tile
             const int r0 = tile_row + l0, r1 = tile_row + l1;
-            const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + (tile % kStages) * kStageBytes);
+            const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + ring_slot * kStageStride);
             uint4 a_lo[4], a_hi[4];  // rows g and g + 8 of this warp's 16, chunks t + 4j
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -305,21 +355,23 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
                 }
             }
             if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc[4] = {0.f, 0.f, 0.f, 0.f}, acc2[4] = {0.f, 0.f, 0.f, 0.f};  // two chains: half the latency
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 mma_16x8x16(acc, a_lo[j].x, a_hi[j].x, a_lo[j].y, a_hi[j].y, bq[j][0][0], bq[j][0][1]);
-                mma_16x8x16(acc, a_lo[j].z, a_hi[j].z, a_lo[j].w, a_hi[j].w, bq[j][1][0], bq[j][1][1]);
+                mma_16x8x16(acc2, a_lo[j].z, a_hi[j].z, a_lo[j].w, a_hi[j].w, bq[j][1][0], bq[j][1][1]);
             }
+#pragma unroll
+            for (int c = 0; c < 4; ++c) acc[c] += acc2[c];
             // acc[0], acc[1]: row g, heads 2t, 2t+1; acc[2], acc[3]: row g + 8
             if (2 * t < GT) {
                 if (r0 < n_cache) {
-                    logits[(2 * t) * p.chunk + r0] = acc[0] * p.scale;
-                    if (2 * t + 1 < GT) logits[(2 * t + 1) * p.chunk + r0] = acc[1] * p.scale;
+                    logits[(2 * t) * lstride + r0] = acc[0] * p.scale;
+                    if (2 * t + 1 < GT) logits[(2 * t + 1) * lstride + r0] = acc[1] * p.scale;
                 }
                 if (r1 < n_cache) {
-                    logits[(2 * t) * p.chunk + r1] = acc[2] * p.scale;
-                    if (2 * t + 1 < GT) logits[(2 * t + 1) * p.chunk + r1] = acc[3] * p.scale;
+                    logits[(2 * t) * lstride + r1] = acc[2] * p.scale;
+                    if (2 * t + 1 < GT) logits[(2 * t + 1) * lstride + r1] = acc[3] * p.scale;
                 }
             }
         }
@@ -332,7 +384,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
         const uint4* krows = reinterpret_cast<const uint4*>(p.k_cache) + (cache_row0 + s0) * LPK + lk;
         for (int base = 0, tile = 0; base < n_cache; base += KPI * U, ++tile) {
             const bool landed = acquire_tile(tile);
-            const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + (tile % kStages) * kStageBytes);
+            const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + ring_slot * kStageStride);
             uint4 raw[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) {
@@ -365,7 +417,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
                 for (int j = 0; j < kHeld; ++j) {
                     const int idx = first + j, g = idx / U, u = idx % U;
                     const int i = base + u * KPI + ks;
-                    if (i < n_cache) logits[g * p.chunk + i] = dots[j] * p.scale;
+                    if (i < n_cache) logits[g * lstride + i] = dots[j] * p.scale;
                 }
             }
         }
@@ -376,39 +428,56 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
             float dot = 0.f;
             for (int i = lane; i < D; i += 32) dot = fmaf(q_s[g][i], knew_s[i], dot);
             dot = warp_sum(dot);
-            if (lane == 0) logits[g * p.chunk + (last - s0)] = dot * p.scale;
+            if (lane == 0) logits[g * lstride + (last - s0)] = dot * p.scale;
         }
     }
     __syncthreads();
 
     // ---- softmax numerators over the chunk ----------------------------------------------------------
-    if constexpr (GT == kMhaWarps) {
-        // one warp per head: warp reductions only, no block barrier until all heads are done
-        float* row = logits + warp * p.chunk;
-        float mx = -FLT_MAX;
-        for (int i = lane; i < n; i += 32) mx = fmaxf(mx, row[i]);
-        mx = warp_max(mx);
-        float sum = 0.f;
-        for (int i = lane; i < n; i += 32) {
-            const float e = expf(row[i] - mx);
-            row[i] = e;
-            sum += e;
-        }
-        sum = warp_sum(sum);
-        if (lane == 0) {
-            m_s[warp] = mx;
-            l_s[warp] = sum;
+    if constexpr (GT % kMhaWarps == 0) {
+        // a warp per head (two when eight heads share the rows): warp reductions only, no block
+        // barrier until all heads are done
+        for (int hh = warp; hh < GT; hh += kMhaWarps) {
+            float* row = logits + hh * lstride;  // 16-byte aligned: chunk and the row pad are multiples of 4 floats
+            const int n4 = n & ~3;
+            float mx = -FLT_MAX;
+            for (int i = 4 * lane; i < n4; i += 128) {
+                const float4 v = *reinterpret_cast<const float4*>(row + i);
+                mx = fmaxf(fmaxf(mx, fmaxf(v.x, v.y)), fmaxf(v.z, v.w));
+            }
+            for (int i = n4 + lane; i < n; i += 32) mx = fmaxf(mx, row[i]);
+            mx = warp_max(mx);
+            float sum = 0.f;
+            for (int i = 4 * lane; i < n4; i += 128) {
+                float4 v = *reinterpret_cast<const float4*>(row + i);
+                v.x = exp_for<T>(v.x - mx);
+                v.y = exp_for<T>(v.y - mx);
+                v.z = exp_for<T>(v.z - mx);
+                v.w = exp_for<T>(v.w - mx);
+                *reinterpret_cast<float4*>(row + i) = v;
+                sum += (v.x + v.y) + (v.z + v.w);
+            }
+            for (int i = n4 + lane; i < n; i += 32) {
+                const float e = exp_for<T>(row[i] - mx);
+                row[i] = e;
+                sum += e;
+            }
+            sum = warp_sum(sum);
+            if (lane == 0) {
+                m_s[hh] = mx;
+                l_s[hh] = sum;
+            }
         }
     } else {
 #pragma unroll
         for (int g = 0; g < GT; ++g) {
-            float* row = logits + g * p.chunk;
+            float* row = logits + g * lstride;
             float mx = -FLT_MAX;
             for (int i = tid; i < n; i += kMhaThreads) mx = fmaxf(mx, row[i]);
             mx = block_max(mx, red_s);
             float sum = 0.f;
             for (int i = tid; i < n; i += kMhaThreads) {
-                const float e = expf(row[i] - mx);
+                const float e = exp_for<T>(row[i] - mx);
                 row[i] = e;
                 sum += e;
             }
@@ -422,61 +491,156 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     __syncthreads();
 
     // ---- numerators x V ----------------------------------------------------------------------------------
-    float acc[GT][E];
+    float* part = dyn_s;  // [warps][GT][D] once every thread is done with the numerators
+    if constexpr (kMmaPV) {
+        // out^T [d x heads] = V^T [d x keys] * P^T [keys x heads] on the tensor cores.  A warp takes
+        // 16 rows of the tile; ldmatrix (transposing) turns them into the A fragments of the eight
+        // 16-wide blocks of d.  The numerators (fp32, at most 1) go in as the B operand split into
+        // a half and the half of the remainder, so the products carry about 22 bits of p.
+        const int g = lane >> 2, t = lane & 3;
+        float acc[8][4];
 #pragma unroll
-    for (int g = 0; g < GT; ++g)
+        for (int blk = 0; blk < 8; ++blk)
 #pragma unroll
-        for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
-    const uint4* vrows = reinterpret_cast<const uint4*>(p.v_cache) + (cache_row0 + s0) * LPK + lk;
-    for (int base = 0, tile = nt; base < n_cache; base += KPI * U, ++tile) {
-        const bool landed = acquire_tile(tile);
-        const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + (tile % kStages) * kStageBytes);
-        uint4 raw[U];
+            for (int c = 0; c < 4; ++c) acc[blk][c] = 0.f;
+        // Which rows of the tile a warp takes is free as long as the numerators follow: k-slot s
+        // (0..7) of this warp stands for tile row 8s + 2 warp, slot 8 + s for row 8s + 2 warp + 1,
+        // so the eight rows of every 8x8 matrix come from the eight groups of the tile.
+        auto tile_offset = [&](int row) { return (row >> 3) * kGroupBytes + (row & 7) * kRowBytes; };
+        const int ld_row = 8 * (lane & 7) + 2 * warp + ((lane >> 4) & 1);  // the row this lane addresses
+        const int ld_off = tile_offset(ld_row) + ((lane >> 3) & 1) * 16;    // and its half of a 16-wide block of d
+        const int p_row = 16 * t + 2 * warp;  // rows p_row, +1 (slots 2t, 2t+8) and p_row + 8, +9 (slots 2t+1, 2t+9)
+        for (int base = 0, tile = nt; base < n_cache; base += kStageRows, ++tile) {
+            const bool landed = acquire_tile(tile);
+            unsigned char* stage = stage_base + ring_slot * kStageStride;
+            const int rows_valid = min(kStageRows, n_cache - base);
+            const bool compute = landed && 2 * warp < rows_valid;
+            uint32_t a[8][4], bh[2] = {0u, 0u}, bl[2] = {0u, 0u};
+            if (compute) {
+                if (rows_valid < kStageRows) {  // this warp's rows past the end of the chunk hold stale bytes
+                    for (int idx = lane; idx < 16 * LPK; idx += 32) {
+                        const int slot = idx / LPK, r = 8 * (slot & 7) + 2 * warp + (slot >> 3);
+                        if (r >= rows_valid)
+                            *reinterpret_cast<uint4*>(stage + tile_offset(r) + (idx % LPK) * 16) = make_uint4(0, 0, 0, 0);
+                    }
+                    __syncwarp();
+                }
+                if (g < GT) {
+                    const float* prow = logits + g * lstride + base + p_row;
+                    const bool full = p_row + 9 < rows_valid;
+                    float2 lo = make_float2(0.f, 0.f), hi = make_float2(0.f, 0.f);  // rows (p_row, +1), (p_row + 8, +9)
+                    if (full) {
+                        lo = *reinterpret_cast<const float2*>(prow);
+                        hi = *reinterpret_cast<const float2*>(prow + 8);
+                    } else {
+                        if (p_row < rows_valid) lo.x = prow[0];
+                        if (p_row + 1 < rows_valid) lo.y = prow[1];
+                        if (p_row + 8 < rows_valid) hi.x = prow[8];
+                        if (p_row + 9 < rows_valid) hi.y = prow[9];
+                    }
+                    // register 0: slots 2t, 2t+1 = rows p_row, p_row + 8; register 1: slots 2t+8, 2t+9
+                    const __half2 h0 = __floats2half2_rn(lo.x, hi.x), h1 = __floats2half2_rn(lo.y, hi.y);
+                    const float2 b0 = __half22float2(h0), b1 = __half22float2(h1);
+                    bh[0] = *reinterpret_cast<const uint32_t*>(&h0);
+                    bh[1] = *reinterpret_cast<const uint32_t*>(&h1);
+                    bl[0] = pack_half2(lo.x - b0.x, hi.x - b0.y);
+                    bl[1] = pack_half2(lo.y - b1.x, hi.y - b1.y);
+                }
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int i = base + u * KPI + ks;
-            if (STAGED)
-                raw[u] = i < n_cache ? stage_v[(u * KPI + ks) * LPK + lk] : make_uint4(0, 0, 0, 0);
-            else
-                raw[u] = i < n_cache ? ld_stream(vrows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
-        }
-        if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
+                for (int blk = 0; blk < 8; ++blk) ldmatrix_x4_trans(a[blk], stage + ld_off + blk * 32);
+            }
+            if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
+            if (compute) {
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-            const int i = base + u * KPI + ks;
-            Unpacked<T> vf;
-            unpack(raw[u], vf);
+                for (int blk = 0; blk < 8; ++blk)
+                    mma_16x8x16(acc[blk], a[blk][0], a[blk][1], a[blk][2], a[blk][3], bh[0], bh[1]);
 #pragma unroll
-            for (int g = 0; g < GT; ++g) {
-                const float w = i < n_cache ? logits[g * p.chunk + i] : 0.f;
-#pragma unroll
-                for (int e = 0; e < E; ++e) acc[g][e] = fmaf(w, vf.v[e], acc[g][e]);
+                for (int blk = 0; blk < 8; ++blk)
+                    mma_16x8x16(acc[blk], a[blk][0], a[blk][1], a[blk][2], a[blk][3], bl[0], bl[1]);
             }
         }
-    }
-    if (has_last && ks == 0) {
+        // acc[blk][0], [1]: d = 16 blk + g, heads 2t, 2t+1; [2], [3]: d = 16 blk + g + 8
+        const int ha = 2 * t, hb = 2 * t + 1;
+        if (has_last && warp == 0) {
+            const float wa = ha < GT ? logits[ha * lstride + (last - s0)] : 0.f;
+            const float wb = hb < GT ? logits[hb * lstride + (last - s0)] : 0.f;
 #pragma unroll
-        for (int g = 0; g < GT; ++g) {
-            const float w = logits[g * p.chunk + (last - s0)];
-#pragma unroll
-            for (int e = 0; e < E; ++e) acc[g][e] = fmaf(w, vnew_s[lk * E + e], acc[g][e]);
+            for (int blk = 0; blk < 8; ++blk) {
+                const float v0 = vnew_s[16 * blk + g], v1 = vnew_s[16 * blk + g + 8];
+                acc[blk][0] = fmaf(wa, v0, acc[blk][0]);
+                acc[blk][1] = fmaf(wb, v0, acc[blk][1]);
+                acc[blk][2] = fmaf(wa, v1, acc[blk][2]);
+                acc[blk][3] = fmaf(wb, v1, acc[blk][3]);
+            }
         }
-    }
-    // rows held by the other lane groups of this warp, then by the other warps
+        __syncthreads();  // every thread is done with the numerators
 #pragma unroll
-    for (int g = 0; g < GT; ++g)
-#pragma unroll
-        for (int e = 0; e < E; ++e)
-#pragma unroll
-            for (int o = LPK; o < 32; o <<= 1) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], o);
-    __syncthreads();  // every thread is done with the numerators: the buffer becomes [warps][GT][D]
-    float* part = dyn_s;
-    constexpr int kLanesUsed = LPK < 32 ? LPK : 32;  // lanes 0..LPK-1 of a warp hold its sums
-    if (lane < kLanesUsed) {
+        for (int blk = 0; blk < 8; ++blk) {
+            if (ha < GT) {
+                part[(warp * GT + ha) * D + 16 * blk + g] = acc[blk][0];
+                part[(warp * GT + ha) * D + 16 * blk + g + 8] = acc[blk][2];
+            }
+            if (hb < GT) {
+                part[(warp * GT + hb) * D + 16 * blk + g] = acc[blk][1];
+                part[(warp * GT + hb) * D + 16 * blk + g + 8] = acc[blk][3];
+            }
+        }
+    } else {
+        float acc[GT][E];
 #pragma unroll
         for (int g = 0; g < GT; ++g)
 #pragma unroll
-            for (int e = 0; e < E; ++e) part[(warp * GT + g) * D + lane * E + e] = acc[g][e];
+            for (int e = 0; e < E; ++e) acc[g][e] = 0.f;
+        const uint4* vrows = reinterpret_cast<const uint4*>(p.v_cache) + (cache_row0 + s0) * LPK + lk;
+        for (int base = 0, tile = nt; base < n_cache; base += KPI * U, ++tile) {
+            const bool landed = acquire_tile(tile);
+            const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + ring_slot * kStageStride);
+            uint4 raw[U];
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = base + u * KPI + ks;
+                if (STAGED)
+                    raw[u] = i < n_cache ? stage_v[(u * KPI + ks) * LPK + lk] : make_uint4(0, 0, 0, 0);
+                else
+                    raw[u] = i < n_cache ? ld_stream(vrows + static_cast<int64_t>(i) * LPK) : make_uint4(0, 0, 0, 0);
+            }
+            if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+                const int i = base + u * KPI + ks;
+                Unpacked<T> vf;
+                unpack(raw[u], vf);
+#pragma unroll
+                for (int g = 0; g < GT; ++g) {
+                    const float w = i < n_cache ? logits[g * lstride + i] : 0.f;
+#pragma unroll
+                    for (int e = 0; e < E; ++e) acc[g][e] = fmaf(w, vf.v[e], acc[g][e]);
+                }
+            }
+        }
+        if (has_last && ks == 0) {
+#pragma unroll
+            for (int g = 0; g < GT; ++g) {
+                const float w = logits[g * lstride + (last - s0)];
+#pragma unroll
+                for (int e = 0; e < E; ++e) acc[g][e] = fmaf(w, vnew_s[lk * E + e], acc[g][e]);
+            }
+        }
+        // rows held by the other lane groups of this warp, then by the other warps
+#pragma unroll
+        for (int g = 0; g < GT; ++g)
+#pragma unroll
+            for (int e = 0; e < E; ++e)
+#pragma unroll
+                for (int o = LPK; o < 32; o <<= 1) acc[g][e] += __shfl_xor_sync(0xffffffffu, acc[g][e], o);
+        __syncthreads();  // every thread is done with the numerators: the buffer becomes [warps][GT][D]
+        constexpr int kLanesUsed = LPK < 32 ? LPK : 32;  // lanes 0..LPK-1 of a warp hold its sums
+        if (lane < kLanesUsed) {
+#pragma unroll
+            for (int g = 0; g < GT; ++g)
+#pragma unroll
+                for (int e = 0; e < E; ++e) part[(warp * GT + g) * D + lane * E + e] = acc[g][e];
+        }
     }
     __syncthreads();
     for (int idx = tid; idx < GT * D; idx += kMhaThreads) {
@@ -520,16 +684,18 @@ decoder_mha_combine_kernel(T* __restrict__ out, const float* __restrict__ worksp
 constexpr int kChunkFloatsDefault = 8192;    // logits floats per CTA without opting in to large shared memory
 constexpr int kChunkFloatsMax = 40960;       // with the opt-in (160 KB)
 
-int pick_group(int64_t q_per_kv) {
-    const int cap = tune(kTuneMhaGroup, 4);
-    for (int g : {4, 2}) if (g <= cap && q_per_kv % g == 0) return g;
+// q heads of one kv head per CTA.  Eight only where both products run on the tensor cores (half
+// rows of 128); with FMA products a group of eight is bound by instruction issue.
+int pick_group(int64_t q_per_kv, bool tensor_cores) {
+    const int cap = tune(kTuneMhaGroup, 8);
+    for (int g : {8, 4, 2})
+        if (g <= cap && q_per_kv % g == 0 && (g < 8 || tensor_cores)) return g;
     return 1;
 }
 
 // Positions per chunk and number of chunks for one (b, kv head, head group).
-void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, bool have_workspace, int* chunk,
-                 int* splits) {
-    const int gt = pick_group(heads / kv_heads);
+void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, bool have_workspace, int gt,
+                 int* chunk, int* splits) {
     const int64_t base_ctas = batch * kv_heads * (heads / kv_heads / gt);
     int64_t want = 1;
     if (have_workspace) {
@@ -538,7 +704,8 @@ void plan_chunks(int64_t batch, int64_t heads, int64_t kv_heads, int64_t step, b
         // chunks as reach two CTAs per SM, down to 128 positions each.
         const int sms = sm_count() > 0 ? sm_count() : 148;
         const int64_t enough = static_cast<int64_t>(tune(kTuneMhaCtasPerSm, 1)) * sms;
-        const int64_t big = tune(kTuneMhaChunk, 1024), small = 128;
+        // (512 with eight heads per CTA: their numerators then leave room for three CTAs per SM)
+        const int64_t big = tune(kTuneMhaChunk, gt >= 8 ? 512 : 1024), small = 128;
         want = ceil_div(step, big);
         if (base_ctas * want < enough) want = std::min(ceil_div(2 * enough, base_ctas), std::max<int64_t>(1, step / small));
         want = std::max<int64_t>(want, ceil_div(step, static_cast<int64_t>(kChunkFloatsDefault / gt)));
@@ -553,8 +720,11 @@ template <typename T, int LPK, int GT, int U, bool STAGED>
 int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, cudaStream_t st) {
     constexpr int D = LPK * VecTraits<T>::kElems;
     auto kernel = decoder_mha_kernel<T, LPK, GT, U, STAGED>;
-    const size_t floats = std::max<size_t>(static_cast<size_t>(GT) * p.chunk, static_cast<size_t>(kMhaWarps) * GT * D);
-    const size_t smem = floats * sizeof(float) + (STAGED ? static_cast<size_t>(kStages) * 16384 : 0);
+    constexpr bool kPadded = STAGED && std::is_same<T, __half>::value && LPK == 16 && GT >= kPvTensorMinGroup;  // the kernel's kMmaPV
+    const size_t floats = std::max<size_t>(static_cast<size_t>(GT) * (p.chunk + (kPadded ? 8 : 0)),
+                                           static_cast<size_t>(kMhaWarps) * GT * D);
+    const size_t stage = 16384 + (kPadded ? 8 * 16 : 0);
+    const size_t smem = floats * sizeof(float) + (STAGED ? static_cast<size_t>(kStages) * stage : 0);
     if (smem > 40 * 1024) {
         if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
             cudaGetLastError();
@@ -582,6 +752,8 @@ int launch_mha_group(const MhaParams<T>& p, const RopeAngles& angles, int gt, in
         }
     }
 #endif
+    if constexpr (std::is_same<T, __half>::value && LPK == 16)
+        if (gt == 8) return launch_mha<T, LPK, 8, 8, true>(p, angles, batch, st);
     switch (gt) {
         case 4: return launch_mha<T, LPK, 4, 8, true>(p, angles, batch, st);
         case 2: return launch_mha<T, LPK, 2, 8, true>(p, angles, batch, st);
@@ -612,13 +784,13 @@ int mha_dispatch(T* out, const T* qkv, const T* bias, T* k_cache, T* v_cache, in
     if (!aligned16(k_cache) || !aligned16(v_cache)) return fail(ISPORE_EALIGN, "decoder_masked_mha: caches must be 16-byte aligned");
 
     MhaParams<T> p;
-    const int gt = pick_group(heads / kv_heads);
+    const int gt = pick_group(heads / kv_heads, std::is_same<T, __half>::value && lpk == 16);
     int chunk = 0, splits = 1;
-    plan_chunks(batch, heads, kv_heads, step, workspace != nullptr, &chunk, &splits);
+    plan_chunks(batch, heads, kv_heads, step, workspace != nullptr, gt, &chunk, &splits);
     const int64_t need = splits > 1 ? batch * heads * splits * (head_size + 2) * static_cast<int64_t>(sizeof(float)) : 0;
     if (need > workspace_bytes || (splits > 1 && (reinterpret_cast<uintptr_t>(workspace) & 3) != 0)) {
         // workspace too small for the plan: fall back to one chunk per (b, head) if shared memory can hold it
-        plan_chunks(batch, heads, kv_heads, step, false, &chunk, &splits);
+        plan_chunks(batch, heads, kv_heads, step, false, gt, &chunk, &splits);
     }
     if (static_cast<int64_t>(chunk) * gt > kChunkFloatsMax)
         return fail(ISPORE_ESCRATCH, "decoder_masked_mha: step %lld needs a workspace of %lld bytes",
@@ -663,9 +835,16 @@ int64_t ispore_decoder_masked_mha_workspace_bytes(int64_t batch_size, int64_t he
                                                   int64_t head_size, int64_t step) {
     if (batch_size <= 0 || head_num <= 0 || kv_head_num <= 0 || head_num % kv_head_num != 0 || head_size <= 0 || step <= 0)
         return 0;
-    int chunk = 0, splits = 1;
-    ispore::plan_chunks(batch_size, head_num, kv_head_num, step, true, &chunk, &splits);
-    return splits > 1 ? batch_size * head_num * splits * (head_size + 2) * static_cast<int64_t>(sizeof(float)) : 0;
+    // The plan depends on the head group, which depends on the element type: enough for either.
+    int64_t bytes = 0;
+    for (bool tensor_cores : {false, true}) {
+        int chunk = 0, splits = 1;
+        const int gt = ispore::pick_group(head_num / kv_head_num, tensor_cores && head_size == 128);
+        ispore::plan_chunks(batch_size, head_num, kv_head_num, step, true, gt, &chunk, &splits);
+        if (splits > 1)
+            bytes = std::max(bytes, batch_size * head_num * splits * (head_size + 2) * static_cast<int64_t>(sizeof(float)));
+    }
+    return bytes;
 }
 
 int ispore_decoder_masked_mha_f32(float* mha_output, const float* qkv_buf, const float* qkv_bias, float* k_cache,

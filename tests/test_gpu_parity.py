@@ -705,6 +705,11 @@ MHA_CASES = [
     (1, 4, 4, 128, 5000, 4100, 128, True, False),   # the same in one CTA per head
     (2, 4, 4, 32, 70, 1, 0, False, False),          # first token: the cache holds nothing yet
     (2, 2, 1, 256, 50, 50, 256, True, True),
+    (2, 16, 2, 128, 200, 131, 128, True, True),     # 8 q heads per kv head on rows of 128
+    (1, 8, 1, 128, 2100, 2049, 128, False, True),   # the same, chunks that end inside a 64-row tile
+    (1, 8, 1, 128, 700, 650, 64, True, False),      # the same in one CTA, partial rotation
+    (2, 8, 1, 128, 20, 1, 128, False, False),       # the same, first token
+    (1, 24, 3, 128, 90, 17, 128, False, True),      # fewer rows than one warp's share of a tile
 ]
 
 
