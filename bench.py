@@ -321,7 +321,7 @@ class GpuChain:
 
 
 NEXT_KERNELS = ["build_causal_mask", "scale_causal_softmax", "cal_padding_offset", "transpose_remove_padding",
-                "repeat_kv", "decoder_masked_mha"]
+                "repeat_kv", "decoder_masked_mha", "decoder_masked_mha_gqa8"]
 
 
 class NextRows:
@@ -382,16 +382,18 @@ class NextRows:
             nbytes = 2 * kd.numel() * 2 + 2 * bs * kvh * ctx * HEAD_SIZE * 2
             return ((lambda: o.launchRepeatKVCache(ks, vs, cl, 0, kd, vd)), nbytes,
                     f"{bs} sequences, {kvh} -> {HEADS} heads, context {ctx}, f16")
-        if name == "decoder_masked_mha":
+        if name in ("decoder_masked_mha", "decoder_masked_mha_gqa8"):
+            # the model's own 32/32 heads, and 64 q heads on 8 kv heads (eight q heads share each cache row)
+            heads, kvh = (HEADS, KV_HEADS) if name == "decoder_masked_mha" else (64, 8)
             bs, ctx = self.decode_batch, self.context
-            qkv = self._randn(bs, 3 * HEADS, HEAD_SIZE)
-            kc, vc = self._randn(1, bs, KV_HEADS, ctx, HEAD_SIZE), self._randn(1, bs, KV_HEADS, ctx, HEAD_SIZE)
-            out = t.empty((bs, HEADS, HEAD_SIZE), dtype=h, device=dev)
-            nb = o.decoderMaskedMHAWorkspaceBytes(bs, HEADS, KV_HEADS, HEAD_SIZE, ctx)
+            qkv = self._randn(bs, heads + 2 * kvh, HEAD_SIZE)
+            kc, vc = self._randn(1, bs, kvh, ctx, HEAD_SIZE), self._randn(1, bs, kvh, ctx, HEAD_SIZE)
+            out = t.empty((bs, heads, HEAD_SIZE), dtype=h, device=dev)
+            nb = o.decoderMaskedMHAWorkspaceBytes(bs, heads, kvh, HEAD_SIZE, ctx)
             ws = t.empty(max(nb, 4), dtype=t.uint8, device=dev)
-            nbytes = 2 * bs * KV_HEADS * ctx * HEAD_SIZE * 2 + qkv.numel() * 2 + out.numel() * 2
+            nbytes = 2 * bs * kvh * ctx * HEAD_SIZE * 2 + qkv.numel() * 2 + out.numel() * 2
             return ((lambda: o.launchDecoderMaskedMHA(qkv, None, 0, kc, vc, None, ctx, out, ROT_DIM, ROT_BASE, ws)), nbytes,
-                    f"{bs} sequences, {HEADS} heads, step {ctx}, f16 caches ({nb >> 10} KiB split workspace)")
+                    f"{bs} sequences, {heads} q / {kvh} kv heads, step {ctx}, f16 caches ({nb >> 10} KiB split workspace)")
         raise KeyError(name)
 
     def time_one(self, name: str, steps: int, warmup: int):

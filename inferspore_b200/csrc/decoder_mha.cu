@@ -19,13 +19,15 @@
 //     for one sequence; here the stride is (heads + 2*kv_heads)*d, the tensor's own layout;
 //   * fp16 products are accumulated in fp32 (the reference multiplies in half, :337).
 //
-// Work split: a CTA owns one (b, kv head), up to four of the q heads that share it, and one chunk
+// Work split: a CTA owns one (b, kv head), up to eight of the q heads that share it, and one chunk
 // of the positions (flash-decoding style split so that small batches still fill 148 SMs); the
 // cache rows of the chunk are read once for all heads of the group.  The rows reach the CTA
 // through a three-deep ring of 16 KB shared-memory tiles filled by TMA bulk copies (K tiles, then
 // V tiles, issued three ahead).  With several q heads on half-precision rows of 128 the q.K
 // products run on the tensor cores (mma m16n8k16, a cache tile as the A operand without any
 // shuffling); otherwise 16 lanes share a row and a halving butterfly sums the partial products.
+// With eight q heads the numerators x V product runs there too (V tiles through ldmatrix), on
+// eight warps.
 // With more than one chunk per (b, head) the CTAs leave (max, sum, unnormalised output) in a
 // workspace and a second kernel combines them.
 #include <float.h>
@@ -161,21 +163,31 @@ constexpr int kStages = 3;
 #endif
 constexpr int kPvTensorMinGroup = ISPORE_MHA_PV_MIN_GROUP;  // q heads per CTA from which numerators x V runs on the tensor cores
 
+// Both products on the tensor cores: half rows of 128, staged tiles, eight q heads per CTA.  That
+// kernel runs eight warps instead of four, so that twice as many warps hide each other's latencies
+// (q.K split by rows, numerators x V by rows and by halves of d).
+template <typename T, int LPK, int GT, bool STAGED>
+constexpr bool mha_both_on_tensor_cores() {
+    return std::is_same<T, __half>::value && LPK == 16 && STAGED && GT >= kPvTensorMinGroup;
+}
+template <typename T, int LPK, int GT, bool STAGED>
+constexpr int mha_threads() { return mha_both_on_tensor_cores<T, LPK, GT, STAGED>() ? 2 * kMhaThreads : kMhaThreads; }
+
 template <typename T, int LPK, int GT, int U, bool STAGED>
-__global__ void __launch_bounds__(kMhaThreads)
+__global__ void __launch_bounds__((mha_threads<T, LPK, GT, STAGED>()))
 decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __restrict__ status) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int D = LPK * E;
-    constexpr int KPI = kMhaThreads / LPK;  // cache rows per CTA iteration
+    constexpr int kThreads = mha_threads<T, LPK, GT, STAGED>();
+    constexpr int kWarps = kThreads / 32;
+    constexpr int KPI = kMhaThreads / LPK;  // cache rows per iteration of the FMA paths (four warps)
     constexpr int N = GT * U;               // dot products per thread per iteration (U rows in flight)
-    constexpr int kStageRows = KPI * U;     // rows per pass of the CTA = rows per shared-memory tile
+    constexpr int kStageRows = KPI * U;     // rows per pass of four warps = rows per shared-memory tile
     constexpr int kStageBytes = kStageRows * D * static_cast<int>(sizeof(T));
     static_assert(!STAGED || kStageBytes == 16384, "a staged tile is one pass of eight rows per thread");
-    // Tensor-core paths: q.K needs several heads on half rows of 128; numerators x V needs the V
-    // tile in shared memory as well, with every row padded by 16 bytes so that the eight row
-    // addresses of one ldmatrix phase fall into different banks.
+    // Tensor-core paths: q.K needs several heads on half rows of 128; numerators x V needs eight.
     constexpr bool kMmaQK = std::is_same<T, __half>::value && LPK == 16 && GT >= 2;
-    constexpr bool kMmaPV = kMmaQK && STAGED && GT >= kPvTensorMinGroup;
+    constexpr bool kMmaPV = mha_both_on_tensor_cores<T, LPK, GT, STAGED>();
     constexpr int kRowBytes = D * static_cast<int>(sizeof(T));
     // A V tile of the tensor-core path lands as eight groups of eight rows, each group 16 bytes
     // further along than rows alone would put it: the eight rows one ldmatrix phase reads are taken
@@ -186,7 +198,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     __shared__ float q_s[GT][D];
     __shared__ float knew_s[D], vnew_s[D];
     __shared__ float2 cs_s[kMaxRotPairs];
-    __shared__ float red_s[kMhaWarps];
+    __shared__ float red_s[kWarps];
     __shared__ float m_s[GT], l_s[GT];
     __shared__ __align__(8) uint64_t full[kStages];
     extern __shared__ __align__(128) unsigned char dyn_raw[];  // [tiles when STAGED][logits / output reduction buffer]
@@ -211,9 +223,8 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
 
     // Tiles 0 .. nt-1 are K rows, nt .. 2nt-1 the same rows of V.
     const int nt = (n_cache + kStageRows - 1) / kStageRows;
-    // Called by every thread.  K tiles (and V tiles of the FMA path) are one contiguous copy issued
-    // by thread 0; a V tile of the tensor-core path is one copy per group of rows, each issued by
-    // its own thread.
+    // K tiles (and V tiles of the FMA path) are one contiguous copy issued by thread 0; a V tile
+    // of the tensor-core path is one copy per group of rows, issued by threads 0..7.
     int ring_slot = 0;         // stage of the tile consumed next
     uint32_t ring_phase = 0;   // parity its barrier completes with
     auto issue_tile = [&](int tile, int slot) {
@@ -240,7 +251,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
             tma::fence_mbar_init();
         }
         if (kMmaPV) __syncthreads();  // other threads issue copies on these barriers too
-        if (kMmaPV || tid == 0)
+        if (tid < (kMmaPV ? kStageRows / kGroupRows : 1))
             for (int tile = 0; tile < kStages && tile < 2 * nt; ++tile) issue_tile(tile, tile);
     }
     // Waits for tile `tile`; false when the copy did not land in time (reported at release).
@@ -260,7 +271,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
             }
             return false;
         }
-        if ((kMmaPV || tid == 0) && tile + kStages < 2 * nt) issue_tile(tile + kStages, ring_slot);
+        if (tid < (kMmaPV ? kStageRows / kGroupRows : 1) && tile + kStages < 2 * nt) issue_tile(tile + kStages, ring_slot);
         if (++ring_slot == kStages) {
             ring_slot = 0;
             ring_phase ^= 1u;
@@ -269,7 +280,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     };
 
     // ---- the new token: bias, RoPE, rounding through T -------------------------------------------
-    for (int i = tid; i < p.rot_pairs; i += kMhaThreads) {
+    for (int i = tid; i < p.rot_pairs; i += kThreads) {
         float sn, cs;
         sincosf(p.rope_t / angles.denom[i], &sn, &cs);
         cs_s[i] = make_float2(cs, sn);
@@ -278,7 +289,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     const int qkv_heads = p.heads + 2 * p.kv_heads;
     const T* tok = p.qkv + static_cast<int64_t>(b) * qkv_heads * D;
     const int rope_rows = GT + (has_last ? 1 : 0);  // q heads, then k
-    for (int idx = tid; idx < rope_rows * (D / 2); idx += kMhaThreads) {
+    for (int idx = tid; idx < rope_rows * (D / 2); idx += kThreads) {
         const int r = idx / (D / 2), i = idx - r * (D / 2);
         const int row = r < GT ? h0 + r : p.heads + kvh;
         float x0 = to_float<T>(tok[row * D + 2 * i]), x1 = to_float<T>(tok[row * D + 2 * i + 1]);
@@ -298,7 +309,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     }
     if (has_last) {
         const int row = p.heads + p.kv_heads + kvh;
-        for (int i = tid; i < D; i += kMhaThreads) {
+        for (int i = tid; i < D; i += kThreads) {
             float x = to_float<T>(tok[row * D + i]);
             if (p.bias != nullptr) x = round_to<T>(x + to_float<T>(p.bias[row * D + i]));
             vnew_s[i] = x;
@@ -308,7 +319,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     if (has_last && hg == 0) {  // one writer per (b, kv head)
         T* kd = p.k_cache + (cache_row0 + last) * D;
         T* vd = p.v_cache + (cache_row0 + last) * D;
-        for (int i = tid; i < D; i += kMhaThreads) {
+        for (int i = tid; i < D; i += kThreads) {
             kd[i] = from_float<T>(knew_s[i]);
             vd[i] = from_float<T>(vnew_s[i]);
         }
@@ -336,22 +347,26 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
                 bq[j][sft][1] = g < GT ? pack_half2(qrow[d0 + 2], qrow[d0 + 3]) : 0u;
             }
         const uint4* kbase = reinterpret_cast<const uint4*>(p.k_cache) + (cache_row0 + s0) * LPK;
-        static_assert(!STAGED || kStageRows == kMhaWarps * 16, "one staged tile is 16 rows per warp");
-        constexpr int kRowsPerIter = kMhaWarps * 16;
-        for (int tile_row = 0, tile = 0; tile_row < n_cache; tile_row += kRowsPerIter, ++tile) {
+        // Four warps take 16 rows of a tile each; eight warps take 8 each and leave rows 8..15 of
+        // their A tile zero (the tensor pipe has time to spare, the issue slots do not).
+        constexpr int kRowsPerWarp = kStageRows / kWarps;
+        static_assert(kRowsPerWarp == 16 || kRowsPerWarp == 8, "a warp's share of a tile fills an A tile or half of one");
+        constexpr bool kTwoRows = kRowsPerWarp == 16;
+        for (int tile_row = 0, tile = 0; tile_row < n_cache; tile_row += kStageRows, ++tile) {
             const bool landed = acquire_tile(tile);
-            const int l0 = warp * 16 + g, l1 = l0 + 8;  // rows inside the tile
-            const int r0 = tile_row + l0, r1 = tile_row + l1;
+            const int l0 = warp * kRowsPerWarp + g, l1 = l0 + 8;  // rows inside the tile
+            const int r0 = tile_row + l0, r1 = kTwoRows ? tile_row + l1 : n_cache;
             const uint4* stage_v = reinterpret_cast<const uint4*>(stage_base + ring_slot * kStageStride);
-            uint4 a_lo[4], a_hi[4];  // rows g and g + 8 of this warp's 16, chunks t + 4j
+            uint4 a_lo[4], a_hi[4];  // rows g and g + 8 of this warp's share, chunks t + 4j
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
+                a_hi[j] = make_uint4(0, 0, 0, 0);
                 if (STAGED) {
                     a_lo[j] = r0 < n_cache ? stage_v[l0 * LPK + t + 4 * j] : make_uint4(0, 0, 0, 0);
-                    a_hi[j] = r1 < n_cache ? stage_v[l1 * LPK + t + 4 * j] : make_uint4(0, 0, 0, 0);
+                    if (kTwoRows && r1 < n_cache) a_hi[j] = stage_v[l1 * LPK + t + 4 * j];
                 } else {
                     a_lo[j] = r0 < n_cache ? ld_stream(kbase + static_cast<int64_t>(r0) * LPK + t + 4 * j) : make_uint4(0, 0, 0, 0);
-                    a_hi[j] = r1 < n_cache ? ld_stream(kbase + static_cast<int64_t>(r1) * LPK + t + 4 * j) : make_uint4(0, 0, 0, 0);
+                    if (kTwoRows && r1 < n_cache) a_hi[j] = ld_stream(kbase + static_cast<int64_t>(r1) * LPK + t + 4 * j);
                 }
             }
             if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
@@ -369,7 +384,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
                     logits[(2 * t) * lstride + r0] = acc[0] * p.scale;
                     if (2 * t + 1 < GT) logits[(2 * t + 1) * lstride + r0] = acc[1] * p.scale;
                 }
-                if (r1 < n_cache) {
+                if (kTwoRows && r1 < n_cache) {
                     logits[(2 * t) * lstride + r1] = acc[2] * p.scale;
                     if (2 * t + 1 < GT) logits[(2 * t + 1) * lstride + r1] = acc[3] * p.scale;
                 }
@@ -434,10 +449,10 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     __syncthreads();
 
     // ---- softmax numerators over the chunk ----------------------------------------------------------
-    if constexpr (GT % kMhaWarps == 0) {
+    if constexpr (GT % kWarps == 0) {
         // a warp per head (two when eight heads share the rows): warp reductions only, no block
         // barrier until all heads are done
-        for (int hh = warp; hh < GT; hh += kMhaWarps) {
+        for (int hh = warp; hh < GT; hh += kWarps) {
             float* row = logits + hh * lstride;  // 16-byte aligned: chunk and the row pad are multiples of 4 floats
             const int n4 = n & ~3;
             float mx = -FLT_MAX;
@@ -473,10 +488,10 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
         for (int g = 0; g < GT; ++g) {
             float* row = logits + g * lstride;
             float mx = -FLT_MAX;
-            for (int i = tid; i < n; i += kMhaThreads) mx = fmaxf(mx, row[i]);
+            for (int i = tid; i < n; i += kThreads) mx = fmaxf(mx, row[i]);
             mx = block_max(mx, red_s);
             float sum = 0.f;
-            for (int i = tid; i < n; i += kMhaThreads) {
+            for (int i = tid; i < n; i += kThreads) {
                 const float e = exp_for<T>(row[i] - mx);
                 row[i] = e;
                 sum += e;
@@ -491,37 +506,42 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     __syncthreads();
 
     // ---- numerators x V ----------------------------------------------------------------------------------
-    float* part = dyn_s;  // [warps][GT][D] once every thread is done with the numerators
+    float* part = dyn_s;  // [four partial sums][GT][D] once every thread is done with the numerators
     if constexpr (kMmaPV) {
-        // out^T [d x heads] = V^T [d x keys] * P^T [keys x heads] on the tensor cores.  A warp takes
-        // 16 rows of the tile; ldmatrix (transposing) turns them into the A fragments of the eight
-        // 16-wide blocks of d.  The numerators (fp32, at most 1) go in as the B operand split into
-        // a half and the half of the remainder, so the products carry about 22 bits of p.
+        // out^T [d x heads] = V^T [d x keys] * P^T [keys x heads] on the tensor cores.  Warp w takes
+        // the 16 rows of key group w % 4 and half w / 4 of d: ldmatrix (transposing) turns the rows
+        // into the A fragments of its four 16-wide blocks of d.  The numerators (fp32, at most 1)
+        // go in as the B operand split into a half and the half of the remainder, so the products
+        // carry about 22 bits of p.
+        static_assert(kWarps == 8, "two warps per key group");
+        constexpr int kBlocks = 4;  // 16-wide blocks of d per warp
         const int g = lane >> 2, t = lane & 3;
-        float acc[8][4];
+        const int kg = warp & 3, dh = warp >> 2;
+        float acc[kBlocks][4];
 #pragma unroll
-        for (int blk = 0; blk < 8; ++blk)
+        for (int blk = 0; blk < kBlocks; ++blk)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[blk][c] = 0.f;
-        // Which rows of the tile a warp takes is free as long as the numerators follow: k-slot s
-        // (0..7) of this warp stands for tile row 8s + 2 warp, slot 8 + s for row 8s + 2 warp + 1,
-        // so the eight rows of every 8x8 matrix come from the eight groups of the tile.
+        // Which rows of the tile a key group takes is free as long as the numerators follow: k-slot
+        // s (0..7) stands for tile row 8s + 2 kg, slot 8 + s for row 8s + 2 kg + 1, so the eight
+        // rows of every 8x8 matrix come from the eight groups of the tile.
         auto tile_offset = [&](int row) { return (row >> 3) * kGroupBytes + (row & 7) * kRowBytes; };
-        const int ld_row = 8 * (lane & 7) + 2 * warp + ((lane >> 4) & 1);  // the row this lane addresses
-        const int ld_off = tile_offset(ld_row) + ((lane >> 3) & 1) * 16;    // and its half of a 16-wide block of d
-        const int p_row = 16 * t + 2 * warp;  // rows p_row, +1 (slots 2t, 2t+8) and p_row + 8, +9 (slots 2t+1, 2t+9)
+        const int ld_row = 8 * (lane & 7) + 2 * kg + ((lane >> 4) & 1);                          // the row this lane addresses
+        const int ld_off = tile_offset(ld_row) + ((lane >> 3) & 1) * 16 + dh * kBlocks * 32;     // and its columns
+        const int p_row = 16 * t + 2 * kg;  // rows p_row, +1 (slots 2t, 2t+8) and p_row + 8, +9 (slots 2t+1, 2t+9)
         for (int base = 0, tile = nt; base < n_cache; base += kStageRows, ++tile) {
             const bool landed = acquire_tile(tile);
             unsigned char* stage = stage_base + ring_slot * kStageStride;
             const int rows_valid = min(kStageRows, n_cache - base);
-            const bool compute = landed && 2 * warp < rows_valid;
-            uint32_t a[8][4], bh[2] = {0u, 0u}, bl[2] = {0u, 0u};
+            const bool compute = landed && 2 * kg < rows_valid;
+            uint32_t a[kBlocks][4], bh[2] = {0u, 0u}, bl[2] = {0u, 0u};
             if (compute) {
-                if (rows_valid < kStageRows) {  // this warp's rows past the end of the chunk hold stale bytes
-                    for (int idx = lane; idx < 16 * LPK; idx += 32) {
-                        const int slot = idx / LPK, r = 8 * (slot & 7) + 2 * warp + (slot >> 3);
+                if (rows_valid < kStageRows) {  // this warp's rows and columns past the end of the chunk hold stale bytes
+                    for (int idx = lane; idx < 16 * (LPK / 2); idx += 32) {
+                        const int slot = idx / (LPK / 2), r = 8 * (slot & 7) + 2 * kg + (slot >> 3);
                         if (r >= rows_valid)
-                            *reinterpret_cast<uint4*>(stage + tile_offset(r) + (idx % LPK) * 16) = make_uint4(0, 0, 0, 0);
+                            *reinterpret_cast<uint4*>(stage + tile_offset(r) + (dh * (LPK / 2) + idx % (LPK / 2)) * 16) =
+                                make_uint4(0, 0, 0, 0);
                     }
                     __syncwarp();
                 }
@@ -547,42 +567,44 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
                     bl[1] = pack_half2(lo.y - b1.x, hi.y - b1.y);
                 }
 #pragma unroll
-                for (int blk = 0; blk < 8; ++blk) ldmatrix_x4_trans(a[blk], stage + ld_off + blk * 32);
+                for (int blk = 0; blk < kBlocks; ++blk) ldmatrix_x4_trans(a[blk], stage + ld_off + blk * 32);
             }
             if (!release_tile(tile, landed)) return;  // the tile is in registers: its stage can be refilled
             if (compute) {
 #pragma unroll
-                for (int blk = 0; blk < 8; ++blk)
+                for (int blk = 0; blk < kBlocks; ++blk)
                     mma_16x8x16(acc[blk], a[blk][0], a[blk][1], a[blk][2], a[blk][3], bh[0], bh[1]);
 #pragma unroll
-                for (int blk = 0; blk < 8; ++blk)
+                for (int blk = 0; blk < kBlocks; ++blk)
                     mma_16x8x16(acc[blk], a[blk][0], a[blk][1], a[blk][2], a[blk][3], bl[0], bl[1]);
             }
         }
-        // acc[blk][0], [1]: d = 16 blk + g, heads 2t, 2t+1; [2], [3]: d = 16 blk + g + 8
+        // acc[blk][0], [1]: d = d_first + 16 blk + g, heads 2t, 2t+1; [2], [3]: the same d + 8
         const int ha = 2 * t, hb = 2 * t + 1;
-        if (has_last && warp == 0) {
+        const int d_first = dh * kBlocks * 16;
+        if (has_last && kg == 0) {
             const float wa = ha < GT ? logits[ha * lstride + (last - s0)] : 0.f;
             const float wb = hb < GT ? logits[hb * lstride + (last - s0)] : 0.f;
 #pragma unroll
-            for (int blk = 0; blk < 8; ++blk) {
-                const float v0 = vnew_s[16 * blk + g], v1 = vnew_s[16 * blk + g + 8];
+            for (int blk = 0; blk < kBlocks; ++blk) {
+                const float v0 = vnew_s[d_first + 16 * blk + g], v1 = vnew_s[d_first + 16 * blk + g + 8];
                 acc[blk][0] = fmaf(wa, v0, acc[blk][0]);
                 acc[blk][1] = fmaf(wb, v0, acc[blk][1]);
                 acc[blk][2] = fmaf(wa, v1, acc[blk][2]);
                 acc[blk][3] = fmaf(wb, v1, acc[blk][3]);
             }
         }
-        __syncthreads();  // every thread is done with the numerators
+        __syncthreads();  // every thread is done with the numerators: the buffer becomes [key groups][GT][D]
 #pragma unroll
-        for (int blk = 0; blk < 8; ++blk) {
+        for (int blk = 0; blk < kBlocks; ++blk) {
+            const int dd = d_first + 16 * blk + g;
             if (ha < GT) {
-                part[(warp * GT + ha) * D + 16 * blk + g] = acc[blk][0];
-                part[(warp * GT + ha) * D + 16 * blk + g + 8] = acc[blk][2];
+                part[(kg * GT + ha) * D + dd] = acc[blk][0];
+                part[(kg * GT + ha) * D + dd + 8] = acc[blk][2];
             }
             if (hb < GT) {
-                part[(warp * GT + hb) * D + 16 * blk + g] = acc[blk][1];
-                part[(warp * GT + hb) * D + 16 * blk + g + 8] = acc[blk][3];
+                part[(kg * GT + hb) * D + dd] = acc[blk][1];
+                part[(kg * GT + hb) * D + dd + 8] = acc[blk][3];
             }
         }
     } else {
@@ -643,11 +665,11 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
         }
     }
     __syncthreads();
-    for (int idx = tid; idx < GT * D; idx += kMhaThreads) {
+    for (int idx = tid; idx < GT * D; idx += kThreads) {
         const int g = idx / D, dd = idx - g * D;
         float o = 0.f;
 #pragma unroll
-        for (int w = 0; w < kMhaWarps; ++w) o += part[(w * GT + g) * D + dd];
+        for (int w = 0; w < kMhaWarps; ++w) o += part[(w * GT + g) * D + dd];  // four partial sums in either variant
         const int64_t bh = static_cast<int64_t>(b) * p.heads + h0 + g;
         if (p.splits == 1) {
             p.out[bh * D + dd] = from_float<T>(o / (l_s[g] + 1e-6f));
@@ -734,7 +756,7 @@ int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, c
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "decoder_masked_mha: no device status word");
     dim3 grid(static_cast<unsigned>(batch * p.kv_heads * p.head_groups), static_cast<unsigned>(p.splits));
-    kernel<<<grid, kMhaThreads, smem, st>>>(p, angles, status);
+    kernel<<<grid, mha_threads<T, LPK, GT, STAGED>(), smem, st>>>(p, angles, status);
     int rc = check_launch("decoder_mha_kernel");
     if (rc != ISPORE_OK || p.splits == 1) return rc;
     decoder_mha_combine_kernel<T><<<static_cast<unsigned>(batch * p.heads), 128, 0, st>>>(p.out, p.workspace, p.splits, D);
