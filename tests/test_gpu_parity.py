@@ -872,3 +872,42 @@ def test_softmax_rows_not_16_byte_aligned_in_place(ops, orc, rng, case, dtype):
         assert over == 0
     else:
         assert_close_f32(host(d), want, floor=1e-30, what="unaligned softmax f32")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("k_len", [9, 15, 17, 31, 255, 263, 513, 777, 1023, 1029, 2047, 3001, 4099, 6143, 8191, 12289, 20001])
+def test_softmax_any_row_length_random_mask(ops, orc, rng, k_len, dtype):
+    # the mask row and the qk row of a (b, h, q) start at different offsets inside their aligned
+    # vectors; 3 heads x 3 q rows x 2 sequences go through every relative shift for odd k_len, and
+    # a random 0/1 mask shows any element that was paired with the wrong mask entry
+    batch, heads, q_len = 2, 3, 3
+    qk = (rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32) * 3).astype(dtype)
+    mask = (rng.random((batch, q_len, k_len)) < 0.6).astype(dtype)
+    mask[1, 1] = 0  # a fully masked row
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    out = torch.full(qk.shape, 7.0, dtype=tdt, device="cuda:0")
+    ops.launchScaleMaskAndSoftmax(dev(qk), dev(mask), out, 0.3)
+    want, want32 = orc.scale_mask_softmax(qk, mask, np.float32(0.3))
+    if dtype == np.float16:
+        err, over, _ = assert_close_f16(host(out), want32, want, "softmax f16, any row length")
+        assert over == 0
+    else:
+        assert_close_f32(host(out), want, floor=1e-30, what="softmax f32, any row length")
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("case", [(3, 5, 9, 45), (2, 3, 11, 333), (1, 2, 5, 1501), (1, 1, 3, 5003)])
+def test_causal_softmax_any_row_length(ops, orc, rng, case, dtype):
+    batch, heads, q_len, k_len = case
+    qk = (rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32) * 3).astype(dtype)
+    ql = rng.integers(1, q_len + 1, batch)
+    kl = np.minimum(ql + rng.integers(0, k_len + 1, batch), k_len)
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    d = dev(qk)
+    ops.launchScaleCausalSoftmax(d, _i32(ql), _i32(kl), d, 0.2)  # in place
+    want, want32 = orc.scale_mask_softmax(qk, orc.build_causal_mask(ql, kl, q_len, k_len, dtype), np.float32(0.2))
+    if dtype == np.float16:
+        err, over, _ = assert_close_f16(host(d), want32, want, "causal softmax f16, any row length")
+        assert over == 0
+    else:
+        assert_close_f32(host(d), want, floor=1e-30, what="causal softmax f32, any row length")
