@@ -529,17 +529,17 @@ int launch_groups(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch,
 }
 
 // Rows of any length in 16-byte aligned buffers, without shared memory: a group (a warp, or the
-// CTA for long rows) takes one row of the flat [rows, k_len] array and walks the aligned vectors
-// that cover it.  The elements of the neighbouring rows at both ends are turned into -FLT_MAX
-// (they vanish from the max and the sum) and only those two vectors are stored element by
-// element.  The mask row of (b, q) starts at another element offset than the qk row: the two
-// aligned mask vectors that hold a qk vector's eight (four) positions are loaded and shifted
-// into place in registers — the shift is the same for the whole row, so one uniform switch per
-// row picks the load routine.  The first and last mask rows and the last qk row, whose covering
-// vectors would reach outside the buffers, take a plain element-wise path.
-// The kernel is bound by instruction issue, so the trips are kept free of guards: the launch
-// shape guarantees that only a thread's last vector can lie past the row, and the two ragged
-// vectors of a row are found by one bit test per trip.
+// CTA for long rows) takes one row.  The whole aligned vectors inside the row go through the
+// vector trips; the up to E-1 elements in front of the first one and the up to E-1 behind the
+// last one (they share their vectors with the neighbouring rows) are taken one per lane by the
+// first lanes of the group, loaded and stored as single elements.  The mask row of (b, q) starts
+// at another element offset than the qk row: the two aligned mask vectors that hold a qk
+// vector's eight (four) positions are loaded and shifted into place in registers — the shift is
+// the same for the whole row, so one uniform switch per row picks the routine compiled for it.
+// The last mask row, whose second vector could reach past the buffer, takes a plain
+// element-wise path.  The kernel is bound by instruction issue, so the trips are kept free of
+// guards (the launch shape guarantees that only a thread's last vector can lie past the row) and
+// the grid is three-dimensional (q, head, sequence) so that no index is recovered by division.
 template <typename T, int S>
 __device__ __forceinline__ uint4 shift_into_place(const uint4& a, const uint4& b) {
     const uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
@@ -550,156 +550,116 @@ __device__ __forceinline__ uint4 shift_into_place(const uint4& a, const uint4& b
                       __funnelshift_r(w[J + 2], w[J + 3], 16), __funnelshift_r(w[J + 3], w[J + 4], 16));
 }
 
-// GROUP lanes per row: 32 (a warp; THREADS / 32 rows per CTA) or 0 = the whole CTA, whose size is
-// then chosen at launch to fit the row.
-template <typename T, int VPT, int GROUP, int THREADS, bool CAUSAL>
-__global__ void __launch_bounds__(THREADS)
-softmax_offset_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
-                          const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens, int64_t total_rows,
-                          int batch, int heads, int q_len, int k_len, float scale) {
+// Division of n < 2^31 by a divisor fixed at launch: n / d = umulhi(n, mul) >> shr with
+// mul = ceil(2^(31 + ceil(log2 d)) / d), exact because the rounding error of mul, scaled by
+// n / 2^(31 + ceil(log2 d)), stays below 1 / d.  d = 1 has mul = 0 and is passed through.
+struct InvariantDivisor {
+    uint32_t mul, shr;
+    explicit InvariantDivisor(uint32_t d) : mul(0), shr(0) {
+        if (d > 1) {
+            uint32_t l = 0;
+            while ((1ull << l) < d) ++l;
+            mul = static_cast<uint32_t>(((1ull << (31 + l)) + d - 1) / d);
+            shr = l - 1;
+        }
+    }
+    __device__ __forceinline__ uint32_t divide(uint32_t n) const { return mul == 0 ? n : __umulhi(n, mul) >> shr; }
+};
+
+template <typename T>
+struct OffsetRow {
+    T* score;
+    const T* qk;
+    const T* mask;
+    int64_t row_elem0, mrow_elem0;  // first element of the qk row and of the mask row
+    float* red_max;
+    float* red_sum;
+    int k_len, head, lo, hi, group, gt;
+    float a;
+};
+
+// One row, for a mask row whose element under the row's first whole vector sits S elements into
+// its own aligned vector.
+template <typename T, int VPT, bool kBlock, bool CAUSAL, int S>
+__device__ __forceinline__ void offset_row_fast(const OffsetRow<T>& row) {
     constexpr int E = VecTraits<T>::kElems;
-    static_assert(GROUP == 32 || GROUP == 0, "a group is a warp or the CTA");
-    constexpr bool kBlock = GROUP == 0;
     using Exp = ExpPolicy<T>;
-    __shared__ float red_max[THREADS / 32], red_sum[THREADS / 32];  // each written once per row: no barrier after the read
-    const int tid = threadIdx.x;
-    const int group = kBlock ? static_cast<int>(blockDim.x) : GROUP;
-    const int gt = kBlock ? tid : (tid & 31);
-    // flat row; 32-bit on purpose (the launcher keeps total_rows below 2^31): a 64-bit division
-    // per row would cost as much as a whole trip
-    const uint32_t r = kBlock ? blockIdx.x : blockIdx.x * (THREADS / 32) + (tid >> 5);
-    if (r >= static_cast<uint32_t>(total_rows)) return;  // a whole group leaves
-    auto all_max = [&](float v) {
-        v = warp_max(v);
-        if (kBlock) {
-            if ((tid & 31) == 0) red_max[tid >> 5] = v;
-            __syncthreads();
-            v = red_max[0];
-            for (int w = 1; w < (group >> 5); ++w) v = fmaxf(v, red_max[w]);
-        }
-        return v;
-    };
-    auto all_sum = [&](float v) {
-        v = warp_sum(v);
-        if (kBlock) {
-            if ((tid & 31) == 0) red_sum[tid >> 5] = v;
-            __syncthreads();
-            v = red_sum[0];
-            for (int w = 1; w < (group >> 5); ++w) v += red_sum[w];
-        }
-        return v;
-    };
-    const uint32_t bh = r / static_cast<uint32_t>(q_len);
-    const int qi = static_cast<int>(r - bh * static_cast<uint32_t>(q_len));
-    const int b = static_cast<int>(bh / static_cast<uint32_t>(heads));
-    const float a = scale * Exp::kPrescale;
     const float neg = -10000.0f * Exp::kPrescale;
-    const float floor_m = FLT_MIN * Exp::kPrescale;
-    const int64_t row_elem0 = static_cast<int64_t>(r) * k_len;
-    int lo = 0, hi = -1;  // CAUSAL: positions lo..hi are visible
-    if (CAUSAL) {
-        const int qlen = __ldg(q_lens + b), klen = __ldg(k_lens + b);
-        lo = klen - qlen;
-        hi = qi < qlen ? min(klen - 1, qi + lo) : -1;
-    }
-    const int64_t mrow_elem0 = (static_cast<int64_t>(b) * q_len + qi) * k_len;
-
-    // (the same rows with and without a mask tensor, so that both give the same bits)
-    const bool outer = r == static_cast<uint32_t>(total_rows - 1) || (b == 0 && qi == 0) || (b == batch - 1 && qi == q_len - 1);
-    if (outer) {  // uniform over the group: element-wise, three passes over the row
-        const T* in = qk + row_elem0;
-        T* out = score + row_elem0;
-        const T* mrow = CAUSAL ? nullptr : mask + mrow_elem0;
-        auto z_at = [&](int k) {
-            const float term = CAUSAL ? ((k >= lo && k <= hi) ? 0.0f : neg) : fmaf(to_float<T>(mrow[k]), -neg, neg);
-            return fmaf(a, to_float<T>(in[k]), term);
-        };
-        float mx = floor_m;
-        for (int k = gt; k < k_len; k += group) mx = fmaxf(mx, z_at(k));
-        mx = all_max(mx);
-        float sum = 0.f;
-        for (int k = gt; k < k_len; k += group) sum += Exp::exp_diff(z_at(k), mx);
-        sum = all_sum(sum);
-        const float inv = 1.0f / (sum + 1e-6f);
-        for (int k = gt; k < k_len; k += group) out[k] = from_float<T>(Exp::exp_diff(z_at(k), mx) * inv);
-        return;
-    }
-
-    const int off = static_cast<int>(row_elem0 & (E - 1));  // elements of the previous row in the first vector
-    const int nvec = (off + k_len + E - 1) / E;
-    const int v_last = nvec - 1;
-    // bit i: this thread's vector of trip i holds elements of a neighbouring row
-    const int trip_last = v_last / group;
-    const unsigned ragged = ((gt == 0 && off != 0) ? 1u : 0u) |
-                            ((gt == v_last - trip_last * group && ((off + k_len) & (E - 1)) != 0) ? (1u << trip_last) : 0u);
-    const bool tail_valid = gt + (VPT - 1) * group < nvec;  // earlier trips are full by the launch shape
-    const uint4* qp = reinterpret_cast<const uint4*>(qk) + (row_elem0 - off) / E + gt;
-    uint4* op = reinterpret_cast<uint4*>(score) + (row_elem0 - off) / E + gt;
+    const int k_len = row.k_len, head = row.head, group = row.group, gt = row.gt;
+    const float a = row.a;
+    const int tail = (k_len - head) & (E - 1);   // elements behind the last whole vector
+    const int n_whole = (k_len - head) / E;      // whole vectors of the row
+    const bool tail_valid = gt + (VPT - 1) * group < n_whole;  // earlier trips are full by the launch shape
+    const uint4* qp = reinterpret_cast<const uint4*>(row.qk + row.row_elem0 + head) + gt;
+    uint4* op = reinterpret_cast<uint4*>(row.score + row.row_elem0 + head) + gt;
+    // the single elements: lanes 0..head-1 the front ones, the next `tail` lanes the back ones
+    const int single = gt < head ? gt : (gt < head + tail ? k_len - tail + (gt - head) : -1);
 
     uint4 raw[VPT], mraw[VPT];
 #pragma unroll
     for (int i = 0; i < VPT; ++i)
         raw[i] = (i < VPT - 1 || tail_valid) ? ld_stream(qp + i * group) : make_uint4(0, 0, 0, 0);
+    // (the single elements are only loaded here and used after the mask vectors are on their way:
+    // their arithmetic in between would hold back the loads behind it for a full memory latency)
+    T single_x = from_float<T>(0.f), single_m = from_float<T>(0.f);
+    if (single >= 0) {
+        single_x = row.qk[row.row_elem0 + single];
+        if (!CAUSAL) single_m = row.mask[row.mrow_elem0 + single];
+    }
+    // every load of the row is issued before the first value is used
+    uint4 mnext[S == 0 ? 1 : VPT];  // the second mask vector of each trip
     if (!CAUSAL) {
-        const int moff = static_cast<int>(mrow_elem0 & (E - 1));
-        const int shift = (moff - off) & (E - 1);
-        const uint4* mp = reinterpret_cast<const uint4*>(mask) + (mrow_elem0 - moff) / E - (moff < off ? 1 : 0) + gt;
-#define ISPORE_LOAD_SHIFTED(S)                                                                   \
-    case S:                                                                                      \
-        _Pragma("unroll") for (int i = 0; i < VPT; ++i) if (i < VPT - 1 || tail_valid)           \
-            mraw[i] = shift_into_place<T, S>(ld_keep(mp + i * group), ld_keep(mp + i * group + 1)); \
-        break;
-        switch (shift) {
-            ISPORE_LOAD_SHIFTED(1)
-            ISPORE_LOAD_SHIFTED(2)
-            ISPORE_LOAD_SHIFTED(3)
-            ISPORE_LOAD_SHIFTED(4)
-            ISPORE_LOAD_SHIFTED(5)
-            ISPORE_LOAD_SHIFTED(6)
-            ISPORE_LOAD_SHIFTED(7)
-            default:
+        const uint4* mp = reinterpret_cast<const uint4*>(row.mask + (row.mrow_elem0 + head - S)) + gt;
 #pragma unroll
-                for (int i = 0; i < VPT; ++i)
-                    if (i < VPT - 1 || tail_valid) mraw[i] = ld_keep(mp + i * group);
+        for (int i = 0; i < VPT; ++i) {
+            if (i < VPT - 1 || tail_valid) {
+                mraw[i] = ld_keep(mp + i * group);
+                if (S != 0) mnext[i] = ld_keep(mp + i * group + 1);
+            }
         }
-#undef ISPORE_LOAD_SHIFTED
+    }
+    float zs = -FLT_MAX;
+    if (single >= 0) {
+        const float term = CAUSAL ? ((single >= row.lo && single <= row.hi) ? 0.0f : neg) : fmaf(to_float<T>(single_m), -neg, neg);
+        zs = fmaf(a, to_float<T>(single_x), term);
     }
     Unpacked<T> z[VPT];
-    float mx = floor_m;
+    float mx = fmaxf(FLT_MIN * Exp::kPrescale, zs);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         unpack(raw[i], z[i]);
         if (i < VPT - 1 || tail_valid) {
-            const int k0 = (gt + i * group) * E - off;  // position of the vector's first element
             if (CAUSAL) {
-                if (k0 >= lo && k0 + E - 1 <= hi) {
+                const int k0 = head + (gt + i * group) * E;  // position of the vector's first element
+                if (k0 >= row.lo && k0 + E - 1 <= row.hi) {
 #pragma unroll
                     for (int e = 0; e < E; ++e) z[i].v[e] *= a;
-                } else if (k0 > hi || k0 + E - 1 < lo) {
+                } else if (k0 > row.hi || k0 + E - 1 < row.lo) {
 #pragma unroll
                     for (int e = 0; e < E; ++e) z[i].v[e] = fmaf(a, z[i].v[e], neg);
                 } else {
 #pragma unroll
                     for (int e = 0; e < E; ++e)
-                        z[i].v[e] = fmaf(a, z[i].v[e], (k0 + e >= lo && k0 + e <= hi) ? 0.0f : neg);
+                        z[i].v[e] = fmaf(a, z[i].v[e], (k0 + e >= row.lo && k0 + e <= row.hi) ? 0.0f : neg);
                 }
             } else {
                 Unpacked<T> m;
-                unpack(mraw[i], m);
+                unpack(S == 0 ? mraw[i] : shift_into_place<T, S>(mraw[i], mnext[S == 0 ? 0 : i]), m);
 #pragma unroll
                 for (int e = 0; e < E; ++e) z[i].v[e] = fmaf(a, z[i].v[e], fmaf(m.v[e], -neg, neg));
-            }
-            if (ragged & (1u << i)) {
-#pragma unroll
-                for (int e = 0; e < E; ++e)
-                    if (static_cast<unsigned>(k0 + e) >= static_cast<unsigned>(k_len)) z[i].v[e] = -FLT_MAX;
             }
 #pragma unroll
             for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[i].v[e]);
         }
     }
-    mx = all_max(mx);
-    float sum = 0.f;
+    mx = warp_max(mx);
+    if (kBlock) {
+        if ((threadIdx.x & 31) == 0) row.red_max[threadIdx.x >> 5] = mx;
+        __syncthreads();
+        mx = row.red_max[0];
+        for (int w = 1; w < (group >> 5); ++w) mx = fmaxf(mx, row.red_max[w]);
+    }
+    float sum = single >= 0 ? (zs = Exp::exp_diff(zs, mx)) : 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         if (i < VPT - 1 || tail_valid) {
@@ -710,23 +670,118 @@ softmax_offset_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const
             }
         }
     }
-    sum = all_sum(sum);
+    sum = warp_sum(sum);
+    if (kBlock) {
+        if ((threadIdx.x & 31) == 0) row.red_sum[threadIdx.x >> 5] = sum;
+        __syncthreads();
+        sum = row.red_sum[0];
+        for (int w = 1; w < (group >> 5); ++w) sum += row.red_sum[w];
+    }
     const float inv = 1.0f / (sum + 1e-6f);
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         if (i < VPT - 1 || tail_valid) {
 #pragma unroll
             for (int e = 0; e < E; ++e) z[i].v[e] *= inv;
-            if (ragged & (1u << i)) {  // only this row's elements are written
-                const int k0 = (gt + i * group) * E - off;
-                T* out = reinterpret_cast<T*>(op + i * group);
-#pragma unroll
-                for (int e = 0; e < E; ++e)
-                    if (static_cast<unsigned>(k0 + e) < static_cast<unsigned>(k_len)) out[e] = from_float<T>(z[i].v[e]);
-            } else {
-                st_stream(op + i * group, pack(z[i]));
-            }
+            st_stream(op + i * group, pack(z[i]));
         }
+    }
+    if (single >= 0) row.score[row.row_elem0 + single] = from_float<T>(zs * inv);
+}
+
+// GROUP lanes per row: 32 (a warp; THREADS / 32 consecutive rows per CTA) or 0 = the whole CTA,
+// whose size is then chosen at launch to fit the row.  The grid is flat over the rows; (sequence,
+// head, q) come back through two multiply-shift divisions.
+template <typename T, int VPT, int GROUP, int THREADS, bool CAUSAL>
+__global__ void __launch_bounds__(THREADS)
+softmax_offset_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
+                          const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens, uint32_t total_rows,
+                          int batch, int q_len, int k_len, InvariantDivisor by_q_len, InvariantDivisor by_heads,
+                          float scale) {
+    constexpr int E = VecTraits<T>::kElems;
+    static_assert(GROUP == 32 || GROUP == 0, "a group is a warp or the CTA");
+    constexpr bool kBlock = GROUP == 0;
+    using Exp = ExpPolicy<T>;
+    __shared__ float red_max[THREADS / 32], red_sum[THREADS / 32];  // each written once per row: no barrier after the read
+    const int tid = threadIdx.x;
+    const int group = kBlock ? static_cast<int>(blockDim.x) : GROUP;
+    const int gt = kBlock ? tid : (tid & 31);
+    const uint32_t r = kBlock ? blockIdx.x : blockIdx.x * (THREADS / 32) + (tid >> 5);  // flat row
+    if (r >= total_rows) return;  // a whole warp leaves
+    const uint32_t bh = by_q_len.divide(r);
+    const int qi = static_cast<int>(r - bh * static_cast<uint32_t>(q_len));
+    const int b = static_cast<int>(by_heads.divide(bh));
+    const float a = scale * Exp::kPrescale;
+    const float neg = -10000.0f * Exp::kPrescale;
+    const int64_t row_elem0 = static_cast<int64_t>(r) * k_len;
+    const int64_t mrow_elem0 = (static_cast<int64_t>(b) * q_len + qi) * k_len;
+    int lo = 0, hi = -1;  // CAUSAL: positions lo..hi are visible
+    if (CAUSAL) {
+        const int qlen = __ldg(q_lens + b), klen = __ldg(k_lens + b);
+        lo = klen - qlen;
+        hi = qi < qlen ? min(klen - 1, qi + lo) : -1;
+    }
+
+    // (the same rows with and without a mask tensor, so that both give the same bits)
+    if (b == batch - 1 && qi == q_len - 1) {  // uniform over the group: element-wise, three passes over the row
+        const T* in = qk + row_elem0;
+        T* out = score + row_elem0;
+        const T* mrow = CAUSAL ? nullptr : mask + mrow_elem0;
+        auto z_at = [&](int k) {
+            const float term = CAUSAL ? ((k >= lo && k <= hi) ? 0.0f : neg) : fmaf(to_float<T>(mrow[k]), -neg, neg);
+            return fmaf(a, to_float<T>(in[k]), term);
+        };
+        float mx = FLT_MIN * Exp::kPrescale;
+        for (int k = gt; k < k_len; k += group) mx = fmaxf(mx, z_at(k));
+        mx = warp_max(mx);
+        if (kBlock) {
+            if ((tid & 31) == 0) red_max[tid >> 5] = mx;
+            __syncthreads();
+            mx = red_max[0];
+            for (int w = 1; w < (group >> 5); ++w) mx = fmaxf(mx, red_max[w]);
+        }
+        float sum = 0.f;
+        for (int k = gt; k < k_len; k += group) sum += Exp::exp_diff(z_at(k), mx);
+        sum = warp_sum(sum);
+        if (kBlock) {
+            if ((tid & 31) == 0) red_sum[tid >> 5] = sum;
+            __syncthreads();
+            sum = red_sum[0];
+            for (int w = 1; w < (group >> 5); ++w) sum += red_sum[w];
+        }
+        const float inv = 1.0f / (sum + 1e-6f);
+        for (int k = gt; k < k_len; k += group) out[k] = from_float<T>(Exp::exp_diff(z_at(k), mx) * inv);
+        return;
+    }
+
+    OffsetRow<T> row;
+    row.score = score;
+    row.qk = qk;
+    row.mask = mask;
+    row.row_elem0 = row_elem0;
+    row.mrow_elem0 = mrow_elem0;
+    row.red_max = red_max;
+    row.red_sum = red_sum;
+    row.k_len = k_len;
+    row.head = static_cast<int>(-row_elem0 & (E - 1));  // elements in front of the row's first whole vector
+    row.lo = lo;
+    row.hi = hi;
+    row.group = group;
+    row.gt = gt;
+    row.a = a;
+    if (CAUSAL) {
+        offset_row_fast<T, VPT, kBlock, true, 0>(row);
+        return;
+    }
+    switch (static_cast<int>((mrow_elem0 + row.head) & (E - 1))) {
+        case 1: offset_row_fast<T, VPT, kBlock, CAUSAL, 1>(row); break;
+        case 2: offset_row_fast<T, VPT, kBlock, CAUSAL, 2>(row); break;
+        case 3: offset_row_fast<T, VPT, kBlock, CAUSAL, 3>(row); break;
+        case 4: offset_row_fast<T, VPT, kBlock, CAUSAL, E == 8 ? 4 : 0>(row); break;
+        case 5: offset_row_fast<T, VPT, kBlock, CAUSAL, E == 8 ? 5 : 0>(row); break;
+        case 6: offset_row_fast<T, VPT, kBlock, CAUSAL, E == 8 ? 6 : 0>(row); break;
+        case 7: offset_row_fast<T, VPT, kBlock, CAUSAL, E == 8 ? 7 : 0>(row); break;
+        default: offset_row_fast<T, VPT, kBlock, CAUSAL, 0>(row); break;
     }
 }
 
@@ -769,33 +824,45 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
     const int64_t rows_per_batch = heads * q_len;
     {
         // Any row length at least two vectors long: one row per warp or per CTA, mask shifted in registers.
-        const int64_t cover = ceil_div(k_len + E - 1, static_cast<int64_t>(E));  // aligned vectors that can cover a row
-        if (aligned16(score) && aligned16(qk) && (CAUSAL || aligned16(ms.mask)) && k_len >= 2 * E && cover <= 4096 &&
-            batch <= INT32_MAX && heads <= INT32_MAX && total_rows < (1ll << 31)) {
-#define ISPORE_SOFTMAX_OFFSET(VPT, GROUP, THREADS, ctas, threads)                                                   \
+        const int64_t whole = k_len / E;  // a row holds `whole` or `whole - 1` whole aligned vectors
+        if (aligned16(score) && aligned16(qk) && (CAUSAL || aligned16(ms.mask)) && k_len >= 2 * E && whole <= 4096 &&
+            total_rows < (1ll << 31)) {
+#define ISPORE_SOFTMAX_OFFSET(VPT, GROUP, THREADS, rows_per_cta, threads)                                          \
     do {                                                                                                           \
-        softmax_offset_row_kernel<T, VPT, GROUP, THREADS, CAUSAL><<<static_cast<unsigned>(ctas), threads, 0, st>>>( \
-            score, qk, ms.mask, ms.q_lens, ms.k_lens, total_rows, static_cast<int>(batch), static_cast<int>(heads), \
-            static_cast<int>(q_len), static_cast<int>(k_len), scale);                                              \
+        const unsigned ctas = static_cast<unsigned>(ceil_div(total_rows, static_cast<int64_t>(rows_per_cta)));      \
+        softmax_offset_row_kernel<T, VPT, GROUP, THREADS, CAUSAL><<<ctas, threads, 0, st>>>(                        \
+            score, qk, ms.mask, ms.q_lens, ms.k_lens, static_cast<uint32_t>(total_rows), static_cast<int>(batch),  \
+            static_cast<int>(q_len), static_cast<int>(k_len), InvariantDivisor(static_cast<uint32_t>(q_len)),      \
+            InvariantDivisor(static_cast<uint32_t>(heads)), scale);                                                \
         return check_launch("softmax_offset_row_kernel");                                                          \
     } while (0)
-            if (cover <= 128) {  // a warp per row, eight rows per CTA
-                const int64_t ctas = ceil_div(total_rows, static_cast<int64_t>(8));
-                if (cover <= 32) ISPORE_SOFTMAX_OFFSET(1, 32, 256, ctas, 256);
-                if (cover <= 64) ISPORE_SOFTMAX_OFFSET(2, 32, 256, ctas, 256);
-                if (cover <= 96) ISPORE_SOFTMAX_OFFSET(3, 32, 256, ctas, 256);
-                ISPORE_SOFTMAX_OFFSET(4, 32, 256, ctas, 256);
+            // a warp per row (the per-row set-up is then paid once, not once per warp): up to 8 vectors
+            // per lane for fp32, 6 for fp16 (8 fp16 vectors are 64 live values per lane: measured slower)
+            if (whole <= (sizeof(T) == 4 ? 256 : 192)) {
+                if (whole <= 32) ISPORE_SOFTMAX_OFFSET(1, 32, 256, 8, 256);
+                if (whole <= 64) ISPORE_SOFTMAX_OFFSET(2, 32, 256, 8, 256);
+                if (whole <= 96) ISPORE_SOFTMAX_OFFSET(3, 32, 256, 8, 256);
+                if (whole <= 128) ISPORE_SOFTMAX_OFFSET(4, 32, 256, 8, 256);
+                if (whole <= 160) ISPORE_SOFTMAX_OFFSET(5, 32, 128, 4, 128);
+                if (whole <= 192) ISPORE_SOFTMAX_OFFSET(6, 32, 128, 4, 128);
+                if (whole <= 224) ISPORE_SOFTMAX_OFFSET(7, 32, 128, 4, 128);
+                ISPORE_SOFTMAX_OFFSET(8, 32, 128, 4, 128);
             }
             // A CTA per row: among the (vectors per thread, CTA size) pairs whose trips before the last
-            // are full for every row (rows are cover - 1 or cover vectors long), the one with the
-            // least issue work: a thread's vectors plus about three vectors' worth of per-row set-up
-            // and block reductions.
+            // are full for every row, the one with the fewest thread slots after weighting by how
+            // well that many vectors per thread ran on B200 (2047 to 8191-long rows: fp16 best at 3
+            // vectors = 24 values per thread, fp32 at 4 to 8 = 16 to 32 values).
             int best_vpt = 0, best_threads = 0;
-            int64_t best_cost = INT64_MAX;
-            for (int vpt : {4, 3, 6, 8, 2, 1}) {
-                const int64_t threads = ceil_div(ceil_div(cover, static_cast<int64_t>(vpt)), static_cast<int64_t>(32)) * 32;
-                if (threads < 64 || threads > 512 || (vpt - 1) * threads > cover - 1) continue;
-                const int64_t cost = threads * (vpt + tune(kTuneSoftmax, 3));
+            double best_cost = 1e30;
+            for (int vpt : {3, 4, 8, 6, 2, 1}) {
+                const int64_t threads = ceil_div(ceil_div(whole, static_cast<int64_t>(vpt)), static_cast<int64_t>(32)) * 32;
+                if (threads < 64 || threads > 512 || (vpt - 1) * threads > whole - 1) continue;
+                double weight;  // relative speed at equal slot count
+                if (sizeof(T) == 2)
+                    weight = vpt == 3 ? 1.0 : vpt == 4 ? 0.87 : vpt == 2 ? 0.85 : vpt == 6 ? 0.8 : vpt == 8 ? 0.75 : 0.55;
+                else
+                    weight = vpt == 4 ? (whole <= 768 ? 1.0 : 0.93) : vpt == 8 ? 0.97 : vpt == 6 ? 0.85 : vpt == 3 ? 0.72 : vpt == 2 ? 0.7 : 0.55;
+                const double cost = static_cast<double>(threads * vpt) / weight;
                 if (cost < best_cost) {
                     best_cost = cost;
                     best_vpt = vpt;
@@ -803,12 +870,12 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
                 }
             }
             switch (best_vpt) {
-                case 1: ISPORE_SOFTMAX_OFFSET(1, 0, 512, total_rows, best_threads);
-                case 2: ISPORE_SOFTMAX_OFFSET(2, 0, 512, total_rows, best_threads);
-                case 3: ISPORE_SOFTMAX_OFFSET(3, 0, 512, total_rows, best_threads);
-                case 4: ISPORE_SOFTMAX_OFFSET(4, 0, 512, total_rows, best_threads);
-                case 6: ISPORE_SOFTMAX_OFFSET(6, 0, 512, total_rows, best_threads);
-                case 8: ISPORE_SOFTMAX_OFFSET(8, 0, 512, total_rows, best_threads);
+                case 1: ISPORE_SOFTMAX_OFFSET(1, 0, 512, 1, best_threads);
+                case 2: ISPORE_SOFTMAX_OFFSET(2, 0, 512, 1, best_threads);
+                case 3: ISPORE_SOFTMAX_OFFSET(3, 0, 512, 1, best_threads);
+                case 4: ISPORE_SOFTMAX_OFFSET(4, 0, 512, 1, best_threads);
+                case 6: ISPORE_SOFTMAX_OFFSET(6, 0, 512, 1, best_threads);
+                case 8: ISPORE_SOFTMAX_OFFSET(8, 0, 512, 1, best_threads);
                 default: break;  // no shape fits: the kernels below take it
             }
 #undef ISPORE_SOFTMAX_OFFSET
