@@ -158,10 +158,7 @@ __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
 // registers or on how many CTAs fit, which is what the wider head groups (more registers, fewer
 // CTAs per SM) need to reach the memory roofline.
 constexpr int kStages = 3;
-#ifndef ISPORE_MHA_PV_MIN_GROUP
-#define ISPORE_MHA_PV_MIN_GROUP 8
-#endif
-constexpr int kPvTensorMinGroup = ISPORE_MHA_PV_MIN_GROUP;  // q heads per CTA from which numerators x V runs on the tensor cores
+constexpr int kPvTensorMinGroup = 8;  // q heads per CTA from which numerators x V runs on the tensor cores
 
 // Both products on the tensor cores: half rows of 128, staged tiles, eight q heads per CTA.  That
 // kernel runs eight warps instead of four, so that twice as many warps hide each other's latencies

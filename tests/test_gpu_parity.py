@@ -911,3 +911,16 @@ def test_causal_softmax_any_row_length(ops, orc, rng, case, dtype):
         assert over == 0
     else:
         assert_close_f32(host(d), want, floor=1e-30, what="causal softmax f32, any row length")
+
+
+@pytest.mark.parametrize("case", [(3000, 7, 3, 17), (2, 1, 4, 19), (5, 16, 1, 23), (1, 3, 1025, 9), (700, 3, 2, 35)])
+def test_softmax_any_row_length_row_index_recovery(ops, orc, rng, case):
+    # many rows, one head, one q row, q_len a power of two and not: (sequence, head, q) are
+    # recovered from the flat row by multiply-shift division, and the mask row depends on them
+    batch, heads, q_len, k_len = case
+    qk = rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32)
+    mask = (rng.random((batch, q_len, k_len)) < 0.5).astype(np.float32)
+    out = torch.empty(qk.shape, device="cuda:0")
+    ops.launchScaleMaskAndSoftmax(dev(qk), dev(mask), out, 0.7)
+    want, _ = orc.scale_mask_softmax(qk, mask, np.float32(0.7))
+    assert_close_f32(host(out), want, floor=1e-30, what="softmax, row index recovery")
