@@ -229,8 +229,9 @@ ISPORE_API int ispore_scale_mask_softmax_f16(void* attn_score, const void* qk, c
  * ref: the predicate of src/kernels/build_casual_mask.cu:36 applied inside the kernel of
  *      src/kernels/attn_softmax_kernel.cu:50-125; replaces the pair of calls
  *      launchBuildCausalMasks + launchScaleMaskAndSoftmax of the reference's context attention.
- * q_lens, k_lens [batch] int32.  The result is bit-identical to ispore_build_causal_mask_* followed
- * by ispore_scale_mask_softmax_* on the same inputs. */
+ * q_lens, k_lens [batch] int32.  Element for element the same arithmetic as ispore_build_causal_mask_*
+ * followed by ispore_scale_mask_softmax_* on the same inputs; the two routes may run different kernels
+ * for a shape, so row sums can be taken in another order (3e-6 relative in fp32, one half-ulp in fp16). */
 ISPORE_API int ispore_scale_causal_softmax_f32(float* attn_score, const float* qk, const int32_t* q_lens,
                                                const int32_t* k_lens, int64_t batch_size, int64_t head_num,
                                                int64_t q_len, int64_t k_len, float scale, ispore_stream_t stream);

@@ -48,7 +48,7 @@ struct ExpPolicy<__half> {
 // row length and head count.
 // CAUSAL: there is no mask tensor; the 0/1 mask row is derived from q_lens[b] and k_lens[b] with
 // the predicate of the reference's mask builder (src/kernels/build_casual_mask.cu:36), so the
-// result is bit-identical to building the mask first and the [bs, q, k] tensor is never read.
+// result of this kernel is bit-identical to running it on a built mask and the [bs, q, k] tensor is never read.
 #define ISPORE_IN_ROW(i, v) (MODE == 0 || (MODE == 1 && (i) < VPT - 1) || (v) < row_vecs)
 template <typename T, int VPT, int GROUP, int THREADS, int HG, int MIN_BLOCKS, int MODE, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS, MIN_BLOCKS)
@@ -800,7 +800,21 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
     const bool vec_ok = k_len % E == 0 && aligned16(score) && aligned16(qk) && (CAUSAL || aligned16(ms.mask)) &&
                         total_rows < (1ll << 32) && heads < (1ll << 31);
     const int64_t vecs = k_len / E;
-    if (vec_ok) {
+    // Two families of kernels.  The head-group kernels (rows of whole vectors only) share a mask row
+    // between heads and win where a row fills their launch shape: short rows and powers of two.
+    // The row kernels take any length and win elsewhere, by a wide margin on lengths such as 640,
+    // 3000 or 5000 and on every fp32 row without a mask tensor.  Measured on B200, both families,
+    // fp16 and fp32, k_len 128 .. 16384.
+    const int64_t whole = k_len / E;  // a row holds `whole` or `whole - 1` whole aligned vectors
+    const bool rows_ok = aligned16(score) && aligned16(qk) && (CAUSAL || aligned16(ms.mask)) && k_len >= 2 * E &&
+                         whole <= 4096 && total_rows < (1ll << 31);
+    const bool pow2 = (k_len & (k_len - 1)) == 0;
+    bool prefer_rows;
+    if (sizeof(T) == 2)
+        prefer_rows = CAUSAL ? (k_len > 512 && k_len != 4096) : (k_len > 512 && !(pow2 && k_len >= 4096));
+    else
+        prefer_rows = CAUSAL ? k_len >= 288 : (k_len > 256 && !pow2 && !(k_len >= 1000 && k_len <= 2048));
+    if (vec_ok && !(rows_ok && prefer_rows)) {
         const int rv = static_cast<int>(vecs);
 #define ISPORE_SOFTMAX(VPT, GROUP, THREADS, HG, MINB) \
     return launch_groups<T, CAUSAL, VPT, GROUP, THREADS, HG, MINB>(score, qk, ms, batch, heads, q_len, rv, scale, st)
@@ -824,9 +838,7 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
     const int64_t rows_per_batch = heads * q_len;
     {
         // Any row length at least two vectors long: one row per warp or per CTA, mask shifted in registers.
-        const int64_t whole = k_len / E;  // a row holds `whole` or `whole - 1` whole aligned vectors
-        if (aligned16(score) && aligned16(qk) && (CAUSAL || aligned16(ms.mask)) && k_len >= 2 * E && whole <= 4096 &&
-            total_rows < (1ll << 31)) {
+        if (rows_ok) {
 #define ISPORE_SOFTMAX_OFFSET(VPT, GROUP, THREADS, rows_per_cta, threads)                                          \
     do {                                                                                                           \
         const unsigned ctas = static_cast<unsigned>(ceil_div(total_rows, static_cast<int64_t>(rows_per_cta)));      \
