@@ -264,8 +264,8 @@ softmax_generic_kernel(T* __restrict__ score, const T* __restrict__ qk, const T*
     }
 }
 
-// Rows that cannot be moved as 128-bit vectors (k_len not a multiple of the vector, unaligned
-// views) but fit a CTA's registers: one CTA per row, EPT scalar elements per thread, the row read
+// Rows that cannot be moved as 128-bit vectors (buffers that are not 16-byte aligned, rows shorter
+// than two vectors) but fit a CTA's registers: one CTA per row, EPT scalar elements per thread, the row read
 // once and written once.
 template <typename T, int THREADS, int EPT, bool CAUSAL>
 __global__ void __launch_bounds__(THREADS)
@@ -325,167 +325,6 @@ softmax_row_scalar_kernel(T* __restrict__ score, const T* __restrict__ qk, const
             if (i < k_len) orow[i] = from_float<T>(z[j] * inv);
         }
         __syncthreads();  // red[] is rewritten by the next row
-    }
-}
-
-// Rows whose starts are not 16-byte aligned (k_len not a multiple of the vector) still sit in a
-// 16-byte aligned buffer: a CTA walks the aligned vectors that cover a row, ignores the elements
-// of the neighbouring rows at both ends, and stores whole vectors for the interior and single
-// elements for the two ragged ends.  The mask row becomes additive terms in shared memory once
-// per (b, q) and serves kHeadsPerCta heads.
-constexpr int kUnalignedThreads = 128;
-
-template <typename T, int VPT, int HPC, bool CAUSAL>
-__global__ void __launch_bounds__(kUnalignedThreads)
-softmax_unaligned_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
-                             const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
-                             int64_t batch, int heads, int q_len, int k_len, float scale) {
-    constexpr int E = VecTraits<T>::kElems;
-    constexpr int THREADS = kUnalignedThreads;
-    constexpr int kWarps = THREADS / 32;
-    using Exp = ExpPolicy<T>;
-    // Additive mask terms, element i at [(i % E) * term_stride + i / E]: a warp reads elements that are
-    // E apart (one per lane's vector), which in this layout are neighbours, not E-way bank conflicts.
-    extern __shared__ __align__(16) float term_s[];
-    const int term_stride = ((k_len + E - 1) / E + 31) / 32 * 32 + 4;
-    auto term_at = [&](int i) -> float& { return term_s[(i & (E - 1)) * term_stride + (i / E)]; };
-    __shared__ float red[2][kWarps];
-    const int tid = threadIdx.x;
-    const int head_groups = (heads + HPC - 1) / HPC;
-    const int64_t unit = blockIdx.x;  // (b, head group, q), q fastest
-    const int qi = static_cast<int>(unit % q_len);
-    const int64_t t = unit / q_len;
-    const int hg = static_cast<int>(t % head_groups);
-    const int64_t b = t / head_groups;
-    const float a = scale * Exp::kPrescale;
-    const float neg = -10000.0f * Exp::kPrescale;
-    const int64_t total_elems = batch * heads * q_len * static_cast<int64_t>(k_len);
-    const int h0 = hg * HPC;
-    const int nh = min(HPC, heads - h0);
-
-    // All loads of the CTA first: HPC rows of qk, then the mask row.
-    uint4 raw[HPC][VPT];
-    int off[HPC];       // elements of the previous row in a row's first vector
-    int64_t vec0[HPC];  // index of that vector
-#pragma unroll
-    for (int hh = 0; hh < HPC; ++hh) {
-        const int64_t row_elem0 = ((b * heads + h0 + (hh < nh ? hh : 0)) * q_len + qi) * static_cast<int64_t>(k_len);
-        off[hh] = static_cast<int>(row_elem0 & (E - 1));
-        vec0[hh] = (row_elem0 - off[hh]) / E;
-        const int nvec = (off[hh] + k_len + E - 1) / E;
-#pragma unroll
-        for (int i = 0; i < VPT; ++i) {
-            const int v = tid + i * THREADS;
-            raw[hh][i] = make_uint4(0, 0, 0, 0);
-            if (hh < nh && v < nvec) {
-                const int64_t first = (vec0[hh] + v) * E;  // flat index of the vector's first element
-                if (first + E <= total_elems) {
-                    raw[hh][i] = ld_stream(reinterpret_cast<const uint4*>(qk) + vec0[hh] + v);
-                } else {  // the buffer ends inside this vector
-                    Unpacked<T> tail;
-#pragma unroll
-                    for (int e = 0; e < E; ++e) tail.v[e] = first + e < total_elems ? to_float<T>(qk[first + e]) : 0.f;
-                    raw[hh][i] = pack(tail);
-                }
-            }
-        }
-    }
-    if (CAUSAL) {
-        const int qlen = __ldg(q_lens + b), klen = __ldg(k_lens + b);
-        const int lo = klen - qlen;
-        const int hi = qi < qlen ? min(klen - 1, qi + lo) : -1;
-        for (int i = tid; i < k_len; i += THREADS) term_at(i) = (i >= lo && i <= hi) ? 0.0f : neg;
-    } else {
-        const T* mrow = mask + (b * q_len + qi) * static_cast<int64_t>(k_len);
-        for (int i = tid; i < k_len; i += THREADS) term_at(i) = fmaf(to_float<T>(mrow[i]), -neg, neg);
-    }
-    __syncthreads();
-
-#pragma unroll
-    for (int hh = 0; hh < HPC; ++hh) {
-        if (hh < nh) {  // uniform over the CTA
-            const int nvec = (off[hh] + k_len + E - 1) / E;
-            Unpacked<T> z[VPT];
-            float mx = FLT_MIN * Exp::kPrescale;
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = tid + i * THREADS;
-                if (v < nvec) {
-                    unpack(raw[hh][i], z[i]);
-                    const int first_idx = v * E - off[hh];
-                    if (first_idx >= 0 && first_idx + E <= k_len) {  // interior vector: no per-element guards
-#pragma unroll
-                        for (int e = 0; e < E; ++e) {
-                            z[i].v[e] = fmaf(a, z[i].v[e], term_at(first_idx + e));
-                            mx = fmaxf(mx, z[i].v[e]);
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < E; ++e) {
-                            const int idx = first_idx + e;
-                            if (idx >= 0 && idx < k_len) {
-                                z[i].v[e] = fmaf(a, z[i].v[e], term_at(idx));
-                                mx = fmaxf(mx, z[i].v[e]);
-                            }
-                        }
-                    }
-                }
-            }
-            mx = warp_max(mx);
-            if ((tid & 31) == 0) red[0][tid >> 5] = mx;
-            __syncthreads();
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, red[0][w]);
-            float sum = 0.f;
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = tid + i * THREADS;
-                if (v < nvec) {
-                    const int first_idx = v * E - off[hh];
-                    if (first_idx >= 0 && first_idx + E <= k_len) {
-#pragma unroll
-                        for (int e = 0; e < E; ++e) {
-                            z[i].v[e] = Exp::exp_diff(z[i].v[e], mx);
-                            sum += z[i].v[e];
-                        }
-                    } else {
-#pragma unroll
-                        for (int e = 0; e < E; ++e) {
-                            const int idx = first_idx + e;
-                            if (idx >= 0 && idx < k_len) {
-                                z[i].v[e] = Exp::exp_diff(z[i].v[e], mx);
-                                sum += z[i].v[e];
-                            }
-                        }
-                    }
-                }
-            }
-            sum = warp_sum(sum);
-            if ((tid & 31) == 0) red[1][tid >> 5] = sum;
-            __syncthreads();
-            sum = 0.f;
-#pragma unroll
-            for (int w = 0; w < kWarps; ++w) sum += red[1][w];
-            const float inv = 1.0f / (sum + 1e-6f);
-#pragma unroll
-            for (int i = 0; i < VPT; ++i) {
-                const int v = tid + i * THREADS;
-                if (v < nvec) {
-                    const int first_idx = v * E - off[hh];
-#pragma unroll
-                    for (int e = 0; e < E; ++e) z[i].v[e] *= inv;
-                    if (first_idx >= 0 && first_idx + E <= k_len) {
-                        st_stream(reinterpret_cast<uint4*>(score) + vec0[hh] + v, pack(z[i]));
-                    } else {  // a ragged end: only this row's elements are written
-                        T* out = score + (vec0[hh] + v) * E;
-#pragma unroll
-                        for (int e = 0; e < E; ++e)
-                            if (first_idx + e >= 0 && first_idx + e < k_len) out[e] = from_float<T>(z[i].v[e]);
-                    }
-                }
-            }
-            __syncthreads();  // red[] is rewritten by the next head
-        }
     }
 }
 
@@ -891,24 +730,6 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
                 default: break;  // no shape fits: the kernels below take it
             }
 #undef ISPORE_SOFTMAX_OFFSET
-        }
-    }
-    {
-        const int64_t cover = ceil_div(k_len + E - 1, static_cast<int64_t>(E));  // aligned vectors that can cover a row
-        const int hpc = cover <= kUnalignedThreads * 2 ? 4 : (cover <= kUnalignedThreads * 4 ? 2 : 1);
-        const int64_t units = batch * q_len * ceil_div(heads, static_cast<int64_t>(hpc));
-        if (aligned16(score) && aligned16(qk) && cover <= kUnalignedThreads * 8 && k_len * 4 <= 40 * 1024 &&
-            units < (1ll << 31) && heads < (1ll << 31)) {
-            const size_t smem = static_cast<size_t>(E) * ((ceil_div(k_len, static_cast<int64_t>(E)) + 31) / 32 * 32 + 4) * sizeof(float);
-#define ISPORE_SOFTMAX_UNALIGNED(VPT, HPC)                                                                         \
-    softmax_unaligned_row_kernel<T, VPT, HPC, CAUSAL><<<static_cast<unsigned>(units), kUnalignedThreads, smem, st>>>( \
-        score, qk, ms.mask, ms.q_lens, ms.k_lens, batch, static_cast<int>(heads), static_cast<int>(q_len),          \
-        static_cast<int>(k_len), scale)
-            if (hpc == 4) ISPORE_SOFTMAX_UNALIGNED(2, 4);
-            else if (hpc == 2) ISPORE_SOFTMAX_UNALIGNED(4, 2);
-            else ISPORE_SOFTMAX_UNALIGNED(8, 1);
-#undef ISPORE_SOFTMAX_UNALIGNED
-            return check_launch("softmax_unaligned_row_kernel");
         }
     }
     if (k_len <= 256 * 16) {
