@@ -320,7 +320,8 @@ class GpuChain:
             events[8].record()
 
 
-NEXT_KERNELS = ["build_causal_mask", "scale_causal_softmax", "cal_padding_offset", "transpose_remove_padding",
+NEXT_KERNELS = ["build_causal_mask", "scale_causal_softmax", "scale_mask_softmax_len777", "cal_padding_offset",
+                "transpose_remove_padding",
                 "repeat_kv", "decoder_masked_mha", "decoder_masked_mha_gqa8"]
 
 
@@ -362,6 +363,15 @@ class NextRows:
             ql = self._i32([SEQ] * B)
             return ((lambda: o.launchScaleCausalSoftmax(qk, ql, ql, out, 1.0 / float(np.sqrt(HEAD_SIZE)))),
                     2 * qk.numel() * 2, f"qk [{B}, {HEADS}, {SEQ}, {SEQ}] f16, no mask tensor")
+        if name == "scale_mask_softmax_len777":
+            # prompts of 777 tokens: rows that are not a whole number of 128-bit vectors, so every
+            # row (and every mask row) starts at another offset inside its aligned vectors
+            n, bs = 777, max(1, self.tokens // 4096)
+            qk = self._randn(bs, HEADS, n, n, scale=3.0)
+            out = t.empty_like(qk)
+            mask = t.tril(t.ones((n, n), dtype=h, device=dev)).expand(bs, n, n).contiguous()
+            return ((lambda: o.launchScaleMaskAndSoftmax(qk, mask, out, 1.0 / float(np.sqrt(HEAD_SIZE)))),
+                    2 * qk.numel() * 2 + mask.numel() * 2, f"qk [{bs}, {HEADS}, {n}, {n}] f16 + mask [{bs}, {n}, {n}]")
         if name == "cal_padding_offset":
             lens = self._i32([SEQ] * B)
             po = t.empty((B, SEQ), dtype=t.int32, device=dev)
