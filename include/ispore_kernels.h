@@ -281,14 +281,21 @@ ISPORE_API int ispore_topk_f16(const void* probs, int64_t rows, int64_t vocab, i
  * synchronisation.  Same results as ispore_topk_f32; the per-slice candidate
  * lists live in a fixed array inside the library image instead of
  * caller-provided scratch.  Neither this call nor anything it reaches calls
- * cudaMalloc/cudaFree or any allocating library routine.
+ * cudaMalloc/cudaFree or any allocating library routine.  What the CUDA runtime
+ * does on its own the first time a process touches this library on a device is
+ * outside that promise: with lazy module loading (the default) the first call
+ * loads the module, which places its image — this array included — in device
+ * memory and synchronises.  So make ONE warm-up call per device while
+ * allocation is still allowed (at start-up); from the second call on, the free
+ * device memory does not move (tests/test_zz_no_alloc.py asserts it).
  *   - Limit: rows * K <= ISPORE_TOPK_STATIC_ENTRIES (131072 list entries,
  *     1 MiB of device memory that every GPU loading the library holds until the
  *     process exits).  Larger requests return ISPORE_ELIMIT with an explanatory
  *     message; use ispore_topk_f32 for those.
- *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, with that device current) and caches it; make that
- *     first call before starting any stream capture on the device.
+ *   - The first call on each device also looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current), raises the kernel's
+ *     shared-memory limit and caches both; make that warm-up call before
+ *     starting any stream capture on the device.
  *   - All calls on a device share the one array, which keeps whatever the last
  *     call left in it.  Nothing needs clearing (every slot that is read is
  *     written first), but two calls that overlap on the GPU — different streams,

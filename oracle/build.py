@@ -32,7 +32,23 @@ HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent
 ORACLE_SO = HERE / "libispore_oracle.so"
 REF_OUT = HERE / "_ref"
-DEFAULT_REF_ROOT = Path(os.environ.get("ISPORE_REFERENCE_ROOT", "/root/reference"))
+
+
+def _default_ref_root() -> Path:
+    """The reference checkout: $ISPORE_REFERENCE_ROOT, else `reference_path` of BASELINE.json at the
+    repository root.  With neither, a path that does not exist (the reference is then not built)."""
+    env = os.environ.get("ISPORE_REFERENCE_ROOT")
+    if env:
+        return Path(env)
+    try:
+        import json
+
+        return Path(json.loads((ROOT / "BASELINE.json").read_text())["reference_path"])
+    except Exception:
+        return ROOT / "_no_reference_tree"
+
+
+DEFAULT_REF_ROOT = _default_ref_root()
 
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
@@ -46,6 +62,7 @@ REF_LIBS = {
         "ref_wrap/ref_concat_softmax.cu",
         ["src/kernels/concat_past_kv.cu", "src/kernels/attn_softmax_kernel.cu"],
     ),
+    "libref_topk.so": ("ref_wrap/ref_topk.cu", ["src/kernels/topK.cu"]),
     "libref_mha.so": ("ref_wrap/ref_mha.cu", []),  # the wrapper includes the kernel file itself
     "libref_layout.so": (
         "ref_wrap/ref_layout.cu",

@@ -5,7 +5,7 @@ reference tree, see oracle/build.py) behind a small C ABI, and eleven of the ref
 tests compiled unmodified against the drop-in headers.  Only reference kernels that are functional
 are run, and only on shapes they are safe for (the wrappers in oracle/ref_wrap/ refuse the rest):
 fp32 residual+RMSNorm, embedding, fp32 QKV+RoPE (the reference applies no bias), SiLU*up, KV concat,
-softmax, causal mask, padding offsets, repeat-KV, decode attention.  Marked gpu.
+softmax, causal mask, padding offsets, repeat-KV, decode attention, top-K (one row, K = 5).  Marked gpu.
 """
 import ctypes as C
 import subprocess
@@ -353,6 +353,55 @@ def test_vs_reference_gpu_decoder_masked_mha(ops, orc, rng, half, heads, kv, ste
     # the reference multiplies q*k*scale in the storage type (half products for fp16): 1e-3 is
     # its own test's tolerance and what half products allow; fp32 agrees far closer
     assert np.max(np.abs(host(ours).astype(np.float64) - host(ref).astype(np.float64))) <= (5e-3 if half else 5e-5)
+
+
+def _distinct_positive(rng, vocab, dtype):
+    """Positive values whose largest ones are pairwise distinct.  fp32: all distinct.  fp16 has only
+    31,743 positive finite patterns, so a longer row repeats some patterns from the lower half of
+    the range, which can never reach the first places."""
+    if dtype == np.float32:
+        v = (rng.random(vocab, dtype=np.float32) + np.float32(1e-3))
+        while np.unique(v).size != vocab:
+            v = (rng.random(vocab, dtype=np.float32) + np.float32(1e-3))
+        return v
+    patterns = np.arange(1, 0x7C00, dtype=np.uint16)  # every positive finite half, subnormals included
+    if vocab <= patterns.size:
+        bits = rng.choice(patterns, vocab, replace=False)
+    else:
+        bits = np.concatenate([patterns, rng.choice(patterns[: patterns.size // 2], vocab - patterns.size)])
+        rng.shuffle(bits)
+    return bits.view(np.float16)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("vocab", [32000, 777])
+def test_vs_reference_gpu_topk(ops, orc, rng, dtype, vocab):
+    # The reference's two top-K kernels on the domain where they are functional: ONE row (round 2
+    # indexes the ids of row 0 for every row, topK.cu:64), K = 5 (compiled in, :87), positive data
+    # (empty list slots hold -1e-20, topK.h:14-19, and would outrank negative values).  On it the value
+    # order (best first) and the layout of ids and values (topK.cu:68-72) are the reference's own:
+    # reference kernel == oracle == this library, ids and value bits.
+    lib = _ref(orc, "libref_topk.so")
+    K, blocks = lib.ref_gpu_topk_k(), lib.ref_gpu_topk_blocks_per_row()
+    assert (K, blocks) == (5, 8)
+    probs = _distinct_positive(rng, vocab, dtype).reshape(1, vocab)
+    dp = dev(probs)
+    tdt = dp.dtype
+    mk_i = lambda *shape: torch.full(shape, -7, dtype=torch.int32, device="cuda:0")
+    mk_v = lambda *shape: torch.full(shape, -7.0, dtype=tdt, device="cuda:0")
+    sc_i, sc_v, f_i, f_v = mk_i(1, blocks, K), mk_v(1, blocks, K), mk_i(1, K), mk_v(1, K)
+    rsc_i, rsc_v, rf_i, rf_v = mk_i(1, blocks, K), mk_v(1, blocks, K), mk_i(1, K), mk_v(1, K)
+    ops.launchTopKforBeamSearch(dp, sc_i, sc_v, f_i, f_v)
+    fn = lib.ref_gpu_topk_f32 if dtype == np.float32 else lib.ref_gpu_topk_f16
+    assert fn(_p(dp), 1, vocab, _p(rsc_i), _p(rsc_v), _p(rf_i), _p(rf_v)) == 0
+    torch.cuda.synchronize()
+    want_i, want_v = orc.topk(probs, K)
+    bits = np.uint32 if dtype == np.float32 else np.uint16
+    assert np.array_equal(host(rf_i), want_i), "reference kernel and oracle disagree on the ids"
+    assert np.array_equal(host(rf_v).view(bits), want_v.view(bits)), "reference kernel and oracle disagree on the values"
+    assert np.array_equal(host(f_i), host(rf_i)) and np.array_equal(host(f_v).view(bits), host(rf_v).view(bits))
+    # the wrapper refuses the rows the reference kernel mishandles
+    assert fn(_p(dp), 2, vocab // 2, _p(rsc_i), _p(rsc_v), _p(rf_i), _p(rf_v)) == -1
 
 
 # ---- a C++ caller of the drop-in templates beyond the reference's own (tiny) test shapes -----------
