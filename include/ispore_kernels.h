@@ -65,6 +65,21 @@ ISPORE_API const char* ispore_last_error_string(void);
 ISPORE_API void ispore_set_stream(ispore_stream_t stream);
 ISPORE_API ispore_stream_t ispore_get_stream(void);
 
+/* Programmatic dependent launch, per calling thread (default: off).
+ * ref: none — the reference launches every kernel with plain stream order.
+ * When on, the library's main kernels are launched with
+ * cudaLaunchAttributeProgrammaticStreamSerialization: a kernel may be scheduled
+ * while its predecessor on the same stream is still finishing its last CTAs, and
+ * waits on the device (griddepcontrol.wait) until that predecessor has completed
+ * and its memory is visible before it touches global memory.  Results are
+ * identical; what changes is that launch latency and CTA ramp-up of one kernel
+ * overlap the tail of the one before, which matters for chains of short kernels
+ * (decode steps, small token shards).  Works for plain launches and inside stream
+ * capture.  Only back-to-back kernels of this library overlap; anything else on
+ * the stream (copies, events, other libraries' kernels) orders as usual. */
+ISPORE_API void ispore_set_programmatic_launch(int enable);
+ISPORE_API int ispore_get_programmatic_launch(void);
+
 /* Copies the current device's status word to *flags_out (host) and optionally
  * clears it.  Synchronises the calling thread with the device; not for use
  * inside the hot loop.  Kernels never trap on bad data: they skip the access
@@ -320,6 +335,25 @@ ISPORE_API int ispore_topk_merge_f16(const int32_t* cand_ids, const void* cand_v
                                      int32_t lists, int32_t K, int32_t* final_ids, void* final_vals,
                                      const float* uniform, float temperature, int32_t* sampled_ids,
                                      ispore_stream_t stream);
+
+/* The same merge for candidate lists that are not laid out [rows, lists, K]: entry k of list a of
+ * row r is cand_ids[r * id_row_stride + a * id_list_stride + k] (values likewise; strides in
+ * ELEMENTS of the respective type, the K entries of a list contiguous).  [rows, lists, K] is
+ * (list stride K, row stride lists*K); a buffer that an all-gather filled with one block per rank,
+ * each block = that rank's [rows, K] ids followed by its [rows, K] values, is merged in place with
+ * list stride = block size and row stride K, cand_vals pointing rows*K ids into the first block —
+ * no re-layout between the collective and the merge.
+ * ref: src/kernels/topK.cu:48-74 (round 2); the strided form has no counterpart upstream. */
+ISPORE_API int ispore_topk_merge_strided_f32(const int32_t* cand_ids, const float* cand_vals, int64_t rows,
+                                             int32_t lists, int32_t K, int64_t id_list_stride, int64_t id_row_stride,
+                                             int64_t val_list_stride, int64_t val_row_stride, int32_t* final_ids,
+                                             float* final_vals, const float* uniform, float temperature,
+                                             int32_t* sampled_ids, ispore_stream_t stream);
+ISPORE_API int ispore_topk_merge_strided_f16(const int32_t* cand_ids, const void* cand_vals, int64_t rows,
+                                             int32_t lists, int32_t K, int64_t id_list_stride, int64_t id_row_stride,
+                                             int64_t val_list_stride, int64_t val_row_stride, int32_t* final_ids,
+                                             void* final_vals, const float* uniform, float temperature,
+                                             int32_t* sampled_ids, ispore_stream_t stream);
 
 /* ---- sampling from a top-K list --------------------------------------------- *
  * ref: absent from the reference (the only trace is the top_k entry that

@@ -24,9 +24,12 @@ SIGNATURES: dict[str, list] = {
     "ispore_last_error_string": [],
     "ispore_set_stream": [_p],
     "ispore_get_stream": [],
+    "ispore_set_programmatic_launch": [C.c_int],
+    "ispore_get_programmatic_launch": [],
     "ispore_device_status": [C.POINTER(C.c_uint), C.c_int],
 }
-_RESTYPES = {"ispore_last_error_string": C.c_char_p, "ispore_set_stream": None, "ispore_get_stream": _p}
+_RESTYPES = {"ispore_last_error_string": C.c_char_p, "ispore_set_stream": None, "ispore_get_stream": _p,
+             "ispore_set_programmatic_launch": None}
 
 for _t in ("f32", "f16"):
     SIGNATURES[f"ispore_add_residual_rmsnorm_{_t}"] = [_p, _p, _p, _p, _f, _i64, _i64, _p]
@@ -43,6 +46,7 @@ for _t in ("f32", "f16"):
     SIGNATURES[f"ispore_decoder_masked_mha_{_t}"] = [_p] * 5 + [_i64] * 8 + [_i32, _f, _f, _p, _i64, _p]
     SIGNATURES[f"ispore_topk_{_t}"] = [_p, _i64, _i64, _i32, _p, _p, _i32, _p, _p, _i32, _p, _f, _p, _p]
     SIGNATURES[f"ispore_topk_merge_{_t}"] = [_p, _p, _i64, _i32, _i32, _p, _p, _p, _f, _p, _p]
+    SIGNATURES[f"ispore_topk_merge_strided_{_t}"] = [_p, _p, _i64, _i32, _i32, _i64, _i64, _i64, _i64, _p, _p, _p, _f, _p, _p]
     SIGNATURES[f"ispore_sampling_{_t}"] = [_p, _p, _p, _p, _i64, _i32, _f, _p]
     SIGNATURES[f"ispore_build_causal_mask_{_t}"] = [_p, _p, _p, _i64, _i64, _i64, _p]
     SIGNATURES[f"ispore_transpose_remove_padding_{_t}"] = [_p, _p, _p, _i64, _i64, _i64, _i64, _i64, _p]

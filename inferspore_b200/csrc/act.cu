@@ -32,6 +32,7 @@ template <typename T, typename Index, int THREADS, int UNROLL>
 __global__ void __launch_bounds__(THREADS)
 silu_mul_vec_kernel(T* __restrict__ out, const T* __restrict__ in, Index total_vecs,
                     uint32_t inter_vecs) {
+    chain_begin();
     const uint4* in_v = reinterpret_cast<const uint4*>(in);
     uint4* out_v = reinterpret_cast<uint4*>(out);
     const Index tile = static_cast<Index>(THREADS) * UNROLL;
@@ -93,12 +94,12 @@ int silu_dispatch(T* out, const T* in, int64_t rows, int64_t inter, cudaStream_t
         const int64_t worst_grid = static_cast<int64_t>(sm_count()) * 8 * 64;
         if (total_vecs * 2 + worst_grid * THREADS * UNROLL < (1ll << 32)) {
             auto kernel = silu_mul_vec_kernel<T, uint32_t, THREADS, UNROLL>;
-            kernel<<<persistent_grid(kernel, THREADS, 0, tiles, tune(kTuneAct, 64)), THREADS, 0, st>>>(
-                out, in, static_cast<uint32_t>(total_vecs), static_cast<uint32_t>(inter_vecs));
+            launch_chained(kernel, persistent_grid(kernel, THREADS, 0, tiles, tune(kTuneAct, 64)), THREADS, 0, st,
+                           out, in, static_cast<uint32_t>(total_vecs), static_cast<uint32_t>(inter_vecs));
         } else {
             auto kernel = silu_mul_vec_kernel<T, uint64_t, THREADS, UNROLL>;
-            kernel<<<persistent_grid(kernel, THREADS, 0, tiles, tune(kTuneAct, 64)), THREADS, 0, st>>>(
-                out, in, static_cast<uint64_t>(total_vecs), static_cast<uint32_t>(inter_vecs));
+            launch_chained(kernel, persistent_grid(kernel, THREADS, 0, tiles, tune(kTuneAct, 64)), THREADS, 0, st,
+                           out, in, static_cast<uint64_t>(total_vecs), static_cast<uint32_t>(inter_vecs));
         }
         return check_launch("silu_mul_vec_kernel");
     }

@@ -13,6 +13,7 @@ namespace {
 
 thread_local char g_error[512] = "";
 thread_local cudaStream_t g_stream = nullptr;
+thread_local bool g_programmatic_launch = false;
 
 // One status word per device, in that device's memory.
 __device__ unsigned g_device_status = 0;
@@ -22,6 +23,8 @@ unsigned* g_status_addr[kMaxDevices] = {};
 std::mutex g_status_mutex;
 
 }  // namespace
+
+bool programmatic_launch_enabled() { return g_programmatic_launch; }
 
 int fail(int code, const char* fmt, ...) {
     va_list ap;
@@ -100,6 +103,40 @@ int resident_ctas(const void* kernel, int threads, size_t dynamic_smem) {
     return total;
 }
 
+bool allow_dynamic_smem(const void* kernel, size_t bytes) {
+    if (bytes <= 40 * 1024) return true;  // static shared memory of the kernel (a few KB) counts against the 48 KB default
+    struct Entry {
+        const void* kernel;
+        size_t granted;
+    };
+    constexpr int kSlots = 128;
+    static std::mutex mutex;
+    static Entry cache[kMaxDevices][kSlots] = {};
+    static int used[kMaxDevices] = {};
+    int dev = 0;
+    const bool cacheable = cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < kMaxDevices;
+    std::lock_guard<std::mutex> lock(mutex);
+    Entry* slot = nullptr;
+    if (cacheable) {
+        for (int i = 0; i < used[dev]; ++i)
+            if (cache[dev][i].kernel == kernel) slot = &cache[dev][i];
+        if (slot != nullptr && slot->granted >= bytes) return true;
+    }
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(bytes)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    if (cacheable) {
+        if (slot == nullptr && used[dev] < kSlots) {
+            slot = &cache[dev][used[dev]++];
+            slot->kernel = kernel;
+            slot->granted = 0;
+        }
+        if (slot != nullptr) slot->granted = bytes;
+    }
+    return true;
+}
+
 }  // namespace ispore
 
 extern "C" {
@@ -117,6 +154,10 @@ const char* ispore_last_error_string(void) { return ispore::g_error; }
 void ispore_set_stream(ispore_stream_t stream) { ispore::g_stream = static_cast<cudaStream_t>(stream); }
 
 ispore_stream_t ispore_get_stream(void) { return ispore::g_stream; }
+
+void ispore_set_programmatic_launch(int enable) { ispore::g_programmatic_launch = enable != 0; }
+
+int ispore_get_programmatic_launch(void) { return ispore::g_programmatic_launch ? 1 : 0; }
 
 int ispore_device_status(unsigned* flags_out, int clear) {
     if (flags_out == nullptr) return ispore::fail(ISPORE_ENULL, "device_status: flags_out is NULL");

@@ -20,6 +20,51 @@ int sm_count();                 // SMs of the current device (cached)
 // and device).  Persistent grid-stride kernels launch exactly this many CTAs:
 // one more would wait for a free slot and start its whole share of the work late.
 int resident_ctas(const void* kernel, int threads, size_t dynamic_smem);
+// Makes sure `kernel` may be launched with `bytes` of dynamic shared memory on the current device.
+// Sizes well inside the 48 KB default (40 KB, leaving room for the kernel's static shared memory)
+// need nothing; above that cudaFuncSetAttribute is called once per
+// (device, kernel) for the largest size seen so far, not on every launch.  Returns false when the
+// runtime refuses (the sticky-free error is cleared).
+bool allow_dynamic_smem(const void* kernel, size_t bytes);
+template <typename Kernel>
+inline bool allow_dynamic_smem(Kernel kernel, size_t bytes) {
+    return allow_dynamic_smem(reinterpret_cast<const void*>(kernel), bytes);
+}
+
+// ---- programmatic dependent launch ---------------------------------------------
+// A kernel launched through launch_chained() may be scheduled while its predecessor on the
+// stream is still draining its last CTAs (the launch carries
+// cudaLaunchAttributeProgrammaticStreamSerialization when the calling thread has switched that
+// on with ispore_set_programmatic_launch).  Every kernel launched this way starts with
+// chain_begin(): it lets ITS successor be scheduled early in turn and then waits until the
+// predecessor grid has completed and its memory is visible, before the first global access.
+// Launched without the attribute both instructions are no-ops, so the same kernel serves both
+// modes.  The wait is unconditional and precedes every early return, so a grid can only complete
+// after its predecessor has: ordering stays transitive along the stream.
+bool programmatic_launch_enabled();  // thread-local, c_api.cu
+
+__device__ __forceinline__ void chain_begin() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t dynamic_smem, cudaStream_t st,
+                           Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = dynamic_smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    if (programmatic_launch_enabled()) {
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+    }
+    (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // the caller reads the status with check_launch()
+}
 
 // Launch-shape experiments: a build with -DISPORE_TUNING exports ispore_tune(key, value)
 // and dispatchers consult tune(key, default); the shipped build compiles this to the default.

@@ -29,6 +29,7 @@ concat_kv_tma_kernel(unsigned char* __restrict__ k_dst, unsigned char* __restric
                      unsigned* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char slots[];  // [ROWS][chunk_bytes]
     __shared__ __align__(8) uint64_t full[ROWS];
+    chain_begin();
     const int lane = threadIdx.x;
     if (lane < ROWS) tma::mbar_init(&full[lane], 1);
     tma::fence_mbar_init();
@@ -139,11 +140,11 @@ int concat_dispatch(T* k_dst, T* v_dst, const T* k_src, const T* v_src, const in
             auto vs = reinterpret_cast<const unsigned char*>(v_src);
             const int64_t lo_bytes = layer_offset * static_cast<int64_t>(sizeof(T));
             if (chunk >= 2048) {
-                concat_kv_tma_kernel<4><<<static_cast<unsigned>(ceil_div(pieces, 4)), 32, 4 * chunk, st>>>(
+                launch_chained(concat_kv_tma_kernel<4>, static_cast<unsigned>(ceil_div(pieces, 4)), 32, 4 * chunk, st,
                     kb, vb, ks, vs, cur_len, hist_len, lo_bytes, (int)kv_heads, (int)(batch * kv_heads), (int)max_q_len,
                     max_seq_len, (uint32_t)row_bytes, chunk, (uint32_t)cps, status);
             } else {
-                concat_kv_tma_kernel<16><<<static_cast<unsigned>(ceil_div(pieces, 16)), 32, 16 * chunk, st>>>(
+                launch_chained(concat_kv_tma_kernel<16>, static_cast<unsigned>(ceil_div(pieces, 16)), 32, 16 * chunk, st,
                     kb, vb, ks, vs, cur_len, hist_len, lo_bytes, (int)kv_heads, (int)(batch * kv_heads), (int)max_q_len,
                     max_seq_len, (uint32_t)row_bytes, chunk, (uint32_t)cps, status);
             }

@@ -744,12 +744,8 @@ int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, c
                                            static_cast<size_t>(kMhaWarps) * GT * D);
     const size_t stage = 16384 + (kPadded ? 8 * 16 : 0);
     const size_t smem = floats * sizeof(float) + (STAGED ? static_cast<size_t>(kStages) * stage : 0);
-    if (smem > 40 * 1024) {
-        if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess) {
-            cudaGetLastError();
-            return fail(ISPORE_ELAUNCH, "decoder_masked_mha: %zu bytes of shared memory refused", smem);
-        }
-    }
+    if (!allow_dynamic_smem(kernel, smem))
+        return fail(ISPORE_ELAUNCH, "decoder_masked_mha: %zu bytes of shared memory refused", smem);
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "decoder_masked_mha: no device status word");
     dim3 grid(static_cast<unsigned>(batch * p.kv_heads * p.head_groups), static_cast<unsigned>(p.splits));

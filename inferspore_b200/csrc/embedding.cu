@@ -18,6 +18,7 @@ __global__ void __launch_bounds__(THREADS)
 embedding_gather_vec_kernel(const int32_t* __restrict__ ids, uint4* __restrict__ out,
                             const uint4* __restrict__ table, int64_t num_tokens, int row_vecs,
                             int64_t vocab, unsigned* __restrict__ status) {
+    chain_begin();
     constexpr int kWarps = THREADS / 32;
     const int lane = threadIdx.x & 31;
     const int64_t warp_global = static_cast<int64_t>(blockIdx.x) * kWarps + (threadIdx.x >> 5);
@@ -60,6 +61,7 @@ embedding_gather_tma_kernel(const int32_t* __restrict__ ids, unsigned char* __re
                             int64_t vocab, unsigned* __restrict__ status) {
     extern __shared__ __align__(128) unsigned char slots[];  // [ROWS][row_bytes]
     __shared__ __align__(8) uint64_t full[ROWS];
+    chain_begin();
     const int lane = threadIdx.x;
     const int64_t t = static_cast<int64_t>(blockIdx.x) * ROWS + lane;
     const bool mine = lane < ROWS && t < num_tokens;
@@ -123,11 +125,9 @@ int embedding_dispatch(const int32_t* ids, T* out, const T* table, int64_t token
 #define ISPORE_EMB_TMA(ROWS)                                                                                     \
     do {                                                                                                         \
         const size_t smem = static_cast<size_t>(ROWS) * row_bytes;                                               \
-        if (smem > 48 * 1024)                                                                                    \
-            cudaFuncSetAttribute(embedding_gather_tma_kernel<ROWS>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                 static_cast<int>(smem));                                                        \
-        embedding_gather_tma_kernel<ROWS><<<static_cast<unsigned>(ceil_div(tokens, ROWS)), 32, smem, st>>>(      \
-            ids, ob, tb, tokens, static_cast<uint32_t>(row_bytes), vocab, status);                               \
+        if (!allow_dynamic_smem(embedding_gather_tma_kernel<ROWS>, smem)) break;                                \
+        launch_chained(embedding_gather_tma_kernel<ROWS>, static_cast<unsigned>(ceil_div(tokens, ROWS)), 32,     \
+                       smem, st, ids, ob, tb, tokens, static_cast<uint32_t>(row_bytes), vocab, status);          \
         return check_launch("embedding_gather_tma_kernel");                                                      \
     } while (0)
         if (variant == 1) ISPORE_EMB_TMA(1);
@@ -140,9 +140,9 @@ int embedding_dispatch(const int32_t* ids, T* out, const T* table, int64_t token
         constexpr int THREADS = 256, UNROLL = 4;
         const int64_t blocks = ceil_div(tokens, THREADS / 32);
         auto kernel = embedding_gather_vec_kernel<THREADS, UNROLL>;
-        kernel<<<persistent_grid(kernel, THREADS, 0, blocks, 16), THREADS, 0, st>>>(
-                ids, reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(table), tokens,
-                static_cast<int>(hidden / E), vocab, status);
+        launch_chained(kernel, persistent_grid(kernel, THREADS, 0, blocks, 16), THREADS, 0, st, ids,
+                       reinterpret_cast<uint4*>(out), reinterpret_cast<const uint4*>(table), tokens,
+                       static_cast<int>(hidden / E), vocab, status);
         return check_launch("embedding_gather_vec_kernel");
     }
     embedding_gather_scalar_kernel<T><<<persistent_grid(embedding_gather_scalar_kernel<T>, 256, 0, tokens), 256, 0, st>>>(

@@ -49,6 +49,7 @@ qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
                               unsigned* __restrict__ status) {
     constexpr int E = VecTraits<T>::kElems;
     __shared__ float2 cos_sin[kMaxRotHalf];
+    chain_begin();
     const int tid = threadIdx.x;
     const int head_size = HEAD_SIZE > 0 ? HEAD_SIZE : head_size_arg;
     const int head_vecs = head_size / E;
@@ -212,6 +213,7 @@ qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
     extern __shared__ __align__(128) unsigned char token_raw[];
     __shared__ float2 cos_sin[HEAD_SIZE > 0 ? HEAD_SIZE / 2 : kMaxRotHalf];
     __shared__ __align__(8) uint64_t bar;
+    chain_begin();
     const int tid = threadIdx.x;
     const int qkv_heads = head_num + 2 * kv_head_num;
     const int64_t token = blockIdx.x;
@@ -427,7 +429,7 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
         const bool has_bias = bias != nullptr;
 #define ISPORE_QKV(HS, FR, HB)                                                                           \
     do {                                                                                                 \
-        qkv_rope_transpose_vec_kernel<T, TH, HS, FR, HB><<<grid, TH, 0, st>>>(                           \
+        launch_chained(qkv_rope_transpose_vec_kernel<T, TH, HS, FR, HB>, grid, TH, 0, st,                \
             q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,        \
             token_num, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);     \
         return check_launch("qkv_rope_transpose_vec_kernel");                                           \
@@ -440,12 +442,8 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
     do {                                                                                                    \
         constexpr int TH = 128; /* measured: 64 and 256 threads are 3-6 % slower */                         \
         auto kernel = qkv_rope_transpose_tma_kernel<T, TH, HS, FR, HB>;                                     \
-        if (token_bytes > 40 * 1024 &&                                                                      \
-            cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)token_bytes) != cudaSuccess) { \
-            cudaGetLastError();                                                                             \
-            break;                                                                                          \
-        }                                                                                                   \
-        kernel<<<static_cast<unsigned>(token_num), TH, static_cast<size_t>(token_bytes), st>>>(             \
+        if (!allow_dynamic_smem(kernel, static_cast<size_t>(token_bytes))) break;                           \
+        launch_chained(kernel, static_cast<unsigned>(token_num), TH, static_cast<size_t>(token_bytes), st,  \
             q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,           \
             (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);                    \
         return check_launch("qkv_rope_transpose_tma_kernel");                                               \

@@ -61,6 +61,7 @@ softmax_head_group_kernel(T* __restrict__ score, const T* __restrict__ qk, const
     constexpr int kWarpsPerGroup = GROUP / 32;
     using Exp = ExpPolicy<T>;
     __shared__ float red[2][kWarpsPerGroup > 1 ? kWarpsPerGroup : 1];  // only used when a CTA is one group
+    chain_begin();
 
     const int tid = threadIdx.x;
     const int g = tid / GROUP;   // group slot inside the CTA
@@ -360,10 +361,9 @@ int launch_groups(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch,
     // One trip per CTA for any realistic size: the hardware scheduler hands out CTAs in
     // address order, which keeps the DRAM access front compact.
     const int grid = static_cast<int>(ctas < (1 << 30) ? ctas : (1 << 30));
-    kernel<<<grid, THREADS, 0, st>>>(score, qk, ms.mask, ms.q_lens, ms.k_lens, static_cast<uint32_t>(units),
-                                     static_cast<uint32_t>(head_groups), static_cast<uint32_t>(heads),
-                                     static_cast<uint32_t>(q_len), row_vecs, scale, log2_or_minus1(q_len),
-                                     log2_or_minus1(head_groups));
+    launch_chained(kernel, grid, THREADS, 0, st, score, qk, ms.mask, ms.q_lens, ms.k_lens, static_cast<uint32_t>(units),
+                   static_cast<uint32_t>(head_groups), static_cast<uint32_t>(heads), static_cast<uint32_t>(q_len),
+                   row_vecs, scale, log2_or_minus1(q_len), log2_or_minus1(head_groups));
     return check_launch("softmax_head_group_kernel");
 }
 
@@ -543,6 +543,7 @@ softmax_offset_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const
     constexpr bool kBlock = GROUP == 0;
     using Exp = ExpPolicy<T>;
     __shared__ float red_max[THREADS / 32], red_sum[THREADS / 32];  // each written once per row: no barrier after the read
+    chain_begin();
     const int tid = threadIdx.x;
     const int group = kBlock ? static_cast<int>(blockDim.x) : GROUP;
     const int gt = kBlock ? tid : (tid & 31);
@@ -682,7 +683,7 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
 #define ISPORE_SOFTMAX_OFFSET(VPT, GROUP, THREADS, rows_per_cta, threads)                                          \
     do {                                                                                                           \
         const unsigned ctas = static_cast<unsigned>(ceil_div(total_rows, static_cast<int64_t>(rows_per_cta)));      \
-        softmax_offset_row_kernel<T, VPT, GROUP, THREADS, CAUSAL><<<ctas, threads, 0, st>>>(                        \
+        launch_chained(softmax_offset_row_kernel<T, VPT, GROUP, THREADS, CAUSAL>, ctas, threads, 0, st,             \
             score, qk, ms.mask, ms.q_lens, ms.k_lens, static_cast<uint32_t>(total_rows), static_cast<int>(batch),  \
             static_cast<int>(q_len), static_cast<int>(k_len), InvariantDivisor(static_cast<uint32_t>(q_len)),      \
             InvariantDivisor(static_cast<uint32_t>(heads)), scale);                                                \

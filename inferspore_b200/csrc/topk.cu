@@ -304,6 +304,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     __shared__ int hist[256];
     __shared__ int s_digit, s_need;
     __shared__ int warp_cnt[kTopkWarps];
+    chain_begin();
 
     const int tid = threadIdx.x;
     const int64_t row = blockIdx.x / slices;
@@ -470,25 +471,31 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
 
 template <typename T>
 __global__ void __launch_bounds__(kTopkThreads)
-topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ cand_vals, int lists,
-                  int list_stride /* lists allocated per row */, int K, int32_t* __restrict__ final_ids,
-                  T* __restrict__ final_vals, const float* __restrict__ uniform, float temperature,
-                  int32_t* __restrict__ sampled_ids) {
+topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ cand_vals, int lists, int K,
+                  int64_t id_list_stride, int64_t id_row_stride, int64_t val_list_stride, int64_t val_row_stride,
+                  int32_t* __restrict__ final_ids, T* __restrict__ final_vals, const float* __restrict__ uniform,
+                  float temperature, int32_t* __restrict__ sampled_ids) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     unsigned long long* comp = reinterpret_cast<unsigned long long*>(smem_raw);  // [lists*K]
     __shared__ int32_t fin_ids[ISPORE_TOPK_MAX_K];
     __shared__ T fin_vals[ISPORE_TOPK_MAX_K];
     __shared__ float p_smem[ISPORE_TOPK_MAX_K];
+    chain_begin();
 
     const int tid = threadIdx.x;
     const int64_t row = blockIdx.x;
     const int total = lists * K;
-    const int32_t* ids = cand_ids + row * list_stride * K;
-    const T* vals = cand_vals + row * list_stride * K;
+    // Entry k of list a of this row sits at a * list_stride + k behind the row's base: lists of a
+    // row next to each other ([rows, lists, K], the slice kernel's scratch) or one block per list
+    // ([lists, rows, K], what an all-gather of per-rank results leaves behind).
+    const int32_t* ids = cand_ids + row * id_row_stride;
+    const T* vals = cand_vals + row * val_row_stride;
+    auto id_at = [&](int c) { const int a = c / K; return ids[a * id_list_stride + (c - a * K)]; };
+    auto val_at = [&](int c) { const int a = c / K; return vals[a * val_list_stride + (c - a * K)]; };
 
     for (int c = tid; c < total; c += kTopkThreads) {
-        const int32_t id = ids[c];
-        comp[c] = id < 0 ? 0ull : composite(order_key(to_float<T>(vals[c])), static_cast<uint32_t>(id));
+        const int32_t id = id_at(c);
+        comp[c] = id < 0 ? 0ull : composite(order_key(to_float<T>(val_at(c))), static_cast<uint32_t>(id));
     }
     for (int s = tid; s < K; s += kTopkThreads) {
         fin_ids[s] = -1;
@@ -515,8 +522,8 @@ topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ ca
             for (int j = 0; j < total; ++j) rank += comp[j] > mine;
         }
         if (rank < K) {
-            fin_ids[rank] = ids[c];
-            fin_vals[rank] = vals[c];
+            fin_ids[rank] = id_at(c);
+            fin_vals[rank] = val_at(c);
         }
     }
     __syncthreads();
@@ -560,11 +567,14 @@ int sampling_dispatch(const int32_t* ids, const T* vals, const float* uniform, i
 }
 
 template <typename T>
-int merge_dispatch(const int32_t* cand_ids, const T* cand_vals, int64_t rows, int32_t lists,
-                   int32_t list_stride, int32_t K, int32_t* final_ids, T* final_vals,
-                   const float* uniform, float temperature, int32_t* sampled_ids, cudaStream_t st) {
+int merge_dispatch(const int32_t* cand_ids, const T* cand_vals, int64_t rows, int32_t lists, int32_t K,
+                   int64_t id_list_stride, int64_t id_row_stride, int64_t val_list_stride, int64_t val_row_stride,
+                   int32_t* final_ids, T* final_vals, const float* uniform, float temperature, int32_t* sampled_ids,
+                   cudaStream_t st) {
     if (int rc = check_k("topk_merge", K)) return rc;
     if (rows < 0 || lists < 1 || rows > INT32_MAX) return fail(ISPORE_ESHAPE, "topk_merge: rows=%lld lists=%d", (long long)rows, lists);
+    if (id_list_stride < 0 || id_row_stride < 0 || val_list_stride < 0 || val_row_stride < 0)
+        return fail(ISPORE_ESHAPE, "topk_merge: negative stride");
     if (static_cast<int64_t>(lists) * K > kMergeCap)
         return fail(ISPORE_ELIMIT, "topk_merge: lists*K=%lld > %d", (long long)lists * K, kMergeCap);
     if (uniform != nullptr && !(temperature > 0.f)) return fail(ISPORE_ESHAPE, "topk_merge: temperature must be > 0");
@@ -572,8 +582,9 @@ int merge_dispatch(const int32_t* cand_ids, const T* cand_vals, int64_t rows, in
     if (!cand_ids || !cand_vals || !final_ids || !final_vals) return fail(ISPORE_ENULL, "topk_merge: NULL buffer");
     if (uniform != nullptr && sampled_ids == nullptr) return fail(ISPORE_ENULL, "topk_merge: uniform given without sampled_ids");
     const size_t smem = static_cast<size_t>(lists) * K * sizeof(unsigned long long);
-    topk_merge_kernel<T><<<static_cast<int>(rows), kTopkThreads, smem, st>>>(
-        cand_ids, cand_vals, lists, list_stride, K, final_ids, final_vals, uniform, temperature, sampled_ids);
+    launch_chained(topk_merge_kernel<T>, static_cast<int>(rows), kTopkThreads, smem, st, cand_ids, cand_vals, lists, K,
+                   id_list_stride, id_row_stride, val_list_stride, val_row_stride, final_ids, final_vals, uniform,
+                   temperature, sampled_ids);
     return check_launch("topk_merge_kernel");
 }
 
@@ -603,16 +614,8 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     constexpr size_t kTmaSmem = 2 * static_cast<size_t>(kTileElems) * sizeof(T);
     auto kernel = use_tma ? topk_slice_kernel<T, 3, true> : topk_slice_kernel<T, 4, false>;
     const size_t smem = use_tma ? kTmaSmem : 0;
-    if (use_tma && kTmaSmem > 48 * 1024) {
-        static bool raised[64] = {};  // per device (and per instantiation); setting it twice is harmless
-        int dev = 0;
-        (void)cudaGetDevice(&dev);
-        if (dev < 0 || dev >= 64 || !raised[dev]) {
-            cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kTmaSmem));
-            if (e != cudaSuccess) return fail(ISPORE_ELAUNCH, "topk: cannot raise dynamic shared memory: %s", cudaGetErrorString(e));
-            if (dev >= 0 && dev < 64) raised[dev] = true;
-        }
-    }
+    if (use_tma && !allow_dynamic_smem(kernel, kTmaSmem))
+        return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", kTmaSmem);
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "topk: no device status word");
     const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, smem);
@@ -634,17 +637,17 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
 
     if (slices == 1) {
         // The slice kernel's sorted list is already the answer.
-        kernel<<<static_cast<int>(rows), kTopkThreads, smem, st>>>(probs, vocab, static_cast<int>(slice_len), 1, K,
-                                                                   final_ids, final_vals, 1, index_offset, vec_loads,
-                                                                   status, uniform, temperature, sampled_ids);
+        launch_chained(kernel, static_cast<int>(rows), kTopkThreads, smem, st, probs, vocab, static_cast<int>(slice_len), 1, K,
+                       final_ids, final_vals, 1, index_offset, vec_loads, status, uniform, temperature, sampled_ids);
         return check_launch("topk_slice_kernel");
     }
-    kernel<<<static_cast<int>(rows * slices), kTopkThreads, smem, st>>>(
-        probs, vocab, static_cast<int>(slice_len), static_cast<int>(slices), K, scratch_ids, scratch_vals,
-        scratch_slices, index_offset, vec_loads, status, nullptr, 1.0f, nullptr);
+    launch_chained(kernel, static_cast<int>(rows * slices), kTopkThreads, smem, st, probs, vocab,
+                   static_cast<int>(slice_len), static_cast<int>(slices), K, scratch_ids, scratch_vals, scratch_slices,
+                   index_offset, vec_loads, status, nullptr, 1.0f, nullptr);
     if (int rc = check_launch("topk_slice_kernel")) return rc;
-    return merge_dispatch<T>(scratch_ids, scratch_vals, rows, static_cast<int32_t>(slices), scratch_slices, K,
-                             final_ids, final_vals, uniform, temperature, sampled_ids, st);
+    const int64_t row_stride = static_cast<int64_t>(scratch_slices) * K;
+    return merge_dispatch<T>(scratch_ids, scratch_vals, rows, static_cast<int32_t>(slices), K, K, row_stride, K,
+                             row_stride, final_ids, final_vals, uniform, temperature, sampled_ids, st);
 }
 
 }  // namespace
@@ -721,16 +724,35 @@ int ispore_topk_f16(const void* probs, int64_t rows, int64_t vocab, int32_t K, i
 int ispore_topk_merge_f32(const int32_t* cand_ids, const float* cand_vals, int64_t rows, int32_t lists,
                           int32_t K, int32_t* final_ids, float* final_vals, const float* uniform,
                           float temperature, int32_t* sampled_ids, ispore_stream_t stream) {
-    return ispore::merge_dispatch<float>(cand_ids, cand_vals, rows, lists, lists, K, final_ids, final_vals,
-                                         uniform, temperature, sampled_ids,
+    const int64_t row_stride = static_cast<int64_t>(lists) * K;
+    return ispore::merge_dispatch<float>(cand_ids, cand_vals, rows, lists, K, K, row_stride, K, row_stride, final_ids,
+                                         final_vals, uniform, temperature, sampled_ids,
                                          static_cast<cudaStream_t>(stream));
+}
+int ispore_topk_merge_strided_f32(const int32_t* cand_ids, const float* cand_vals, int64_t rows, int32_t lists,
+                                  int32_t K, int64_t id_list_stride, int64_t id_row_stride, int64_t val_list_stride,
+                                  int64_t val_row_stride, int32_t* final_ids, float* final_vals, const float* uniform,
+                                  float temperature, int32_t* sampled_ids, ispore_stream_t stream) {
+    return ispore::merge_dispatch<float>(cand_ids, cand_vals, rows, lists, K, id_list_stride, id_row_stride,
+                                         val_list_stride, val_row_stride, final_ids, final_vals, uniform, temperature,
+                                         sampled_ids, static_cast<cudaStream_t>(stream));
+}
+int ispore_topk_merge_strided_f16(const int32_t* cand_ids, const void* cand_vals, int64_t rows, int32_t lists,
+                                  int32_t K, int64_t id_list_stride, int64_t id_row_stride, int64_t val_list_stride,
+                                  int64_t val_row_stride, int32_t* final_ids, void* final_vals, const float* uniform,
+                                  float temperature, int32_t* sampled_ids, ispore_stream_t stream) {
+    return ispore::merge_dispatch<__half>(cand_ids, static_cast<const __half*>(cand_vals), rows, lists, K,
+                                          id_list_stride, id_row_stride, val_list_stride, val_row_stride, final_ids,
+                                          static_cast<__half*>(final_vals), uniform, temperature, sampled_ids,
+                                          static_cast<cudaStream_t>(stream));
 }
 int ispore_topk_merge_f16(const int32_t* cand_ids, const void* cand_vals, int64_t rows, int32_t lists,
                           int32_t K, int32_t* final_ids, void* final_vals, const float* uniform,
                           float temperature, int32_t* sampled_ids, ispore_stream_t stream) {
-    return ispore::merge_dispatch<__half>(cand_ids, static_cast<const __half*>(cand_vals), rows, lists, lists,
-                                          K, final_ids, static_cast<__half*>(final_vals), uniform,
-                                          temperature, sampled_ids, static_cast<cudaStream_t>(stream));
+    const int64_t row_stride = static_cast<int64_t>(lists) * K;
+    return ispore::merge_dispatch<__half>(cand_ids, static_cast<const __half*>(cand_vals), rows, lists, K, K,
+                                          row_stride, K, row_stride, final_ids, static_cast<__half*>(final_vals),
+                                          uniform, temperature, sampled_ids, static_cast<cudaStream_t>(stream));
 }
 int ispore_sampling_f32(const int32_t* topk_ids, const float* topk_vals, const float* uniform,
                         int32_t* output_ids, int64_t rows, int32_t K, float temperature,

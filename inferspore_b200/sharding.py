@@ -74,43 +74,58 @@ def gather_candidates(local_ids: torch.Tensor, local_vals: torch.Tensor,
 
 class VocabShardedTopK:
     """Top-K (and optional sampling) over logits whose vocab axis is split across ranks, with
-    every buffer allocated once: local top-K with global ids, ONE all-gather of the packed
-    (ids | values) candidate lists, merge (+ sampling) on every rank."""
+    every buffer allocated once: local top-K with global ids written straight into this rank's
+    packed record ([rows, K] int32 ids | [rows, K] values, padded to 16 bytes), ONE all-gather of
+    the records, and a merge (+ sampling) on every rank that reads the gathered buffer in place
+    (ispore_topk_merge_strided_*: one list per rank, list stride = record size).  Three launches
+    per call — local top-K, the collective, the merge — and no re-layout copy."""
 
     def __init__(self, rows: int, K: int, dtype: torch.dtype, device: torch.device,
                  group: Optional[dist.ProcessGroup] = None, slices: int = 8):
+        from . import ops
+
         self.rows, self.K, self.group = rows, K, group
         self.world = dist.get_world_size(group)
         esize = torch.empty((), dtype=dtype).element_size()
         ids_bytes, vals_bytes = rows * K * 4, rows * K * esize
-        self.packed = torch.empty(ids_bytes + vals_bytes, dtype=torch.uint8, device=device)
+        self.record_bytes = ops.packed_record_bytes(rows, K, dtype)
+        self.packed = torch.zeros(self.record_bytes, dtype=torch.uint8, device=device)
         self.loc_i = self.packed[:ids_bytes].view(torch.int32).view(rows, K)
-        self.loc_v = self.packed[ids_bytes:].view(dtype).view(rows, K)
-        self.gathered = torch.empty((self.world, ids_bytes + vals_bytes), dtype=torch.uint8, device=device)
-        self.all_i = self.gathered[:, :ids_bytes].view(torch.int32).view(self.world, rows, K)  # strided views
-        self.all_v = self.gathered[:, ids_bytes:].view(dtype).view(self.world, rows, K)
-        self.cand_i = torch.empty((rows, self.world, K), dtype=torch.int32, device=device)
-        self.cand_v = torch.empty((rows, self.world, K), dtype=dtype, device=device)
+        self.loc_v = self.packed[ids_bytes:ids_bytes + vals_bytes].view(dtype).view(rows, K)
+        self.gathered = torch.empty((self.world, self.record_bytes), dtype=torch.uint8, device=device)
         self.sc_i = torch.empty((rows, slices, K), dtype=torch.int32, device=device)
         self.sc_v = torch.empty((rows, slices, K), dtype=dtype, device=device)
         self.out_i = torch.empty((rows, K), dtype=torch.int32, device=device)
         self.out_v = torch.empty((rows, K), dtype=dtype, device=device)
         self.picked = torch.empty((rows,), dtype=torch.int32, device=device)
 
-    def __call__(self, local_logits: torch.Tensor, shard: Shard, uniform: Optional[torch.Tensor] = None,
-                 temperature: float = 1.0):
+    def local(self, local_logits: torch.Tensor, shard: Shard) -> None:
+        """Step 1: this rank's candidates (global ids) into its packed record."""
         from . import ops
 
         if local_logits.shape != (self.rows, shard.size):
             raise ValueError("local logits must be [rows, shard.size]")
         ops.launchTopKforBeamSearch(local_logits, self.sc_i, self.sc_v, self.loc_i, self.loc_v,
                                     index_offset=shard.start)
+
+    def exchange(self) -> None:
+        """Step 2: every rank's record to every rank (the path's only collective)."""
         dist.all_gather_into_tensor(self.gathered.view(-1), self.packed, group=self.group)
-        self.cand_i.copy_(self.all_i.permute(1, 0, 2))  # rank-major -> the merge kernel's [rows, lists, K]
-        self.cand_v.copy_(self.all_v.permute(1, 0, 2))
+
+    def merge(self, uniform: Optional[torch.Tensor] = None, temperature: float = 1.0):
+        """Step 3: merge the gathered lists where they lie; optionally draw one id per row."""
+        from . import ops
+
         picked = self.picked if uniform is not None else None
-        ops.launchTopKMerge(self.cand_i, self.cand_v, self.out_i, self.out_v, uniform, temperature, picked)
+        ops.launchTopKMergeGathered(self.gathered, self.world, self.rows, self.K, self.out_i, self.out_v, uniform,
+                                    temperature, picked)
         return self.out_i, self.out_v, picked
+
+    def __call__(self, local_logits: torch.Tensor, shard: Shard, uniform: Optional[torch.Tensor] = None,
+                 temperature: float = 1.0):
+        self.local(local_logits, shard)
+        self.exchange()
+        return self.merge(uniform, temperature)
 
 
 _SHARDED_TOPK_CACHE: dict = {}

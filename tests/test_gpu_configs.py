@@ -30,7 +30,19 @@ def _sync_and_free(cuda):
     torch.cuda.empty_cache()
 
 
-def test_config1_embedding_qkv_rope_full_size(ops, orc, rng):
+def test_config1_fused_residual_rmsnorm_fp32_unit_test_shape(ops, orc, rng):
+    # BASELINE config 1: input [64, 4096] ~N(0,1), residual ~N(0,1), gamma ~U(0.5,1.5), eps 1e-6, fp32
+    x = rng.standard_normal((64, HIDDEN), dtype=np.float32)
+    r = rng.standard_normal((64, HIDDEN), dtype=np.float32)
+    g = rng.uniform(0.5, 1.5, HIDDEN).astype(np.float32)
+    dx, dr = dev(x), dev(r)
+    ops.launchFusedAddBiasResidualRMSNorm(dr, dx, None, dev(g), 1e-6)
+    want_x, want_r, _ = orc.add_residual_rmsnorm(x, r, None, g, 1e-6)
+    assert np.array_equal(host(dr), want_r)  # the updated residual is one IEEE add
+    assert_close_f32(host(dx), want_x, what="config 1 normed output")
+
+
+def test_config2_embedding_qkv_rope_full_size(ops, orc, rng):
     batch, seq = 8, 512
     tokens = batch * seq
     ids = rng.integers(0, VOCAB, tokens).astype(np.int32)
@@ -50,11 +62,11 @@ def test_config1_embedding_qkv_rope_full_size(ops, orc, rng):
     wq, wk, wv, q32, k32 = orc.qkv_bias_rope_transpose(qkv, bias, pad, hist, batch, seq, HEADS, HEADS, HEAD_SIZE, 10000.0)
     assert np.array_equal(host(v).view(np.uint16), wv.view(np.uint16))  # one rounded add, no rotation
     for got, want32, want in ((q, q32, wq), (k, k32, wk)):
-        err, over, same = assert_close_f16(host(got), want32, want, "config 1 q/k")
+        err, over, same = assert_close_f16(host(got), want32, want, "config 2 q/k")
         assert over == 0 and same > 0.99
 
 
-def test_config2_norm_and_silu_full_size(ops, orc, rng):
+def test_config3_norm_and_silu_full_size(ops, orc, rng):
     tokens = 16384
     x, r = randn16(rng, (tokens, HIDDEN)), randn16(rng, (tokens, HIDDEN))
     g = rng.uniform(0.5, 1.5, HIDDEN).astype(np.float16)
@@ -62,7 +74,7 @@ def test_config2_norm_and_silu_full_size(ops, orc, rng):
     ops.launchFusedAddBiasResidualRMSNorm(dr, dx, None, dev(g), 1e-6)
     want_x, want_r, want32 = orc.add_residual_rmsnorm(x, r, None, g, 1e-6)
     assert np.array_equal(host(dr).view(np.uint16), want_r.view(np.uint16))
-    err, over, _ = assert_close_f16(host(dx), want32, want_x, "config 2 norm")
+    err, over, _ = assert_close_f16(host(dx), want32, want_x, "config 3 norm")
     assert over == 0
     del dx, dr
 
@@ -70,11 +82,11 @@ def test_config2_norm_and_silu_full_size(ops, orc, rng):
     out = torch.empty((tokens, INTER), dtype=torch.float16, device="cuda:0")
     ops.launchAct(dev(act), out)
     want, want32 = orc.silu_mul(act)
-    err, over, same = assert_close_f16(host(out), want32, want, "config 2 SiLU*up")
+    err, over, same = assert_close_f16(host(out), want32, want, "config 3 SiLU*up")
     assert same > 0.999  # the few over-2e-3 elements are |value| >= 8, checked inside
 
 
-def test_config3_decode_cache_beyond_32_bit_offsets(ops, rng):
+def test_config4_decode_cache_beyond_32_bit_offsets(ops, rng):
     # 9 layers of [64, 32, 4096, 128] halves: layer 8 starts 8.6e9 elements into the cache
     layers, batch, heads, max_seq = 9, 64, 32, 4096
     g = torch.Generator(device="cuda:0")
@@ -98,7 +110,7 @@ def test_config3_decode_cache_beyond_32_bit_offsets(ops, rng):
         assert int(torch.count_nonzero(cache[layer])) == int(torch.count_nonzero(src))
 
 
-def test_config3_decode_softmax_full_size(ops, orc, rng):
+def test_config4_decode_softmax_full_size(ops, orc, rng):
     batch, k_len = 64, 4096
     steps = rng.integers(1, k_len, batch)
     qk = randn16(rng, (batch, HEADS, 1, k_len), 3.0)
@@ -108,12 +120,12 @@ def test_config3_decode_softmax_full_size(ops, orc, rng):
     ops.launchScaleMaskAndSoftmax(dev(qk), dev(mask), out, scale)
     want, want32 = orc.scale_mask_softmax(qk, mask, np.float32(scale))
     got = host(out)
-    err, over, _ = assert_close_f16(got, want32, want, "config 3 softmax")
+    err, over, _ = assert_close_f16(got, want32, want, "config 4 softmax")
     assert over == 0
     assert np.all(got[np.broadcast_to(mask[:, None] == 0, got.shape)] == 0)
 
 
-def test_config3_decode_attention_full_size(ops, orc, rng):
+def test_config4_decode_attention_full_size(ops, orc, rng):
     # the fused decode attention at the configuration's batch, heads and cache depth; the oracle
     # (a few G multiply-adds) runs on a quarter of the sequences, the rest is checked for agreement
     # between the split and the unsplit kernel
@@ -137,12 +149,12 @@ def test_config3_decode_attention_full_size(ops, orc, rng):
     want, want_k, want_v, want32 = orc.decoder_masked_mha(host(qkv[:nb]), None, host(kc2[:, :nb]), host(vc2[:, :nb]), 0,
                                                           step, HEAD_SIZE, 10000.0)
     # (the caches handed to the oracle already hold the new row; it writes the same row again)
-    err, over, _ = assert_close_f16(host(out[:nb]), want32, want, "config 3 decode attention")
+    err, over, _ = assert_close_f16(host(out[:nb]), want32, want, "config 4 decode attention")
     assert over == 0
     assert np.array_equal(host(vc[:, :nb]).view(np.uint16), want_v.view(np.uint16))
 
 
-def test_config4_topk_sampling_full_size(ops, orc, rng):
+def test_config5_topk_sampling_full_size(ops, orc, rng):
     rows, K = 256, 50
     logits = (rng.standard_normal((rows, VOCAB), dtype=np.float32) * 2.0)
     u = rng.random(rows).astype(np.float32)
@@ -160,7 +172,7 @@ def test_config4_topk_sampling_full_size(ops, orc, rng):
     assert not np.any(differ & (margin > 1e-6))
 
 
-def test_config4_sweep_properties_at_65536_tokens(ops):
+def test_config5_sweep_properties_at_65536_tokens(ops):
     # size-independent properties at the sweep's size, computed on the GPU with plain torch ops
     tokens, batch, seq = 65536, 128, 512
     g = torch.Generator(device="cuda:0")

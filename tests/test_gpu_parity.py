@@ -540,6 +540,34 @@ def test_topk_vocab_sharded_merge_equals_unsharded(ops, orc, rng):
     assert np.array_equal(host(f_i), want_i) and np.array_equal(host(f_v), want_v)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("rows,K,shards", [(32, 50, 8), (7, 5, 3), (3, 1, 2)])
+def test_topk_merge_of_gathered_records_in_place(ops, orc, rng, dtype, rows, K, shards):
+    """The merge reads an all-gather's output where it lies: one packed record per rank
+    ([rows, K] int32 ids | [rows, K] values, padded to 16 bytes), list stride = record size."""
+    vocab = 4000 * shards
+    tdt = torch.float16 if dtype == np.float16 else torch.float32
+    probs = (rng.standard_normal((rows, vocab), dtype=np.float32) * 2).astype(dtype)
+    probs[:, ::97] = probs[:, 5:6]  # ties across shards
+    want_i, want_v = orc.topk(probs, K)
+    per = vocab // shards
+    record = ops.packed_record_bytes(rows, K, tdt)
+    gathered = np.full((shards, record), 0xAB, np.uint8)
+    for s in range(shards):
+        i, v, _ = _topk_run(ops, np.ascontiguousarray(probs[:, s * per:(s + 1) * per]), K, index_offset=s * per)
+        gathered[s, :rows * K * 4] = i.view(np.uint8).reshape(-1)
+        gathered[s, rows * K * 4:rows * K * (4 + v.itemsize)] = v.view(np.uint8).reshape(-1)
+    u = rng.random(rows, dtype=np.float32)
+    f_i = torch.empty((rows, K), dtype=torch.int32, device="cuda:0")
+    f_v = torch.empty((rows, K), dtype=tdt, device="cuda:0")
+    picked = torch.empty(rows, dtype=torch.int32, device="cuda:0")
+    ops.launchTopKMergeGathered(dev(gathered), shards, rows, K, f_i, f_v, dev(u), 0.9, picked)
+    assert np.array_equal(host(f_i), want_i)
+    assert np.array_equal(host(f_v).view(np.uint8), want_v.view(np.uint8))
+    want_pick, margin = orc.sampling(want_i, want_v, u, 0.9)
+    assert np.all(margin[host(picked) != want_pick] < 1e-6)
+
+
 @pytest.mark.parametrize("temperature", [1.0, 0.7, 2.5])
 def test_sampling_fused_and_standalone(ops, orc, rng, temperature):
     rows, vocab, K = 256, 32000, 50
