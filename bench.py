@@ -7,16 +7,24 @@
 A step is one pass of the per-layer fused kernels over one batch of synthetic
 Llama-2-7B-shaped input (fp16 activations, seeded): embedding gather ->
 plain RMSNorm -> QKV bias+RoPE+head transpose -> KV-cache concat -> scale+mask+
-softmax -> residual add+RMSNorm -> SiLU(gate)*up -> top-K(50)+sampling.  Every
-rank owns its own batch (token-axis sharding, no data-path collective), so
-scaling is weak: per-GPU work is fixed as N grows.
+softmax -> residual add+RMSNorm -> SiLU(gate)*up -> top-K(50)+sampling.  The
+batch is the 65,536-token sweep (128 sequences of 512) plus 256 rows of logits;
+with N GPUs it is split along the token axis in whole sequences, 65,536 / N
+tokens and 256 / N logits rows per rank, with no data-path collective, so
+scaling is strong: total work is fixed as N grows.
 
-Rank 0 prints ONE JSON line.  `value` is rows (tokens) per second through the
-chain with inputs resident in HBM; `e2e` is the same chain driven from pinned
-host buffers with the host<->device copies inside the timed region; `kernels`
-gives rows/s and algorithmic GB/s per kernel; `roofline` is the kernel that
-moves the most bytes (SiLU*up); `cpu_baseline` (N=1 only) is the reference's
-CPU code / the oracle port timed on the host cores on a bounded sample.
+Rank 0 prints ONE JSON line.  `value` is rows (tokens) per second of the whole
+job through the chain with inputs resident in HBM (the steps replayed from a
+CUDA graph with programmatic dependent launch; `--no-graph` / `--no-pdl` switch
+either off); `eager` is the same K steps launched one by one with CUDA events
+around every kernel, which gives `kernels` (rows/s and algorithmic GB/s per
+kernel) and `roofline` (SiLU*up, the kernel that moves the most bytes); `e2e`
+is the chain driven from pinned host buffers with the host<->device copies
+inside the timed region; `weak` (N > 1) is the per-GPU-65,536-token figure;
+`vocab_sharded_topk` (N > 1) times the path's one real exchange and checks it
+against the unsharded kernel bit for bit; `configs` (N = 1) times BASELINE's
+configurations 1-4 as stated; `cpu_baseline` (N = 1) is the reference's CPU
+code / the oracle port timed on the host cores on a bounded sample.
 
 --impl reference times that CPU chain alone, on the same metric and unit.
 """
@@ -44,12 +52,19 @@ NOMINAL_HBM_GBS = 8000.0
 FALLBACK_HBM_GBS = 6650.0
 KERNELS = ["input_embedding", "rmsnorm", "qkv_bias_rope_transpose", "concat_kv", "scale_mask_softmax",
            "add_residual_rmsnorm", "silu_mul", "topk_sampling"]
-LAUNCHES_PER_STEP = 8  # one per kernel (at 256 rows top-K runs one slice per row and samples in the same launch)
-# DRAM traffic of the roofline kernel (SiLU*up) from the ncu capture summarised in
-# profiles/silu_mul_16384tok.md: dram__bytes_read.sum + dram__bytes_write.sum of one launch at 16,384
-# tokens (1,037.6 MB) over that launch's algorithmic bytes (1,082.1 MB).  The kernel is a flat
-# streaming pass, so traffic grows in proportion to the rows; a full-size launch is scaled by it.
+TOTAL_TOKENS = 65536
+# DRAM traffic of the roofline kernel (SiLU*up): dram__bytes_read.sum + dram__bytes_write.sum of one
+# launch at 16,384 tokens from an ncu capture (1,037.6 MB) over that launch's algorithmic bytes
+# (1,082.1 MB).  The kernel is a flat streaming pass, so traffic grows in proportion to the rows; a
+# full-size launch is scaled by it.  --traffic overrides it with a fresh capture's figure.
 NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1037.6 / 1082.13
+
+
+def launches_per_step(topk_rows: int) -> int:
+    """Kernels of this library per chain step: one per op, and a second one (the merge) for top-K
+    when the rows are too few to fill the GPU with one CTA each, so that each row is cut in slices
+    (3 CTAs per SM x 148 SMs resident: two or more slices per row up to 222 rows)."""
+    return 8 + (1 if 2 * topk_rows <= 3 * 148 else 0)
 
 
 def algorithmic_bytes(tokens: int, topk_rows: int) -> dict:
@@ -242,12 +257,12 @@ def time_cpu_chain(tokens: int, threads: int, steps: int, warmup: int, budget_s:
 # ---- the GPU chain --------------------------------------------------------------------------------------
 
 class GpuChain:
-    def __init__(self, tokens: int, device, seed: int, topk_buffers: int = 5):
+    def __init__(self, tokens: int, device, seed: int, topk_buffers: int = 5, topk_rows: int = 256):
         import torch
 
         from inferspore_b200 import ops
 
-        self.torch, self.ops, self.dev, self.tokens = torch, ops, device, tokens
+        self.torch, self.ops, self.dev, self.tokens, self.topk_rows = torch, ops, device, tokens, topk_rows
         self.batch = tokens // SEQ
         g = torch.Generator(device=device)
         g.manual_seed(seed)
@@ -278,13 +293,13 @@ class GpuChain:
         self.attn_out = randn(T, HIDDEN)                                   # stands for the o-proj GEMM output
         self.act_in = randn(T, 2, INTER)
         self.act_out = torch.empty((T, INTER), dtype=h, device=device)
-        self.logits = [randn(TOPK_ROWS, VOCAB, dtype=torch.float32, scale=2.0) for _ in range(topk_buffers)]
-        self.u = torch.rand(TOPK_ROWS, generator=g, device=device)
-        self.sc_i = torch.empty((TOPK_ROWS, 8, TOPK_K), dtype=torch.int32, device=device)
-        self.sc_v = torch.empty((TOPK_ROWS, 8, TOPK_K), dtype=torch.float32, device=device)
-        self.top_i = torch.empty((TOPK_ROWS, TOPK_K), dtype=torch.int32, device=device)
-        self.top_v = torch.empty((TOPK_ROWS, TOPK_K), dtype=torch.float32, device=device)
-        self.picked = torch.empty(TOPK_ROWS, dtype=torch.int32, device=device)
+        self.logits = [randn(topk_rows, VOCAB, dtype=torch.float32, scale=2.0) for _ in range(topk_buffers)]
+        self.u = torch.rand(topk_rows, generator=g, device=device)
+        self.sc_i = torch.empty((topk_rows, 8, TOPK_K), dtype=torch.int32, device=device)
+        self.sc_v = torch.empty((topk_rows, 8, TOPK_K), dtype=torch.float32, device=device)
+        self.top_i = torch.empty((topk_rows, TOPK_K), dtype=torch.int32, device=device)
+        self.top_v = torch.empty((topk_rows, TOPK_K), dtype=torch.float32, device=device)
+        self.picked = torch.empty(topk_rows, dtype=torch.int32, device=device)
         self.scale = 1.0 / float(np.sqrt(HEAD_SIZE))
         self.n = 0
 
@@ -319,10 +334,43 @@ class GpuChain:
         if events is not None:
             events[8].record()
 
+    def capture(self, steps: int, pdl: bool):
+        """`steps` chain steps captured into one CUDA graph (top-K walks through its logits buffers as
+        in the eager loop).  With `pdl` the launches carry the programmatic-dependent-launch attribute,
+        so inside the graph one kernel's ramp-up overlaps the tail of the one before."""
+        return capture_graph(self.torch, self.ops, self.dev, lambda: [self.step() for _ in range(steps)], pdl)
 
-NEXT_KERNELS = ["build_causal_mask", "scale_causal_softmax", "scale_mask_softmax_len777", "cal_padding_offset",
-                "transpose_remove_padding",
-                "repeat_kv", "decoder_masked_mha", "decoder_masked_mha_gqa8"]
+
+def capture_graph(torch, ops, device, body, pdl: bool):
+    """Runs `body` under stream capture (every entry point must have run once before) and returns the graph."""
+    ops.set_programmatic_launch(pdl)
+    try:
+        graph, side = torch.cuda.CUDAGraph(), torch.cuda.Stream(device)
+        with torch.cuda.stream(side):
+            with torch.cuda.graph(graph, stream=side):
+                body()
+    finally:
+        ops.set_programmatic_launch(False)
+    torch.cuda.current_stream(device).wait_stream(side)
+    return graph
+
+
+def timed_ms(torch, fn, iters: int) -> float:
+    """Mean milliseconds of `fn` over `iters` back-to-back calls (CUDA events on the current stream)."""
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+NEXT_KERNELS = ["build_causal_mask", "scale_causal_softmax", "scale_mask_softmax_len777", "scale_mask_softmax_len16384",
+                "cal_padding_offset", "transpose_remove_padding", "repeat_kv", "decoder_masked_mha",
+                "decoder_masked_mha_gqa8", "decoder_masked_mha_32q4kv", "decoder_masked_mha_gqa8_step8192",
+                "topk_sampling_4096rows"]
 
 
 class NextRows:
@@ -372,6 +420,29 @@ class NextRows:
             mask = t.tril(t.ones((n, n), dtype=h, device=dev)).expand(bs, n, n).contiguous()
             return ((lambda: o.launchScaleMaskAndSoftmax(qk, mask, out, 1.0 / float(np.sqrt(HEAD_SIZE)))),
                     2 * qk.numel() * 2 + mask.numel() * 2, f"qk [{bs}, {HEADS}, {n}, {n}] f16 + mask [{bs}, {n}, {n}]")
+        if name == "scale_mask_softmax_len16384":
+            # few, very long rows: 8,192 rows of 16,384 (a long-context prefill chunk of 128 queries)
+            bs, q, n = 2, 128, 16384
+            qk = self._randn(bs, HEADS, q, n, scale=3.0)
+            out = t.empty_like(qk)
+            mask = t.ones((bs, q, n), dtype=h, device=dev)
+            mask[:, :, n - 100:] = 0
+            return ((lambda: o.launchScaleMaskAndSoftmax(qk, mask, out, 1.0 / float(np.sqrt(HEAD_SIZE)))),
+                    2 * qk.numel() * 2 + mask.numel() * 2, f"qk [{bs}, {HEADS}, {q}, {n}] f16 + mask [{bs}, {q}, {n}]")
+        if name == "topk_sampling_4096rows":
+            rows = 4096
+            logits = [(t.randn(rows, VOCAB, generator=self.g, device=dev) * 2.0) for _ in range(2)]
+            u = t.rand(rows, generator=self.g, device=dev)
+            sc_i = t.empty((rows, 8, TOPK_K), dtype=t.int32, device=dev)
+            sc_v = t.empty((rows, 8, TOPK_K), device=dev)
+            top_i, top_v = t.empty((rows, TOPK_K), dtype=t.int32, device=dev), t.empty((rows, TOPK_K), device=dev)
+            picked = t.empty(rows, dtype=t.int32, device=dev)
+            state = {"n": 0}
+
+            def launch():
+                o.launchTopKforBeamSearch(logits[state["n"] & 1], sc_i, sc_v, top_i, top_v, 0, u, 1.0, picked)
+                state["n"] += 1
+            return launch, rows * VOCAB * 4 + rows * TOPK_K * 8 + 2 * rows * 4, f"logits [{rows}, {VOCAB}] f32, K = {TOPK_K}, + sampling"
         if name == "cal_padding_offset":
             lens = self._i32([SEQ] * B)
             po = t.empty((B, SEQ), dtype=t.int32, device=dev)
@@ -392,10 +463,13 @@ class NextRows:
             nbytes = 2 * kd.numel() * 2 + 2 * bs * kvh * ctx * HEAD_SIZE * 2
             return ((lambda: o.launchRepeatKVCache(ks, vs, cl, 0, kd, vd)), nbytes,
                     f"{bs} sequences, {kvh} -> {HEADS} heads, context {ctx}, f16")
-        if name in ("decoder_masked_mha", "decoder_masked_mha_gqa8"):
-            # the model's own 32/32 heads, and 64 q heads on 8 kv heads (eight q heads share each cache row)
-            heads, kvh = (HEADS, KV_HEADS) if name == "decoder_masked_mha" else (64, 8)
+        if name.startswith("decoder_masked_mha"):
+            # the model's own 32/32 heads; 64 q heads on 8 kv heads (eight q heads share each cache row), also
+            # at 16 sequences x step 8192; 32 q heads on 4 kv heads
+            heads, kvh = {"decoder_masked_mha": (HEADS, KV_HEADS), "decoder_masked_mha_32q4kv": (32, 4)}.get(name, (64, 8))
             bs, ctx = self.decode_batch, self.context
+            if name == "decoder_masked_mha_gqa8_step8192":
+                bs, ctx = max(1, self.decode_batch // 4), 2 * self.context
             qkv = self._randn(bs, heads + 2 * kvh, HEAD_SIZE)
             kc, vc = self._randn(1, bs, kvh, ctx, HEAD_SIZE), self._randn(1, bs, kvh, ctx, HEAD_SIZE)
             out = t.empty((bs, heads, HEAD_SIZE), dtype=h, device=dev)
@@ -476,6 +550,156 @@ class NextRows:
         return out
 
 
+class StatedConfigs:
+    """BASELINE configurations 1-4 exactly as stated (configuration 5 is the headline workload itself).
+    Kernels whose tensors fit in L2 are timed one launch at a time with a buffer larger than L2
+    written between launches; configuration 1 (a 4 us kernel) instead walks through enough input
+    sets to exceed L2, launched one by one and replayed from a CUDA graph."""
+
+    L2_FLUSH_BYTES = 256 << 20
+
+    def __init__(self, device):
+        import torch
+
+        from inferspore_b200 import ops
+
+        self.torch, self.ops, self.dev = torch, ops, device
+        self.g = torch.Generator(device=device)
+        self.g.manual_seed(99)
+        self.flush = torch.empty(self.L2_FLUSH_BYTES, dtype=torch.uint8, device=device)
+        self.peak, _ = measured_peak_gbs()
+
+    def _flushed_us(self, launch, iters: int = 10) -> float:
+        t = self.torch
+        for _ in range(3):
+            launch()
+        total = 0.0
+        for _ in range(iters):
+            self.flush.zero_()
+            s, e = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            s.record()
+            launch()
+            e.record()
+            e.synchronize()
+            total += s.elapsed_time(e)
+        return total / iters * 1e3
+
+    def _entry(self, us: float, nbytes: int, workload: str, **extra) -> dict:
+        gbs = nbytes / (us * 1e-6) / 1e9
+        return {"us": round(us, 2), "bytes": nbytes, "gbs": round(gbs, 1), "frac_of_peak": round(gbs / self.peak, 4),
+                "frac_of_8TBs": round(gbs / NOMINAL_HBM_GBS, 4), "workload": workload, **extra}
+
+    def config1(self) -> dict:
+        t, o, dev = self.torch, self.ops, self.dev
+        rows, sets = 64, 72  # 72 x (x + residual) of 1 MiB each = 151 MB > L2
+        xs = [t.randn(rows, HIDDEN, generator=self.g, device=dev) for _ in range(sets)]
+        rs = [t.randn(rows, HIDDEN, generator=self.g, device=dev) for _ in range(sets)]
+        gamma = t.rand(HIDDEN, generator=self.g, device=dev) + 0.5
+
+        def sweep():
+            for x, r in zip(xs, rs):
+                o.launchFusedAddBiasResidualRMSNorm(r, x, None, gamma, EPS)
+
+        sweep()
+        eager_us = timed_ms(t, sweep, 5) / sets * 1e3
+        graph = capture_graph(t, o, dev, sweep, True)
+        graph.replay()
+        graph_us = timed_ms(t, graph.replay, 5) / sets * 1e3
+        nbytes = 4 * rows * HIDDEN * 4 + HIDDEN * 4
+        return self._entry(graph_us, nbytes, f"residual add + RMSNorm fp32 [{rows}, {HIDDEN}], {sets} input sets in turn "
+                           "(past L2), per launch, replayed from a CUDA graph", eager_us=round(eager_us, 2))
+
+    def config2(self) -> dict:
+        chain = GpuChain(4096, self.dev, seed=11, topk_buffers=1, topk_rows=16)
+        la = dict(chain.launchers())
+        by = algorithmic_bytes(4096, 16)
+        return {k: self._entry(self._flushed_us(la[k]), by[k], f"fp16, 4096 tokens (8 x 512), L2 flushed between launches")
+                for k in ("input_embedding", "qkv_bias_rope_transpose")}
+
+    def config3(self) -> dict:
+        chain = GpuChain(16384, self.dev, seed=12, topk_buffers=1, topk_rows=64)
+        la = dict(chain.launchers())
+        by = algorithmic_bytes(16384, 64)
+        return {k: self._entry(self._flushed_us(la[k]), by[k], f"fp16, 16384 tokens, L2 flushed between launches")
+                for k in ("add_residual_rmsnorm", "silu_mul")}
+
+    def config4(self) -> dict:
+        t, o, dev, h = self.torch, self.ops, self.dev, self.torch.float16
+        bs, max_seq = 64, 4096
+        per_layer = 2 * bs * KV_HEADS * max_seq * HEAD_SIZE * 2
+        free, _ = t.cuda.mem_get_info(dev)
+        layers = int(max(1, min(32, (free * 3 // 4) // per_layer)))
+        kc = t.empty((layers, bs, KV_HEADS, max_seq, HEAD_SIZE), dtype=h, device=dev)
+        vc = t.empty_like(kc)
+        k = (t.randn(bs, KV_HEADS, 1, HEAD_SIZE, generator=self.g, device=dev)).to(h)
+        v = (t.randn(bs, KV_HEADS, 1, HEAD_SIZE, generator=self.g, device=dev)).to(h)
+        steps = t.randint(1, max_seq, (bs,), generator=self.g, device=dev, dtype=t.int32)
+        cur = t.ones(bs, dtype=t.int32, device=dev)
+
+        def all_layers():
+            for layer in range(layers):
+                o.launchConcatKVCache(k, v, layer, cur, steps, kc, vc)
+
+        all_layers()
+        eager_us = timed_ms(t, all_layers, 5) / layers * 1e3
+        graph = capture_graph(t, o, dev, all_layers, True)
+        graph.replay()
+        graph_us = timed_ms(t, graph.replay, 5) / layers * 1e3
+        concat_bytes = 2 * 2 * bs * KV_HEADS * HEAD_SIZE * 2 + 2 * bs * 4
+        out = {"concat_kv": self._entry(graph_us, concat_bytes, f"k, v [{bs}, {KV_HEADS}, 1, {HEAD_SIZE}] f16 into caches "
+                                        f"[{layers}, {bs}, {KV_HEADS}, {max_seq}, {HEAD_SIZE}] at steps ~U[1, {max_seq}), per layer, "
+                                        f"{layers} layers in turn replayed from a CUDA graph", eager_us=round(eager_us, 2),
+                                        layers=layers)}
+        del kc, vc, graph
+        t.cuda.empty_cache()
+        qk = (t.randn(bs, HEADS, 1, max_seq, generator=self.g, device=dev) * 3.0).to(h)
+        score = t.empty_like(qk)
+        mask = (t.arange(max_seq, device=dev)[None, None, :] < steps[:, None, None]).to(h).contiguous()
+        us = self._flushed_us(lambda: o.launchScaleMaskAndSoftmax(qk, mask, score, 1.0 / float(np.sqrt(HEAD_SIZE))))
+        out["scale_mask_softmax"] = self._entry(us, 2 * qk.numel() * 2 + mask.numel() * 2,
+                                                f"qk [{bs}, {HEADS}, 1, {max_seq}] f16, valid length = step, L2 flushed between launches")
+        return out
+
+    def measure(self) -> dict:
+        out = {}
+        for name in ("config1", "config2", "config3", "config4"):
+            out[name] = getattr(self, name)()
+            self.torch.cuda.empty_cache()
+        return out
+
+
+def small_shard_table(device, use_pdl: bool, tokens: int = 8192, topk_rows: int = 32, steps: int = 20) -> dict:
+    """The chain at the per-GPU size of the 8-way split, on this one GPU: per-kernel times launched
+    one by one, and the step time replayed from a CUDA graph with and without programmatic
+    dependent launch.  What limits the 1 -> 8 curve is here, not in any collective."""
+    import torch
+
+    chain = GpuChain(tokens, device, seed=5000, topk_rows=topk_rows)
+    peak, _ = measured_peak_gbs()
+    for _ in range(3):
+        chain.step()
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(9)] for _ in range(steps)]
+    torch.cuda.synchronize()
+    for i in range(steps):
+        chain.step(ev[i])
+    torch.cuda.synchronize()
+    eager_ms = ev[0][0].elapsed_time(ev[-1][8]) / steps
+    by = algorithmic_bytes(tokens, topk_rows)
+    kernels = {}
+    for j, name in enumerate(KERNELS):
+        ms = sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(steps)) / steps
+        gbs = by[name] / (ms * 1e-3) / 1e9
+        kernels[name] = {"us": round(ms * 1e3, 2), "gbs": round(gbs, 1), "frac_of_peak": round(gbs / peak, 4)}
+    out = {"tokens": tokens, "topk_rows": topk_rows, "eager_us_per_step": round(eager_ms * 1e3, 1), "kernels": kernels,
+           "ideal_us_at_peak": round(sum(by.values()) / peak / 1e3, 1)}
+    for key, pdl in (("graph_us_per_step", False), ("graph_pdl_us_per_step", True)):
+        graph = chain.capture(steps, pdl)
+        graph.replay()
+        out[key] = round(timed_ms(torch, graph.replay, 3) / steps * 1e3, 1)
+        del graph
+    return out
+
+
 class HostDrivenChain:
     """The same chain for a caller whose data lives in host memory: every step copies the step's
     inputs from pinned host buffers to the GPU, runs the kernels and copies every output back.
@@ -538,9 +762,33 @@ class HostDrivenChain:
             cur.wait_stream(st)
 
 
+def host_memory_available() -> int:
+    """Bytes of host memory this process may still take (the smaller of the machine's and the
+    cgroup's head-room)."""
+    avail = 1 << 62
+    try:
+        import psutil
+
+        avail = psutil.virtual_memory().available
+    except Exception:
+        pass
+    for limit, used in (("/sys/fs/cgroup/memory.max", "/sys/fs/cgroup/memory.current"),
+                        ("/sys/fs/cgroup/memory/memory.limit_in_bytes", "/sys/fs/cgroup/memory/memory.usage_in_bytes")):
+        try:
+            lim = Path(limit).read_text().strip()
+            if lim != "max":
+                avail = min(avail, int(lim) - int(Path(used).read_text().strip()))
+        except Exception:
+            pass
+    return avail
+
+
 def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
+
+    from inferspore_b200 import capi, ops
+    from inferspore_b200.sharding import shard_range, shard_sequences
 
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -561,29 +809,103 @@ def run_ours(args) -> dict:
             dist.barrier()
         torch.cuda.synchronize()
 
-    tokens = args.tokens
-    chain = GpuChain(tokens, device, seed=1000 + rank)
-    for _ in range(max(3, args.warmup)):
+    def max_over_ranks(ms: float) -> float:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # This rank's share of the job: whole sequences of the 65,536-token batch, and rows of the logits.
+    if args.tokens is not None:  # per-GPU override (small cases for development and profiling)
+        tokens, total_tokens = args.tokens, args.tokens * world
+        topk_rows = args.topk_rows if args.topk_rows is not None else max(1, TOPK_ROWS * tokens // TOTAL_TOKENS)
+        total_topk_rows = topk_rows * world
+    else:
+        total_tokens, total_topk_rows = TOTAL_TOKENS, TOPK_ROWS
+        _, tok = shard_sequences(total_tokens // SEQ, SEQ, world, rank)
+        tokens, topk_rows = tok.size, shard_range(total_topk_rows, world, rank).size
+    use_graph, use_pdl = not args.no_graph, not args.no_pdl
+    K, W = args.steps, max(3, args.warmup)
+
+    chain = GpuChain(tokens, device, seed=1000 + rank, topk_rows=topk_rows)
+    for _ in range(W):
         chain.step()
     barrier()
 
-    K = args.steps
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(9)] for _ in range(K)]
+    # Timed region 1 (`value`): exactly K steps, one graph launch (or K eager steps with --no-graph).
+    graph = None
+    if use_graph:
+        try:
+            graph = chain.capture(K, use_pdl)
+            graph.replay()  # one more warm-up pass, through the graph
+        except Exception as exc:  # capture refused: fall back to plain launches and say so
+            print(f"bench: graph capture failed ({exc}); timing plain launches", file=sys.stderr)
+            graph = None
+    if graph is None and use_pdl:
+        ops.set_programmatic_launch(True)
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(local_rank) as clocks:
         barrier()
-        for i in range(K):
-            chain.step(ev[i])
+        s.record()
+        if graph is not None:
+            graph.replay()
+        else:
+            for _ in range(K):
+                chain.step()
+        e.record()
         barrier()
-    total_ms = ev[0][0].elapsed_time(ev[-1][8])
-    per_kernel_ms = [sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) / K for j in range(8)]
-    t = torch.tensor([total_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    ms_per_step = total_ms / K
+    ops.set_programmatic_launch(False)
+    ms_per_step = max_over_ranks(s.elapsed_time(e)) / K
+    launch_mode = ("graph" if graph is not None else "eager") + ("+pdl" if use_pdl else "")
 
-    # end to end from host buffers, smaller batch (rows/s is size-normalised)
-    e2e_chains = [GpuChain(args.e2e_tokens, device, seed=2000 + 10 * rank + i, topk_buffers=1) for i in range(2)]
+    # Timed region 2 (`eager`, `kernels`, `roofline`): the same K steps launched one by one, CUDA events
+    # around every kernel.
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(9)] for _ in range(K)]
+    barrier()
+    for i in range(K):
+        chain.step(ev[i])
+    barrier()
+    eager_ms_per_step = max_over_ranks(ev[0][0].elapsed_time(ev[-1][8])) / K
+    per_kernel_ms = [sum(ev[i][j].elapsed_time(ev[i][j + 1]) for i in range(K)) / K for j in range(8)]
+    del graph
+
+    # Weak scaling beside the strong figure: every rank runs the whole 65,536-token batch.
+    weak = None
+    if world > 1 and args.tokens is None and not args.no_weak:
+        wchain = GpuChain(TOTAL_TOKENS, device, seed=3000 + rank, topk_rows=TOPK_ROWS)
+        wk = max(3, min(K, 10))
+        for _ in range(3):
+            wchain.step()
+        wgraph = wchain.capture(wk, use_pdl) if use_graph else None
+        if wgraph is not None:
+            wgraph.replay()
+        barrier()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        if wgraph is not None:
+            wgraph.replay()
+        else:
+            for _ in range(wk):
+                wchain.step()
+        e.record()
+        barrier()
+        wms = max_over_ranks(s.elapsed_time(e)) / wk
+        weak = {"value": round(world * TOTAL_TOKENS / (wms * 1e-3), 1), "unit": "rows/s", "ms_per_step": round(wms, 4),
+                "tokens_per_gpu": TOTAL_TOKENS, "topk_rows_per_gpu": TOPK_ROWS, "steps": wk, "scaling": "weak"}
+        del wchain, wgraph
+        torch.cuda.empty_cache()
+
+    # End to end from host buffers: this rank's share of the same batch, unless the host cannot pin
+    # that much (two buffer sets of inputs and outputs); rows/s is size-normalised either way.
+    e2e_tokens = args.e2e_tokens if args.e2e_tokens is not None else tokens
+    per_token_pinned = 2 * (930 + 852) * (1 << 20) // 8192  # both directions, two buffer sets
+    budget = host_memory_available() // (3 * max(1, world if args.e2e_tokens is None else 1))
+    while e2e_tokens > SEQ and e2e_tokens * per_token_pinned > budget:
+        e2e_tokens = max(SEQ, (e2e_tokens // 2) // SEQ * SEQ)
+    e2e_topk = max(1, topk_rows * e2e_tokens // tokens)
+    del chain
+    torch.cuda.empty_cache()
+    e2e_chains = [GpuChain(e2e_tokens, device, seed=2000 + 10 * rank + i, topk_buffers=1, topk_rows=e2e_topk) for i in range(2)]
     hd = HostDrivenChain(e2e_chains)
     e2e_steps = max(3, min(K, args.e2e_steps))
     hd.begin()
@@ -599,49 +921,26 @@ def run_ours(args) -> dict:
     hd.end()
     e.record()
     barrier()
-    t2 = torch.tensor([s.elapsed_time(e)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t2, op=dist.ReduceOp.MAX)
-    e2e_ms_per_step = float(t2.item()) / e2e_steps
+    e2e_ms_per_step = max_over_ranks(s.elapsed_time(e)) / e2e_steps
+    e2e = {"value": round(world * e2e_tokens / (e2e_ms_per_step * 1e-3), 1), "unit": "rows/s",
+           "h2d_bytes_per_step": hd.h2d, "d2h_bytes_per_step": hd.d2h, "rows_per_step": e2e_tokens,
+           "rows_per_step_all_gpus": world * e2e_tokens, "steps": e2e_steps, "ms_per_step": round(e2e_ms_per_step, 3)}
+    del e2e_chains, hd
+    torch.cuda.empty_cache()
 
-    # The path's one real exchange, timed on its own when there are ranks to exchange with: top-K
-    # over logits whose vocabulary axis is split across the ranks (local top-K with global ids, one
-    # NCCL all-gather of the candidate lists, merge + sampling on every rank).
-    sharded_topk = None
-    if world > 1:
-        from inferspore_b200.sharding import vocab_shard, vocab_sharded_topk
-
-        shard = vocab_shard(VOCAB, world, rank)
-        g = torch.Generator(device=device)
-        g.manual_seed(4000)  # the same logits on every rank; each keeps its own columns
-        full = torch.randn(TOPK_ROWS, VOCAB, generator=g, device=device) * 2.0
-        local = full[:, shard.start:shard.stop].contiguous()
-        uni = torch.rand(TOPK_ROWS, generator=g, device=device)
-        for _ in range(3):
-            vocab_sharded_topk(local, shard, TOPK_K, uniform=uni)
-        barrier()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        for _ in range(20):
-            vocab_sharded_topk(local, shard, TOPK_K, uniform=uni)
-        e.record()
-        barrier()
-        t3 = torch.tensor([s.elapsed_time(e) / 20], dtype=torch.float64, device=device)
-        dist.all_reduce(t3, op=dist.ReduceOp.MAX)
-        sharded_topk = {"ms": round(float(t3.item()), 4), "rows": TOPK_ROWS, "vocab_per_rank": shard.size,
-                        "gathered_bytes_per_rank": TOPK_ROWS * TOPK_K * 8 * world}
-
-    from inferspore_b200 import capi
+    sharded_topk = vocab_sharded_leg(torch, dist, ops, device, rank, world, barrier, max_over_ranks) if world > 1 else None
 
     status = capi.device_status(clear=True)
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
+        if sharded_topk is not None and not sharded_topk["matches_unsharded"]:
+            raise SystemExit(3)
         return {}
 
     peak, peak_kind = measured_peak_gbs()
-    bytes_per = algorithmic_bytes(tokens, TOPK_ROWS)
-    rows_per = {k: (TOPK_ROWS if k == "topk_sampling" else tokens) for k in KERNELS}
+    bytes_per = algorithmic_bytes(tokens, topk_rows)
+    rows_per = {k: (topk_rows if k == "topk_sampling" else tokens) for k in KERNELS}
     kernels = {}
     for name, ms in zip(KERNELS, per_kernel_ms):
         gbs = bytes_per[name] / (ms * 1e-3) / 1e9
@@ -649,48 +948,132 @@ def run_ours(args) -> dict:
                          "gbs": round(gbs, 1), "frac_of_8TBs": round(gbs / NOMINAL_HBM_GBS, 4),
                          "frac_of_peak": round(gbs / peak, 4), "bytes": bytes_per[name]}
     dom = "silu_mul"
+    total_bytes = sum(algorithmic_bytes(total_tokens, total_topk_rows).values())
     out = {
         "metric": "rows/s through the fused layer-kernel chain (per-kernel GB/s in `kernels`)",
-        "value": round(world * tokens / (ms_per_step * 1e-3), 1),
+        "value": round(total_tokens / (ms_per_step * 1e-3), 1),
         "unit": "rows/s",
         "n_gpus": world,
         "steps": K,
-        "warmup": max(3, args.warmup),
+        "warmup": W,
         "ms_per_step": round(ms_per_step, 4),
         "higher_is_better": True,
-        "scaling": "weak",
+        "scaling": "strong",
         "vs_baseline": None,
         "dtype": "f16",
         "data": "synthetic",
-        "config": {"workload": f"Llama-2-7B prefill layer-kernel chain, {tokens} tokens ({tokens // SEQ} x {SEQ}) per GPU "
-                               f"+ top-K(50)+sampling over [{TOPK_ROWS}, {VOCAB}] fp32 logits",
-                   "tokens_per_gpu": tokens, "l2": "inputs larger than L2 (top-K rotates 5 logits buffers)",
-                   "sharding": f"token axis, {world} shard(s), no collective"},
-        "gbs": round(world * sum(bytes_per.values()) / (ms_per_step * 1e-3) / 1e9, 1),
+        "config": {"workload": f"Llama-2-7B prefill layer-kernel chain over {total_tokens} tokens ({total_tokens // SEQ} x {SEQ}) "
+                               f"+ top-K(50)+sampling over [{total_topk_rows}, {VOCAB}] fp32 logits, split over {world} GPU(s)",
+                   "tokens_per_gpu": tokens, "topk_rows_per_gpu": topk_rows,
+                   "l2": "inputs larger than L2 (2.4 GB of tensors per step even at 8,192 tokens per GPU; top-K rotates 5 "
+                         "logits buffers)",
+                   "sharding": f"token axis, whole sequences, {world} shard(s), no collective",
+                   "launch": launch_mode},
+        "gbs": round(total_bytes / (ms_per_step * 1e-3) / 1e9, 1),
+        "eager": {"ms_per_step": round(eager_ms_per_step, 4), "value": round(total_tokens / (eager_ms_per_step * 1e-3), 1),
+                  "note": "the same K steps launched one by one with CUDA events around every kernel; source of `kernels` "
+                          "and `roofline`"},
         "kernels": kernels,
         "roofline": {"bound": "hbm", "kernel": dom, "achieved": kernels[dom]["gbs"], "peak": peak, "unit": "GB/s",
                      "frac": round(kernels[dom]["gbs"] / peak, 4), "peak_kind": f"{peak_kind} copy bandwidth",
                      "traffic": args.traffic if args.traffic is not None
                      else round(NCU_TRAFFIC_PER_ALGORITHMIC_BYTE * bytes_per[dom])},
         "clocks": clocks.summary(),
-        "e2e": {"value": round(world * args.e2e_tokens / (e2e_ms_per_step * 1e-3), 1), "unit": "rows/s",
-                "h2d_bytes_per_step": hd.h2d, "d2h_bytes_per_step": hd.d2h, "rows_per_step": args.e2e_tokens,
-                "steps": e2e_steps, "ms_per_step": round(e2e_ms_per_step, 3)},
-        "gpu_launches": K * LAUNCHES_PER_STEP,
+        "e2e": e2e,
+        "gpu_launches": K * launches_per_step(topk_rows),
         "device_status": status,
     }
+    if weak is not None:
+        out["weak"] = weak
     if sharded_topk is not None:
         out["vocab_sharded_topk"] = sharded_topk
     if world == 1 and not args.no_next_rows:
-        del chain, e2e_chains, hd
         torch.cuda.empty_cache()
-        out["next_rows"] = NextRows(tokens, device).measure()
+        out["next_rows"] = NextRows(total_tokens, device).measure()
+        out["configs"] = StatedConfigs(device).measure()
+        out["small_shard"] = small_shard_table(device, use_pdl)
     if world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
         rps, dt, cpu = time_cpu_chain(args.cpu_tokens, threads, steps=3, warmup=1, budget_s=40.0)
         out["cpu_baseline"] = {"value": round(rps, 1), "unit": "rows/s", "cores": threads, "kind": cpu.kind,
                                "sample": cpu.describe(), "s_per_step": round(dt, 3)}
+    if sharded_topk is not None and not sharded_topk["matches_unsharded"]:
+        print(json.dumps(out), file=sys.stderr)
+        raise SystemExit(3)
     return out
+
+
+def vocab_sharded_leg(torch, dist, ops, device, rank, world, barrier, max_over_ranks) -> dict:
+    """The path's one real exchange, timed on its own and checked: top-K over logits whose vocabulary
+    axis is split across the ranks (local top-K with global ids, one NCCL all-gather of the packed
+    candidate records, merge + sampling on every rank, reading the gathered records in place).
+    Outside the timed loops the unsharded kernel runs on the full logits and its ids, values and
+    sampled ids must equal the sharded result bit for bit on every rank."""
+    from inferspore_b200.sharding import VocabShardedTopK, vocab_shard
+
+    shard = vocab_shard(VOCAB, world, rank)
+    g = torch.Generator(device=device)
+    g.manual_seed(4000)  # the same logits on every rank; each keeps its own columns
+    full = torch.randn(TOPK_ROWS, VOCAB, generator=g, device=device) * 2.0
+    full[:, ::97] = full[:, 5:6]  # equal values in different shards: the tie rule has to hold across ranks
+    local = full[:, shard.start:shard.stop].contiguous()
+    uni = torch.rand(TOPK_ROWS, generator=g, device=device)
+    op = VocabShardedTopK(TOPK_ROWS, TOPK_K, torch.float32, device)
+    iters = 20
+
+    def whole():
+        return op(local, shard, uni, 1.0)
+
+    for _ in range(3):
+        whole()
+    barrier()
+    total = max_over_ranks(timed_ms(torch, whole, iters))
+    barrier()
+    local_ms = max_over_ranks(timed_ms(torch, lambda: op.local(local, shard), iters))
+    barrier()
+    gather_ms = max_over_ranks(timed_ms(torch, op.exchange, iters))
+    barrier()
+    merge_ms = max_over_ranks(timed_ms(torch, lambda: op.merge(uni, 1.0), iters))
+    barrier()
+
+    # parity, outside the timed loops
+    ids, vals, picked = whole()
+    sc_i = torch.empty((TOPK_ROWS, 8, TOPK_K), dtype=torch.int32, device=device)
+    sc_v = torch.empty((TOPK_ROWS, 8, TOPK_K), device=device)
+    f_i = torch.empty((TOPK_ROWS, TOPK_K), dtype=torch.int32, device=device)
+    f_v = torch.empty((TOPK_ROWS, TOPK_K), device=device)
+    f_p = torch.empty(TOPK_ROWS, dtype=torch.int32, device=device)
+    ops.launchTopKforBeamSearch(full, sc_i, sc_v, f_i, f_v, 0, uni, 1.0, f_p)
+    torch.cuda.synchronize()
+    same = bool(torch.equal(ids, f_i) and torch.equal(vals.view(torch.int32), f_v.view(torch.int32)) and torch.equal(picked, f_p))
+    flag = torch.tensor([1 if same else 0], dtype=torch.int32, device=device)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+
+    # Last, the three steps replayed from one CUDA graph (NCCL collectives can be captured).  Every
+    # rank replays only if every rank captured, so that no rank waits in the all-gather for one
+    # that has nothing to replay.
+    graph, graph_ms = None, None
+    try:
+        graph = capture_graph(torch, ops, device, whole, True)
+    except Exception as exc:
+        print(f"bench: capture of the sharded top-K failed on rank {rank} ({exc})", file=sys.stderr)
+    captured = torch.tensor([0 if graph is None else 1], dtype=torch.int32, device=device)
+    dist.all_reduce(captured, op=dist.ReduceOp.MIN)
+    if captured.item() == 1:
+        graph.replay()
+        barrier()
+        graph_ms = max_over_ranks(timed_ms(torch, graph.replay, iters))
+        barrier()
+        g_same = bool(torch.equal(op.out_i, f_i) and torch.equal(op.picked, f_p))
+        flag2 = torch.tensor([1 if g_same else 0], dtype=torch.int32, device=device)
+        dist.all_reduce(flag2, op=dist.ReduceOp.MIN)
+        flag = torch.minimum(flag, flag2)
+    del graph
+    return {"ms": round(total, 4), "local_topk_us": round(local_ms * 1e3, 2), "allgather_us": round(gather_ms * 1e3, 2),
+            "merge_us": round(merge_ms * 1e3, 2), "graph_us": None if graph_ms is None else round(graph_ms * 1e3, 2),
+            "rows": TOPK_ROWS, "vocab_per_rank": shard.size, "record_bytes_per_rank": op.record_bytes,
+            "gathered_bytes_per_rank": op.record_bytes * world, "matches_unsharded": bool(flag.item() == 1),
+            "checked": "ids, value bits and sampled ids of every rank against launchTopKforBeamSearch on the full logits"}
 
 
 def run_only(args) -> dict:
@@ -737,7 +1120,7 @@ def run_reference(args) -> dict:
         "metric": "rows/s through the fused layer-kernel chain (per-kernel GB/s in `kernels`)",
         "value": round(rps, 1), "unit": "rows/s", "n_gpus": int(os.environ.get("WORLD_SIZE", "1")),
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "Llama-2-7B prefill layer-kernel chain on the host cores, bounded sample: " + cpu.describe()},
         "cpu_baseline": {"value": round(rps, 1), "unit": "rows/s", "cores": threads, "kind": cpu.kind,
                          "sample": cpu.describe()},
@@ -751,8 +1134,15 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
-    ap.add_argument("--tokens", type=int, default=65536, help="tokens per GPU per step (multiple of 512)")
-    ap.add_argument("--e2e-tokens", type=int, default=8192, help="tokens per step of the host-driven leg")
+    ap.add_argument("--tokens", type=int, default=None,
+                    help="tokens per GPU per step (multiple of 512); default: 65536 split over the GPUs")
+    ap.add_argument("--topk-rows", type=int, default=None, help="logits rows per GPU (default: 256 split over the GPUs)")
+    ap.add_argument("--e2e-tokens", type=int, default=None,
+                    help="tokens per GPU per step of the host-driven leg (default: this GPU's share of the batch, "
+                         "halved until two pinned buffer sets fit the host)")
+    ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")
+    ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch in the timed steps")
+    ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the extra 65,536-tokens-per-GPU (weak scaling) leg")
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-tokens", type=int, default=4096, help="tokens per step of the CPU chain sample")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -763,8 +1153,11 @@ def main() -> int:
     ap.add_argument("--traffic", type=float, default=None,
                     help="override: DRAM bytes per launch of the roofline kernel from a fresh ncu capture")
     args = ap.parse_args()
-    if args.tokens % SEQ or args.e2e_tokens % SEQ or args.tokens <= 0:
-        ap.error("--tokens and --e2e-tokens must be positive multiples of 512")
+    for v in (args.tokens, args.e2e_tokens):
+        if v is not None and (v % SEQ or v <= 0):
+            ap.error("--tokens and --e2e-tokens must be positive multiples of 512")
+    if args.only and args.tokens is None:
+        args.tokens = 16384
     # stdout carries exactly one JSON line: anything a library prints there during the run (NCCL's
     # version banner, for one) is sent to stderr instead, and the line is written to the real stdout.
     sys.stdout.flush()

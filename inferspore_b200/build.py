@@ -7,6 +7,14 @@ newer than the source and every header), then linked into
 inferspore_b200/lib/libispore_kernels.so.  nvcc cross-compiles without a GPU.
 `-Xptxas -v` output (registers, spills, shared memory per kernel) is kept next
 to the objects as <name>.ptxas.txt.
+
+The same objects also go into one static archive per kernel under
+inferspore_b200/lib/static/, named after the reference's per-kernel CMake
+targets (src/kernels/CMakeLists.txt:1-69 of m0dulo/InferSpore: embeddingFunctor,
+qkv_bias_and_rope, concat_kv, mask_softmax, fused_addresidual_norm, act, topk,
+...), so that a build of the reference that links `-lact` or `-ltopk` keeps its
+link lines: each archive holds the objects its launcher needs plus the
+library-level object (error text, stream, status word).
 """
 from __future__ import annotations
 
@@ -25,6 +33,24 @@ INCLUDE = ROOT / "include"
 OBJ_DIR = ROOT / "build" / "ispore_obj"
 LIB_DIR = PKG / "lib"
 LIB_PATH = LIB_DIR / "libispore_kernels.so"
+STATIC_DIR = LIB_DIR / "static"
+
+# reference CMake target (src/kernels/CMakeLists.txt) -> our objects that implement its launcher
+ARCHIVES = {
+    "embeddingFunctor": ["embedding"],
+    "cal_paddingoffset": ["layout_ops"],
+    "build_casual_mask": ["layout_ops"],
+    "qkv_bias_and_rope": ["qkv_rope"],
+    "concat_kv": ["concat_kv"],
+    "repeat_kv": ["layout_ops"],
+    "mask_softmax": ["softmax"],
+    "fused_transpose_and_remv_pad": ["layout_ops"],
+    "fused_addresidual_norm": ["rmsnorm"],
+    "act": ["act"],
+    "topk": ["topk"],
+    "fused_decoder_self_attention": ["decoder_mha"],
+}
+COMMON_OBJECTS = ["c_api"]  # error text, thread-local stream, device status word, occupancy cache
 
 NVCC_FLAGS = [
     "-std=c++17",
@@ -92,7 +118,27 @@ def build_library(force: bool = False, verbose: bool = False) -> Path:
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
+    build_archives(force=force or bool(todo))
     return LIB_PATH
+
+
+def build_archives(force: bool = False) -> list[Path]:
+    """One static archive per reference CMake target from the objects already compiled."""
+    STATIC_DIR.mkdir(parents=True, exist_ok=True)
+    out = []
+    for target, stems in ARCHIVES.items():
+        path = STATIC_DIR / f"lib{target}.a"
+        objs = [OBJ_DIR / f"{stem}.o" for stem in stems + COMMON_OBJECTS]
+        missing = [o for o in objs if not o.exists()]
+        if missing:
+            raise RuntimeError(f"archive {target}: objects missing: {missing}")
+        if force or _stale(path, objs):
+            path.unlink(missing_ok=True)
+            proc = subprocess.run(["ar", "rcs", str(path), *map(str, objs)], capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise RuntimeError(f"ar failed for {target}:\n{proc.stderr}")
+        out.append(path)
+    return out
 
 
 def main(argv: list[str] | None = None) -> int:

@@ -1,8 +1,16 @@
 // Drop-in for the reference's src/kernels/fused_decoder_self_attention.h: same launcher name and
-// arguments (:10-18), forwarding to the C ABI of libispore_kernels.  The reference launcher takes
-// no scratch; this one keeps a per-thread device buffer that grows on demand so that long
-// sequences at small batch can be split over several CTAs.  Build with
-// -DISPORE_MHA_NO_WORKSPACE to forbid that allocation (one CTA per sequence and head group then).
+// arguments (:10-18), forwarding to the C ABI of libispore_kernels.
+//
+// Scratch.  The reference launcher takes no scratch argument; the kernel here can use one to split
+// long sequences at small batch over several CTAs (without it: one CTA per sequence and head
+// group — still correct, slower below ~64 sequences).  By default this header allocates NOTHING:
+// the host hands a device buffer over once per thread and device,
+//     ispore_compat::set_mha_workspace(ptr, bytes);   // with that device current
+// sized with ispore_decoder_masked_mha_workspace_bytes() for its largest batch and step, and keeps
+// ownership of it.  A host that prefers the header to manage the buffer builds with
+// -DISPORE_MHA_ALLOC_WORKSPACE: then one buffer per (thread, device) is allocated on first use,
+// grown when a call needs more (cudaFree + cudaMalloc: both synchronise the device, so size the
+// first call generously) and freed when the thread exits.
 #pragma once
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -15,26 +23,70 @@
 #include "src/weights/base_weights.h"
 
 namespace ispore_compat {
-inline void* mha_workspace(int64_t bytes) {
-#ifdef ISPORE_MHA_NO_WORKSPACE
-    (void)bytes;
-    return nullptr;
-#else
-    thread_local void* buf = nullptr;
-    thread_local int64_t cap = 0;
-    if (bytes > cap) {
-        if (buf) cudaFree(buf);
-        buf = nullptr;
-        cap = 0;
-        if (cudaMalloc(&buf, static_cast<size_t>(bytes)) != cudaSuccess) {
+
+constexpr int kMhaMaxDevices = 64;
+
+// One slot per device for the calling thread: a buffer belongs to the device it was allocated
+// on and is never offered to a kernel running on another one.
+struct MhaWorkspaceSlots {
+    void* buf[kMhaMaxDevices] = {};
+    int64_t cap[kMhaMaxDevices] = {};
+    bool owned[kMhaMaxDevices] = {};
+    ~MhaWorkspaceSlots() {
+        for (int d = 0; d < kMhaMaxDevices; ++d) {
+            if (!owned[d] || buf[d] == nullptr) continue;
+            int prev = 0;
+            if (cudaGetDevice(&prev) != cudaSuccess) break;  // the runtime is already shutting down
+            if (cudaSetDevice(d) == cudaSuccess) cudaFree(buf[d]);
+            cudaSetDevice(prev);
             cudaGetLastError();
-            buf = nullptr;
-            return nullptr;  // the launcher then runs unsplit
         }
-        cap = bytes;
     }
-    return buf;
+};
+inline MhaWorkspaceSlots& mha_slots() {
+    thread_local MhaWorkspaceSlots slots;
+    return slots;
+}
+inline int mha_current_device() {
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMhaMaxDevices) return -1;
+    return dev;
+}
+
+// Hands the calling thread's decode-attention scratch for the CURRENT device to the launcher
+// (ptr == nullptr or bytes == 0 withdraws it).  The buffer stays the caller's.
+inline void set_mha_workspace(void* ptr, int64_t bytes) {
+    const int dev = mha_current_device();
+    if (dev < 0) return;
+    MhaWorkspaceSlots& s = mha_slots();
+    if (s.owned[dev] && s.buf[dev] != nullptr) cudaFree(s.buf[dev]);
+    s.buf[dev] = bytes > 0 ? ptr : nullptr;
+    s.cap[dev] = ptr != nullptr && bytes > 0 ? bytes : 0;
+    s.owned[dev] = false;
+}
+
+// The scratch the next call on the current device may use for `bytes`; nullptr = run unsplit.
+inline void* mha_workspace(int64_t bytes) {
+    const int dev = mha_current_device();
+    if (dev < 0) return nullptr;
+    MhaWorkspaceSlots& s = mha_slots();
+    if (bytes <= s.cap[dev]) return s.buf[dev];
+#ifdef ISPORE_MHA_ALLOC_WORKSPACE
+    if (s.buf[dev] == nullptr || s.owned[dev]) {  // a buffer the caller handed over is never replaced
+        if (s.buf[dev] != nullptr) cudaFree(s.buf[dev]);
+        s.buf[dev] = nullptr;
+        s.cap[dev] = 0;
+        s.owned[dev] = true;
+        if (cudaMalloc(&s.buf[dev], static_cast<size_t>(bytes)) != cudaSuccess) {
+            cudaGetLastError();
+            s.buf[dev] = nullptr;
+            return nullptr;
+        }
+        s.cap[dev] = bytes;
+        return s.buf[dev];
+    }
 #endif
+    return nullptr;  // too small for a split plan of this size: the launcher runs unsplit
 }
 }  // namespace ispore_compat
 

@@ -113,8 +113,8 @@ int concat_dispatch(T* k_dst, T* v_dst, const T* k_src, const T* v_src, const in
                     "concat_kv: bad shape layer=%lld/%lld bs=%lld heads=%lld q=%lld seq=%lld d=%lld",
                     (long long)layer, (long long)num_layers, (long long)batch, (long long)kv_heads,
                     (long long)max_q_len, (long long)max_seq_len, (long long)head_size);
-    if (batch * kv_heads > 65535)
-        return fail(ISPORE_ELIMIT, "concat_kv: batch*kv_heads %lld > 65535", (long long)(batch * kv_heads));
+    if (batch * kv_heads > INT32_MAX)
+        return fail(ISPORE_ELIMIT, "concat_kv: batch*kv_heads %lld too large", (long long)(batch * kv_heads));
     if (batch == 0 || max_q_len == 0) return ISPORE_OK;
     if (!k_dst || !v_dst || !k_src || !v_src || !cur_len || !hist_len)
         return fail(ISPORE_ENULL, "concat_kv: NULL buffer");
@@ -151,6 +151,11 @@ int concat_dispatch(T* k_dst, T* v_dst, const T* k_src, const T* v_src, const in
             return check_launch("concat_kv_tma_kernel");
         }
     }
+    // The scalar kernel puts (b, h) on gridDim.y, which the hardware caps at 65535 (the TMA path's
+    // grid is flat and has no such limit).
+    if (batch * kv_heads > 65535)
+        return fail(ISPORE_ELIMIT, "concat_kv: batch*kv_heads %lld > 65535 on the unaligned path",
+                    (long long)(batch * kv_heads));
     int64_t gx = ceil_div(max_q_len * head_size, 256);
     if (gx > 64) gx = 64;
     dim3 grid(static_cast<unsigned>(gx), static_cast<unsigned>(batch * kv_heads), 2);

@@ -9,19 +9,22 @@
 // (value descending, index ascending), -0.0 == +0.0.
 //
 // Round 1 (one CTA per row slice) streams its slice from HBM once, a tile of
-// 8192 elements at a time, straight into registers (32 raw bit patterns per
-// thread, all loads of a tile in flight together).  A threshold that is
-// guaranteed to keep at least K elements of the tile comes from one
-// representative per thread with warp-level max-reductions only; while the
-// threshold is a positive value the per-element test is a single integer compare
-// on the raw bits.  The few survivors are compacted into shared memory and
-// ranked by counting against each other, which yields the running top-K already
-// sorted without a sorting network.  Later tiles
-// additionally have to beat the current K-th best.  Adversarial tiles (e.g.
-// constant data, where the threshold keeps everything) fall back to an exact
-// radix select over the keys in registers, ties resolved by an index-ordered
-// block scan.  Round 2 (one CTA per row) merges the slices' sorted lists by
-// binary search and can draw the sampled token in its epilogue.
+// 8192 elements at a time (TMA bulk copies into a two-stage shared-memory ring,
+// the next tile requested before the current one is touched), into registers
+// as raw bit patterns, 32 per thread.  First tile: a threshold that is
+// guaranteed to keep at least K elements comes from one representative per
+// thread with warp-level max-reductions only; the few survivors are compacted
+// into shared memory and ranked by counting against each other, which yields
+// the running top-K already sorted without a sorting network.  Every later tile
+// only has to beat the running K-th best: while that is a positive value the
+// test is one integer compare of the thread's maximum (nearly every thread of
+// every later tile holds no survivor and is done after it), survivors are
+// parked behind the running best, and the ranking runs once every few tiles
+// rather than once per tile — a later tile costs one block barrier.
+// Adversarial tiles (e.g. constant data, where the threshold keeps everything)
+// fall back to an exact radix select over the tile, ties resolved by an
+// index-ordered block scan.  Round 2 (one CTA per row) merges the slices' sorted
+// lists by binary search and can draw the sampled token in its epilogue.
 #include <float.h>
 #include <limits.h>
 #include <math.h>
@@ -249,38 +252,52 @@ __device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int
     }
 }
 
-// exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.
-// One warp: lanes evaluate the exponentials, lane 0 accumulates sequentially.
+// exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.  One warp.  The sums
+// are the sequential fp32 sums of the definition (p_0 + p_1 + ... in index order): every lane
+// carries the same running sum, fed one term at a time by a shuffle from the lane that holds
+// the term, so there is no dependent chain of shared-memory loads; lane i % 32 keeps the running
+// sum after term i.  The pick is the smallest valid i whose running sum reaches u * total.
 template <typename T>
 __device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, int K, float u,
-                                           float temperature, float* p_smem, int32_t* out) {
+                                           float temperature, int32_t* out) {
+    constexpr int kSlots = ISPORE_TOPK_MAX_K / 32;
     const int lane = threadIdx.x & 31;
     const float v0 = to_float<T>(vals[0]);
-    for (int i = lane; i < K; i += 32)
-        p_smem[i] = ids[i] < 0 ? 0.f : expf((to_float<T>(vals[i]) - v0) / temperature);
-    __syncwarp();
-    if (lane == 0) {
-        float total = 0.f;
-        int last = -1;
-        for (int i = 0; i < K; ++i) {
-            if (ids[i] >= 0) {
-                total += p_smem[i];
-                last = i;
-            }
-        }
-        const float target = u * total;
-        float cum = 0.f;
-        int pick = last;
-        for (int i = 0; i < K; ++i) {
-            if (ids[i] < 0) continue;
-            cum += p_smem[i];
-            if (cum >= target) {
-                pick = i;
-                break;
-            }
-        }
-        *out = pick >= 0 ? ids[pick] : -1;
+    float p[kSlots], cum[kSlots];
+    int32_t id[kSlots];
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+        const int i = s * 32 + lane;
+        id[s] = i < K ? ids[i] : -1;
+        p[s] = id[s] < 0 ? 0.f : expf((to_float<T>(vals[i < K ? i : 0]) - v0) / temperature);
+        cum[s] = 0.f;
     }
+    float run = 0.f;
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+        if (s * 32 < K) {  // uniform
+            const unsigned valid = __ballot_sync(0xffffffffu, id[s] >= 0);
+            for (int l = 0; l < 32 && s * 32 + l < K; ++l) {
+                const float term = __shfl_sync(0xffffffffu, p[s], l);
+                if ((valid >> l) & 1u) run += term;  // empty slots are skipped, not added as zeros
+                if (l == lane) cum[s] = run;
+            }
+        }
+    }
+    const float target = u * run;
+    int pick = INT_MAX, last = -1;
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+        const int i = s * 32 + lane;
+        if (i < K && id[s] >= 0) {
+            last = i;
+            if (cum[s] >= target && i < pick) pick = i;
+        }
+    }
+    pick = __reduce_min_sync(0xffffffffu, pick);
+    last = __reduce_max_sync(0xffffffffu, last);
+    if (pick == INT_MAX) pick = last;  // nothing reached the target (rounding): the last valid slot
+    if (lane == 0) *out = pick >= 0 ? ids[pick] : -1;
 }
 
 // TMA: the tiles arrive through the copy engine (cp.async.bulk into one of two shared-memory
@@ -301,6 +318,8 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     __shared__ unsigned long long cand[2][kCandSlots];  // [cur]: running best then tile survivors
     __shared__ uint32_t warp_thr[kTopkWarps];
     __shared__ int s_count;
+    __shared__ int s_push[4];
+    __shared__ int s_timeout;
     __shared__ int hist[256];
     __shared__ int s_digit, s_need;
     __shared__ int warp_cnt[kTopkWarps];
@@ -314,6 +333,8 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     if (n64 > slice_len) n64 = slice_len;
     const int n = n64 > 0 ? static_cast<int>(n64) : 0;
     const T* src = probs + row * vocab + begin;
+
+    if (tid < 4) s_push[tid] = 0;  // visible before its first use: every tile kind has a barrier before the next tile
 
     int cur = 0;    // which cand[] buffer holds the running best
     int nbest = 0;  // entries of the running best (sorted, best first)
@@ -329,6 +350,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             tma::mbar_init(&full[0], 1);
             tma::mbar_init(&full[1], 1);
             tma::fence_mbar_init();
+            s_timeout = 0;
         }
         __syncthreads();
         if (tid == 0 && n > 0) {
@@ -337,20 +359,87 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         }
     }
 
+    // `pending` survivors of streamed tiles sit behind the running best, not yet ranked (uniform).
+    // Streamed tiles count their survivors in s_push[tile & 3]: the count of tile t is read by
+    // everyone after the barrier of tile t+1 while tile t+1 already counts in the next slot, and
+    // the slot is cleared again two tiles later, so no thread reads a counter that another is
+    // still adding to.
+    int pending = 0;
+    bool streamed_prev = false;  // the previous tile's survivors are parked and not yet counted into `pending`
+    uint32_t thr = 0;
+    // A bounded wait on a tile ran out somewhere in the CTA: record it, wait once more for the copy
+    // in flight (shared memory must not be released under it) and leave; every thread comes here.
+    auto timed_out = [&](int tile_no) {
+        if (tid == 0) {
+            atomicOr(status, ISPORE_DEV_TIMEOUT);
+            tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1);
+            if ((tile_no + 1) * kTileElems < n)  // the next tile was already on its way, too
+                tma::mbar_wait(&full[(tile_no + 1) & 1], ((tile_no + 1) >> 1) & 1);
+        }
+    };
+    auto issue_next = [&](int tile_no, int tile_begin) {
+        if (TMA && tid == 0 && tile_begin + kTileElems < n) {
+            const int next = tile_begin + kTileElems;
+            uint64_t* bar = &full[(tile_no + 1) & 1];
+            tma::mbar_arrive_expect_tx(bar, tile_bytes(next));
+            tma::load(stage_raw + static_cast<size_t>((tile_no + 1) & 1) * kStageBytes, src + next, tile_bytes(next), bar);
+        }
+    };
+    // Ranks the running best together with the first `count` entries behind it; afterwards the
+    // (sorted) best is in the other buffer.  Called by every thread; ends with a barrier.
+    auto rank_pending = [&](int count) {
+        const int total = nbest + count;
+        rank_into(cand[cur], nbest, total, K, cand[cur ^ 1]);
+        cur ^= 1;
+        nbest = total < K ? total : K;
+        pending = 0;
+        __syncthreads();
+        if (nbest == K) {
+            const uint32_t kth = static_cast<uint32_t>(cand[cur][K - 1] >> 32);
+            thr = kth == 0xffffffffu ? kth : kth + 1u;  // a later element must beat the K-th best outright
+        }
+    };
+    // The survivors of tile `tile_begin` did not fit behind the `kept` earlier ones: rank those,
+    // then select the tile's K largest exactly and rank again.
+    auto overflow_tile = [&](int tile_begin, int kept) {
+        if (kept > 0) rank_pending(kept);
+        exact_select_tile<T>(src, tile_begin, n, begin, K, cand[cur] + nbest,
+                             SelectScratch{hist, warp_cnt, &s_count, &s_digit, &s_need});
+        __syncthreads();
+        rank_pending(K);
+    };
+
+    // Counts the survivors the previous (streamed) tile parked behind the running best; ranks when
+    // the next tile's survivors (about K; room for twice that is kept) might no longer fit, and
+    // falls back to the exact selection when the previous tile alone overflowed its room.  Runs at
+    // the top of an iteration, after the barrier that ended the previous one, while no tile is
+    // held in registers.
+    auto settle_previous = [&](int prev_tile_no, bool last) {
+        const int added = s_push[prev_tile_no & 3];
+        if (pending + added > kTileCap) {
+            overflow_tile(prev_tile_no * kTileElems, pending);
+        } else {
+            pending += added;
+            if (pending > 0 && (last || pending + 2 * K > kTileCap)) rank_pending(pending);
+        }
+    };
+
     int tile_no = 0;
     for (int tile_begin = 0; tile_begin < n; tile_begin += kTileElems, ++tile_no) {
+        // The stage the next tile goes to was last read during the previous iteration, which ended
+        // with a barrier: the copy can start now and fly while this tile is worked on.
+        issue_next(tile_no, tile_begin);
+        if (tid == 0) s_push[(tile_no + 1) & 3] = 0;  // that slot was read for the last time two tiles ago
+        if (streamed_prev) settle_previous(tile_no - 1, false);
+        streamed_prev = false;
+
         int bits[kElemsPerThread];
         int pmax;
         const T* stage = reinterpret_cast<const T*>(stage_raw + static_cast<size_t>(tile_no & 1) * kStageBytes);
         if (TMA) {
-            const bool arrived = tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1);
-            if (__syncthreads_or(!arrived)) {  // uniform: a copy did not land in time
-                if (tid == 0) {
-                    atomicOr(status, ISPORE_DEV_TIMEOUT);
-                    tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1);  // once more for the copy in flight
-                }
-                return;
-            }
+            // A wait that runs out is recorded here and acted on by the whole CTA after the next
+            // barrier (whatever was read meanwhile is discarded).
+            if (!tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1)) s_timeout = 1;
             pmax = INT_MIN;
             const uint4* stage_v = reinterpret_cast<const uint4*>(stage);
 #pragma unroll
@@ -370,82 +459,75 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         }
         // Slot i of this thread is slice element elem_of(i); a slot is live iff that is < n.
         auto elem_of = [&](int i) { return tile_begin + (tid + (i / E) * kTopkThreads) * E + (i % E); };
+        // Survivors of this thread: the slots whose key reaches `limit`, pushed behind the running
+        // best from position base + (this thread's share of `counter`), dropped beyond kTileCap
+        // (the counter still counts them, which is how the overflow is noticed).
+        auto push_survivors = [&](uint32_t limit, int base, int* counter) {
+            uint32_t mask = 0;
+            if (limit > 0x80000000u) {
+                // limit is the key of a positive float: survivors are exactly the slots whose raw
+                // bits, as signed ints, reach its bits (empty slots hold INT_MIN and never do).
+                // pmax is the largest of them, so one compare clears a thread without survivors —
+                // nearly every thread of every tile after the first.
+                const int limit_bits = static_cast<int>(limit & 0x7fffffffu);
+                if (pmax >= limit_bits) {
+#pragma unroll
+                    for (int i = 0; i < kElemsPerThread; ++i) mask |= (bits[i] >= limit_bits ? 1u : 0u) << i;
+                }
+            } else {
+#pragma unroll
+                for (int i = 0; i < kElemsPerThread; ++i)
+                    mask |= (elem_of(i) < n && order_key(__int_as_float(bits[i])) >= limit ? 1u : 0u) << i;
+            }
+            if (TOPK_DEBUG(16)) mask = 0;
+            if (mask != 0) {
+                int pos = base + atomicAdd(counter, __popc(mask));
+                unsigned long long* mine = cand[cur] + nbest;
+                while (mask != 0 && pos < kTileCap) {
+                    const int i = __ffs(mask) - 1;
+                    mask &= mask - 1;
+                    const int el = elem_of(i);
+                    // The slot's value is re-read (cache hit) rather than picked out of the register
+                    // array with a run-time index.
+                    const T value = TMA ? stage[el - tile_begin] : src[el];
+                    mine[pos++] = composite(order_key(to_float<T>(value)), static_cast<uint32_t>(begin + el));
+                }
+            }
+        };
 
-        // Threshold.  First tile(s), while fewer than K entries are held: the q-th largest
-        // thread representative of every warp, minimum over warps => at least K tile elements
-        // have key >= threshold.  Once K entries are held an element only matters if it beats
-        // the current K-th best outright (on a tie the earlier index, already held, wins).
-        uint32_t thr;
-        if (nbest == K) {
-            const uint32_t kth = static_cast<uint32_t>(cand[cur][K - 1] >> 32);
-            thr = kth == 0xffffffffu ? kth : kth + 1u;
-            if (tid == 0) s_count = 0;
-            __syncthreads();
-        } else {
+        if (nbest < K) {
+            // Fewer than K entries are held (the first tile; later ones only in tiny tiles): the
+            // threshold is the q-th largest thread representative of every warp, minimum over warps,
+            // so that at least K tile elements have key >= threshold; the survivors are ranked at once.
             const bool any_live = elem_of(0) < n;
             const uint32_t wq = warp_qth_largest(any_live ? order_key(__int_as_float(pmax)) : 0u, q);
             if ((tid & 31) == 0) warp_thr[tid >> 5] = wq;
             if (tid == 0) s_count = 0;
             __syncthreads();
-            thr = warp_thr[0];
+            if (TMA && s_timeout) return timed_out(tile_no);
+            uint32_t first_thr = warp_thr[0];
 #pragma unroll
-            for (int w = 1; w < kTopkWarps; ++w) thr = min(thr, warp_thr[w]);
-        }
-
-        // Every thread has its tile in registers (the barrier above): the other stage is free,
-        // so the next tile can start flying now and land while this one is ranked.
-        if (TMA && tid == 0 && tile_begin + kTileElems < n) {
-            const int next = tile_begin + kTileElems;
-            uint64_t* bar = &full[(tile_no + 1) & 1];
-            tma::mbar_arrive_expect_tx(bar, tile_bytes(next));
-            tma::load(stage_raw + static_cast<size_t>((tile_no + 1) & 1) * kStageBytes, src + next, tile_bytes(next), bar);
-        }
-
-        // Survivor mask of this thread's 32 slots.
-        uint32_t mask = 0;
-        if (TOPK_DEBUG(16)) {
-            mask = 0;
-        } else if (thr > 0x80000000u) {
-            // thr is the key of a positive float: survivors are exactly the slots whose raw
-            // bits, as signed ints, reach thr's bits (empty slots hold INT_MIN and never do).
-            const int thr_bits = static_cast<int>(thr & 0x7fffffffu);
-#pragma unroll
-            for (int i = 0; i < kElemsPerThread; ++i) mask |= (bits[i] >= thr_bits ? 1u : 0u) << i;
-        } else {
-#pragma unroll
-            for (int i = 0; i < kElemsPerThread; ++i)
-                mask |= (elem_of(i) < n && order_key(__int_as_float(bits[i])) >= thr ? 1u : 0u) << i;
-        }
-        unsigned long long* mine = cand[cur] + nbest;  // tile survivors go behind the running best
-        if (mask != 0 && !TOPK_DEBUG(8)) {
-            int pos = atomicAdd(&s_count, __popc(mask));
-            while (mask != 0 && pos < kTileCap) {
-                const int i = __ffs(mask) - 1;
-                mask &= mask - 1;
-                const int el = elem_of(i);
-                // The slot's value is re-read (cache hit) rather than picked out of the register
-                // array with a run-time index.
-                const T value = TMA ? stage[el - tile_begin] : src[el];
-                mine[pos++] = composite(order_key(to_float<T>(value)), static_cast<uint32_t>(begin + el));
-            }
-        }
-        __syncthreads();
-        int count = s_count;
-
-        if (count > kTileCap) {
-            exact_select_tile<T>(src, tile_begin, n, begin, K, mine,
-                                 SelectScratch{hist, warp_cnt, &s_count, &s_digit, &s_need});
-            count = K;
+            for (int w = 1; w < kTopkWarps; ++w) first_thr = min(first_thr, warp_thr[w]);
+            push_survivors(first_thr, 0, &s_count);
             __syncthreads();
+            const int count = s_count;
+            if (count > kTileCap) {
+                overflow_tile(tile_begin, 0);
+            } else {
+                rank_pending(count);
+            }
+            continue;
         }
 
-        // Merge the tile's survivors into the running best: rank everything, keep rank < K.
-        const int total = nbest + count;
-        if (!TOPK_DEBUG(4)) rank_into(cand[cur], nbest, total, K, cand[cur ^ 1]);
-        cur ^= 1;
-        nbest = total < K ? total : K;
-        __syncthreads();
+        // Streamed tile: K entries are held, an element only matters if it beats the current K-th
+        // best outright (on a tie the earlier index, already held, wins).  Survivors are parked
+        // behind the running best and ranked every few tiles, not per tile.
+        push_survivors(thr, pending, &s_push[tile_no & 3]);
+        streamed_prev = true;
+        __syncthreads();  // the tile has been read and its survivors counted by every thread
+        if (TMA && s_timeout) return timed_out(tile_no);
     }
+    if (streamed_prev) settle_previous(tile_no - 1, true);
 
     int32_t* out_ids = out_ids_base + (row * out_lists + slice) * K;
     T* out_vals = out_vals_base + (row * out_lists + slice) * K;
@@ -464,8 +546,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     if (uniform != nullptr) {
         __syncthreads();  // the list written above is visible to warp 0
         if (tid < 32)
-            sample_row<T>(out_ids, out_vals, K, uniform[row], temperature, reinterpret_cast<float*>(hist),
-                          sampled_ids + row);
+            sample_row<T>(out_ids, out_vals, K, uniform[row], temperature, sampled_ids + row);
     }
 }
 
@@ -479,7 +560,6 @@ topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ ca
     unsigned long long* comp = reinterpret_cast<unsigned long long*>(smem_raw);  // [lists*K]
     __shared__ int32_t fin_ids[ISPORE_TOPK_MAX_K];
     __shared__ T fin_vals[ISPORE_TOPK_MAX_K];
-    __shared__ float p_smem[ISPORE_TOPK_MAX_K];
     chain_begin();
 
     const int tid = threadIdx.x;
@@ -532,7 +612,7 @@ topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ ca
         final_vals[row * K + s] = fin_vals[s];
     }
     if (uniform != nullptr && tid < 32)
-        sample_row<T>(fin_ids, fin_vals, K, uniform[row], temperature, p_smem, sampled_ids + row);
+        sample_row<T>(fin_ids, fin_vals, K, uniform[row], temperature, sampled_ids + row);
 }
 
 template <typename T>
@@ -540,12 +620,10 @@ __global__ void __launch_bounds__(kTopkThreads)
 sampling_kernel(const int32_t* __restrict__ topk_ids, const T* __restrict__ topk_vals,
                 const float* __restrict__ uniform, int32_t* __restrict__ output_ids, int64_t rows,
                 int K, float temperature) {
-    __shared__ float p_smem[kTopkWarps][ISPORE_TOPK_MAX_K];
     const int warp = threadIdx.x >> 5;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * kTopkWarps + warp;
     if (row >= rows) return;  // whole warps leave; no block barrier follows
-    sample_row<T>(topk_ids + row * K, topk_vals + row * K, K, uniform[row], temperature, p_smem[warp],
-                  output_ids + row);
+    sample_row<T>(topk_ids + row * K, topk_vals + row * K, K, uniform[row], temperature, output_ids + row);
 }
 
 int check_k(const char* who, int32_t K) {

@@ -85,6 +85,8 @@ DROPIN_TESTS = [
 ]
 # The decode attention test calls CHECK_CUDA_ERROR, which no header of the reference defines
 # (src/utils/macro.h has CHECK only); the definition comes from the command line, the file is untouched.
+# unit test -> the per-kernel static archive it links in the reference's tests/unittests/CMakeLists.txt
+STATIC_DROPIN = {"test_act": "act", "test_mask_softmax": "mask_softmax"}
 DROPIN_FLAGS = {"test_fused_decoder_attention": ["-DCHECK_CUDA_ERROR(call)=CHECK(call)"]}
 
 
@@ -138,9 +140,20 @@ def build_reference(ref_root: Path = DEFAULT_REF_ROOT, force: bool = False) -> l
                                f"-I{ROOT / 'include'}",
                                str(src), "-o", str(out), f"-L{lib_dir}", "-lispore_kernels",
                                "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN/../../../inferspore_b200/lib"]))
+    # The reference links each unit test against one per-kernel static archive (e.g. test_act against
+    # `act`, tests/unittests/CMakeLists.txt); the same link line against this library's archives of
+    # the same names, without the shared library:
+    static_dir = lib_dir / "static"
+    for test, archive in STATIC_DROPIN.items():
+        out = REF_OUT / "dropin" / f"{test}_static"
+        src = ref_root / "tests" / "unittests" / f"{test}.cu"
+        if (static_dir / f"lib{archive}.a").exists() and (force or not _newer(out, [src, *headers, static_dir / f"lib{archive}.a"])):
+            jobs.append((out, [nvcc, "-std=c++17", "-O2", *ARCH, "-w", f"-I{compat}", f"-I{ROOT / 'include'}", str(src),
+                               "-o", str(out), f"-L{static_dir}", f"-l{archive}"]))
     with cf.ThreadPoolExecutor(max_workers=8) as pool:
         list(pool.map(lambda job: _run(job[1]), jobs))
-    return [REF_OUT / n for n in REF_LIBS] + [REF_OUT / "dropin" / t for t in DROPIN_TESTS]
+    return ([REF_OUT / n for n in REF_LIBS] + [REF_OUT / "dropin" / t for t in DROPIN_TESTS] +
+            [REF_OUT / "dropin" / f"{t}_static" for t in STATIC_DROPIN])
 
 
 def main(argv: list[str] | None = None) -> int:

@@ -500,6 +500,35 @@ def test_topk_any_scratch_size(ops, orc, rng, slices, rows, vocab, K):
     assert np.all(margin[picked != want_pick] < 1e-6)
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("shape", ["noise", "rising", "falling", "steps", "negative"])
+@pytest.mark.parametrize("vocab,K", [(100000, 50), (65536, 256), (70001, 100), (40000, 1)])
+def test_topk_one_cta_walks_a_long_row(ops, orc, rng, dtype, shape, vocab, K):
+    """One slice per row, so a CTA streams 5 to 13 tiles: later tiles park their survivors behind the
+    running best and are ranked every few tiles.  `rising` makes every later tile beat the running
+    K-th best with many elements (parked lists overflow: exact selection per tile), `steps` does so
+    for some tiles only, `falling` and `noise` leave few or no survivors, `negative` keeps the
+    threshold below zero (the slower order-key compare).  70001 is not a whole number of 128-bit
+    vectors: plain loads instead of the TMA ring."""
+    rows = 3
+    x = rng.standard_normal((rows, vocab)).astype(np.float32)
+    t = np.arange(vocab, dtype=np.float32) / vocab
+    if shape == "rising":
+        x += 8 * t
+    elif shape == "falling":
+        x -= 8 * t
+    elif shape == "steps":
+        x += 3.0 * ((np.arange(vocab) // 8192) % 3 == 2)
+    elif shape == "negative":
+        x = -np.abs(x) - 1.0
+    probs = x.astype(dtype)
+    got_i, got_v, _ = _topk_run(ops, probs, K, slices=1)
+    want_i, want_v = orc.topk(probs, K)
+    bits = np.uint32 if dtype == np.float32 else np.uint16
+    assert np.array_equal(got_i, want_i)
+    assert np.array_equal(got_v.view(bits), want_v.view(bits))
+
+
 def test_topk_without_scratch(ops, orc, rng):
     probs = (rng.standard_normal((4, 20000), dtype=np.float32))
     f_i = torch.empty((4, 10), dtype=torch.int32, device="cuda:0")

@@ -61,6 +61,21 @@ def test_dropin_act(cuda, half):
     assert "test passed" in out and "res is wrong" not in out
 
 
+@pytest.mark.parametrize("half", [False, True])
+def test_dropin_act_linked_against_the_static_archive(cuda, half):
+    # the reference's own link line: test_act against the per-kernel archive `act`, no shared library
+    out = _run("test_act_static", *(["1"] if half else []))
+    assert "test passed" in out and "res is wrong" not in out
+
+
+def test_dropin_mask_softmax_linked_against_the_static_archive(cuda):
+    out = _run("test_mask_softmax_static")
+    vals = np.array([float(l.split("=")[1]) for l in out.splitlines() if l.startswith("attn score[")])
+    z = 0.5 * np.arange(8)
+    e = np.exp(z - z.max())
+    assert vals.shape == (128,) and np.allclose(vals, np.tile(e / (e.sum() + 1e-6), 16), atol=2e-6)
+
+
 @pytest.mark.parametrize("fp32", [False, True])
 def test_dropin_input_embedding(cuda, fp32):
     out = _run("test_input_embedding", *(["1"] if fp32 else []))
@@ -433,7 +448,7 @@ int main() {
     CUDA_OK(cudaMemcpy(d_qkv, h_qkv.data(), n_qkv * 2, cudaMemcpyHostToDevice));
     for (half* p : {d_k, d_v, d_k2, d_v2}) CUDA_OK(cudaMemcpy(p, h_cache.data(), n_cache * 2, cudaMemcpyHostToDevice));
 
-    // 1. through the reference's launcher signature: the template sizes and keeps its own workspace
+    // 1. through the reference's launcher signature
     TensorWrapper<half> qkv(GPU, FP16, {batch, heads + 2 * kv, d}, d_qkv);
     TensorWrapper<half> kc(GPU, FP16, {1, batch, kv, max_seq, d}, d_k), vc(GPU, FP16, {1, batch, kv, max_seq, d}, d_v);
     TensorWrapper<half> out(GPU, FP16, {batch, heads, d}, d_out);
@@ -445,9 +460,29 @@ int main() {
     params.rotary_embedding_base = 10000.0f;
     params.max_position_embeddings = 4096;
     params.use_dynamic_ntk = false;
-    if (ispore_decoder_masked_mha_workspace_bytes(batch, heads, kv, d, step) <= 0) { std::printf("expected a split plan\n"); return 1; }
-    for (int rep = 0; rep < 2; ++rep)  // the second call reuses the buffer
+    const long long ws_bytes = ispore_decoder_masked_mha_workspace_bytes(batch, heads, kv, d, step);
+    if (ws_bytes <= 0) { std::printf("expected a split plan\n"); return 1; }
+#ifndef ISPORE_MHA_ALLOC_WORKSPACE
+    // default build of the header: it allocates nothing, the host hands its own scratch over
+    void* ws = nullptr;
+    CUDA_OK(cudaMalloc(&ws, ws_bytes));
+    ispore_compat::set_mha_workspace(ws, ws_bytes);
+#endif
+    launchDecoderMaskedMHA(&qkv, w, &lid, &kc, &vc, &fin, &st, &out, params);  // first call: the CUDA module loads here
+    CUDA_OK(cudaDeviceSynchronize());
+    for (half* p : {d_k, d_v}) CUDA_OK(cudaMemcpy(p, h_cache.data(), n_cache * 2, cudaMemcpyHostToDevice));
+    size_t free_before = 0, free_after = 0, total_mem = 0;
+    CUDA_OK(cudaMemGetInfo(&free_before, &total_mem));
+    for (int rep = 0; rep < 2; ++rep)  // later calls reuse the buffer
         launchDecoderMaskedMHA(&qkv, w, &lid, &kc, &vc, &fin, &st, &out, params);
+    CUDA_OK(cudaDeviceSynchronize());
+    CUDA_OK(cudaMemGetInfo(&free_after, &total_mem));
+    if (free_after != free_before) { std::printf("free device memory moved by %lld bytes\n", (long long)free_before - (long long)free_after); return 1; }
+#ifdef ISPORE_MHA_ALLOC_WORKSPACE
+    if (!ispore_compat::mha_slots().owned[0] || ispore_compat::mha_slots().cap[0] < ws_bytes) { std::printf("expected the opt-in build to own its scratch\n"); return 1; }
+#else
+    if (ispore_compat::mha_slots().owned[0] || ispore_compat::mha_slots().buf[0] != ws) { std::printf("expected the host's scratch to be used\n"); return 1; }
+#endif
     // 2. the C ABI without a workspace: one CTA per (sequence, head)
     if (ispore_decoder_masked_mha_f16(d_out2, d_qkv, nullptr, d_k2, d_v2, 0, 1, batch, heads, kv, max_seq, d, step, 128,
                                       10000.0f, float(step), nullptr, 0, nullptr) != ISPORE_OK) {
@@ -472,7 +507,11 @@ int main() {
 """
 
 
-def test_cpp_caller_decoder_attention_with_template_workspace(cuda, tmp_path):
+@pytest.mark.parametrize("mode", ["handed_over", "header_allocates"])
+def test_cpp_caller_decoder_attention_with_template_workspace(cuda, tmp_path, mode):
+    """The drop-in launcher with scratch handed over by the host (default build: the header must not
+    allocate — free device memory is compared around the calls) and with the opt-in build in which
+    the header allocates it; both against the C ABI without scratch."""
     import shutil
 
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
@@ -481,6 +520,7 @@ def test_cpp_caller_decoder_attention_with_template_workspace(cuda, tmp_path):
     exe = tmp_path / "mha_caller"
     lib_dir = ROOT / "inferspore_b200" / "lib"
     cmd = [nvcc, "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-w",
+           *(["-DISPORE_MHA_ALLOC_WORKSPACE"] if mode == "header_allocates" else []),
            f"-I{ROOT / 'inferspore_b200' / 'compat'}", f"-I{ROOT / 'include'}", str(src), "-o", str(exe),
            f"-L{lib_dir}", "-lispore_kernels", "-Xlinker", "-rpath", "-Xlinker", str(lib_dir)]
     build = subprocess.run(cmd, capture_output=True, text=True)

@@ -111,3 +111,44 @@ def test_reference_unit_tests_build_unmodified():
         assert exe.exists(), name
         ldd = subprocess.run(["ldd", str(exe)], capture_output=True, text=True).stdout
         assert "libispore_kernels.so" in ldd and "not found" not in ldd.split("libispore_kernels.so")[1].split("\n")[0]
+
+
+def test_per_kernel_static_archives_carry_the_reference_target_names(tmp_path):
+    """inferspore_b200/build.py emits one archive per CMake target of the reference's
+    src/kernels/CMakeLists.txt; each defines the C-ABI symbols its launcher template calls, and a
+    program that includes every launcher links against all of them together (the shared object
+    that several archives contain is pulled once: no duplicate symbols)."""
+    from inferspore_b200 import build as lib_build
+
+    static = lib_build.STATIC_DIR
+    needs = {
+        "embeddingFunctor": ["ispore_input_embedding_f16"],
+        "cal_paddingoffset": ["ispore_cal_padding_offset"],
+        "build_casual_mask": ["ispore_build_causal_mask_f32"],
+        "qkv_bias_and_rope": ["ispore_qkv_bias_rope_transpose_f16", "ispore_rope_decode_f32"],
+        "concat_kv": ["ispore_concat_kv_f16"],
+        "repeat_kv": ["ispore_repeat_kv_f16"],
+        "mask_softmax": ["ispore_scale_mask_softmax_f16", "ispore_scale_causal_softmax_f32"],
+        "fused_transpose_and_remv_pad": ["ispore_transpose_remove_padding_f16"],
+        "fused_addresidual_norm": ["ispore_add_residual_rmsnorm_f32", "ispore_rmsnorm_f16"],
+        "act": ["ispore_silu_mul_f16"],
+        "topk": ["ispore_topk_f32", "ispore_topk_merge_f16", "ispore_sampling_f32"],
+        "fused_decoder_self_attention": ["ispore_decoder_masked_mha_f16"],
+    }
+    assert set(needs) == set(lib_build.ARCHIVES)
+    for target, symbols in needs.items():
+        archive = static / f"lib{target}.a"
+        assert archive.exists(), archive
+        defined = subprocess.run(["nm", "--defined-only", str(archive)], capture_output=True, text=True).stdout
+        for sym in symbols + ["ispore_last_error_string", "ispore_get_stream"]:
+            assert f" T {sym}" in defined, (target, sym)
+    src = tmp_path / "compat_host.cu"
+    src.write_text(PROGRAM)
+    exe = tmp_path / "compat_static"
+    cmd = [lib_build.find_nvcc(), "-std=c++17", "-w", "-gencode", "arch=compute_100a,code=sm_100a",
+           f"-I{ROOT / 'inferspore_b200' / 'compat'}", f"-I{ROOT / 'include'}", str(src), "-o", str(exe), f"-L{static}",
+           *[f"-l{t}" for t in needs]]
+    build = subprocess.run(cmd, capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr[-3000:]
+    out = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert out.returncode == 0 and "compat ok" in out.stdout, out.stdout + out.stderr
