@@ -198,6 +198,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
     __shared__ float red_s[kWarps];
     __shared__ float m_s[GT], l_s[GT];
     __shared__ __align__(8) uint64_t full[kStages];
+    chain_begin();
     extern __shared__ __align__(128) unsigned char dyn_raw[];  // [tiles when STAGED][logits / output reduction buffer]
     unsigned char* const stage_base = dyn_raw;
     float* const dyn_s = reinterpret_cast<float*>(dyn_raw + (STAGED ? kStages * kStageStride : 0));
@@ -685,6 +686,7 @@ decoder_mha_kernel(const MhaParams<T> p, const RopeAngles angles, unsigned* __re
 template <typename T>
 __global__ void __launch_bounds__(128)
 decoder_mha_combine_kernel(T* __restrict__ out, const float* __restrict__ workspace, int splits, int head_size) {
+    chain_begin();
     const int64_t bh = blockIdx.x;
     const float* ws = workspace + bh * splits * (head_size + 2);
     float mx = -FLT_MAX;
@@ -749,10 +751,11 @@ int launch_mha(const MhaParams<T>& p, const RopeAngles& angles, int64_t batch, c
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "decoder_masked_mha: no device status word");
     dim3 grid(static_cast<unsigned>(batch * p.kv_heads * p.head_groups), static_cast<unsigned>(p.splits));
-    kernel<<<grid, mha_threads<T, LPK, GT, STAGED>(), smem, st>>>(p, angles, status);
+    launch_chained(kernel, grid, mha_threads<T, LPK, GT, STAGED>(), smem, st, p, angles, status);
     int rc = check_launch("decoder_mha_kernel");
     if (rc != ISPORE_OK || p.splits == 1) return rc;
-    decoder_mha_combine_kernel<T><<<static_cast<unsigned>(batch * p.heads), 128, 0, st>>>(p.out, p.workspace, p.splits, D);
+    launch_chained(decoder_mha_combine_kernel<T>, static_cast<unsigned>(batch * p.heads), 128, 0, st, p.out, p.workspace,
+                   p.splits, D);
     return check_launch("decoder_mha_combine_kernel");
 }
 

@@ -370,6 +370,7 @@ __global__ void __launch_bounds__(THREADS)
 rope_decode_kernel(T* __restrict__ qkv, int head_num, int kv_head_num, int head_size, int rot_half,
                    float position, const RopeDenominators freq) {
     __shared__ float2 cos_sin[kMaxRotHalf];
+    chain_begin();
     const int tid = threadIdx.x;
     for (int j = tid; j < rot_half; j += THREADS) {
         float sn, cs;
@@ -496,7 +497,7 @@ int rope_decode_dispatch(T* qkv, int64_t batch, int64_t head_num, int64_t kv_hea
     if (batch == 0) return ISPORE_OK;
     if (!qkv) return fail(ISPORE_ENULL, "rope_decode: NULL buffer");
     constexpr int THREADS = 256;
-    rope_decode_kernel<T, THREADS><<<static_cast<int>(batch), THREADS, 0, st>>>(
+    launch_chained(rope_decode_kernel<T, THREADS>, static_cast<int>(batch), THREADS, 0, st,
         qkv, (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2,
         static_cast<float>(step - 1), freq);
     return check_launch("rope_decode_kernel");

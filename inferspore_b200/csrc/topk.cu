@@ -620,6 +620,7 @@ __global__ void __launch_bounds__(kTopkThreads)
 sampling_kernel(const int32_t* __restrict__ topk_ids, const T* __restrict__ topk_vals,
                 const float* __restrict__ uniform, int32_t* __restrict__ output_ids, int64_t rows,
                 int K, float temperature) {
+    chain_begin();
     const int warp = threadIdx.x >> 5;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * kTopkWarps + warp;
     if (row >= rows) return;  // whole warps leave; no block barrier follows
@@ -639,7 +640,7 @@ int sampling_dispatch(const int32_t* ids, const T* vals, const float* uniform, i
     if (!(temperature > 0.f)) return fail(ISPORE_ESHAPE, "sampling: temperature must be > 0");
     if (rows == 0) return ISPORE_OK;
     if (!ids || !vals || !uniform || !out) return fail(ISPORE_ENULL, "sampling: NULL buffer");
-    sampling_kernel<T><<<static_cast<int>(ceil_div(rows, kTopkWarps)), kTopkThreads, 0, st>>>(
+    launch_chained(sampling_kernel<T>, static_cast<int>(ceil_div(rows, kTopkWarps)), kTopkThreads, 0, st,
         ids, vals, uniform, out, rows, K, temperature);
     return check_launch("sampling_kernel");
 }

@@ -375,9 +375,8 @@ def _distinct_positive(rng, vocab, dtype):
     31,743 positive finite patterns, so a longer row repeats some patterns from the lower half of
     the range, which can never reach the first places."""
     if dtype == np.float32:
-        v = (rng.random(vocab, dtype=np.float32) + np.float32(1e-3))
-        while np.unique(v).size != vocab:
-            v = (rng.random(vocab, dtype=np.float32) + np.float32(1e-3))
+        v = ((rng.permutation(vocab) + 1) / np.float32(vocab)).astype(np.float32)  # k / vocab: exact steps, all distinct
+        assert np.unique(v).size == vocab
         return v
     patterns = np.arange(1, 0x7C00, dtype=np.uint16)  # every positive finite half, subnormals included
     if vocab <= patterns.size:
