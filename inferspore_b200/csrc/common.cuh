@@ -43,8 +43,11 @@ inline bool allow_dynamic_smem(Kernel kernel, size_t bytes) {
 // after its predecessor has: ordering stays transitive along the stream.
 bool programmatic_launch_enabled();  // thread-local, c_api.cu
 
+#ifndef ISPORE_CHAIN_MODE
+#define ISPORE_CHAIN_MODE 0  // experiments: 1 = wait only (the successor is released when this grid's CTAs exit)
+#endif
 __device__ __forceinline__ void chain_begin() {
-    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    if (ISPORE_CHAIN_MODE == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     asm volatile("griddepcontrol.wait;" ::: "memory");
 }
 

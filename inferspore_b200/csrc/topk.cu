@@ -46,8 +46,9 @@ __device__ int g_topk_debug = 0;  // ablation switches, tuning builds only
 
 constexpr int kTopkThreads = 256;  // measured: 512 threads x 16 keys is 1.5x slower (barriers over 16 warps)
 constexpr int kTopkWarps = kTopkThreads / 32;
-constexpr int kElemsPerThread = 32;                          // keys a thread holds per tile
-constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
+constexpr int kElemsPerThread = 16;                          // keys a thread holds per tile
+constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 4096
+constexpr int kMaxStages = 8;                                // tiles of the shared-memory ring
 constexpr int kTileCap = 256;                                // survivors a tile may add on the fast path
 constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + tile survivors
 constexpr int kMergeCap = 4096;                              // lists*K candidates the merge kernel holds
@@ -300,21 +301,23 @@ __device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, in
     if (lane == 0) *out = pick >= 0 ? ids[pick] : -1;
 }
 
-// TMA: the tiles arrive through the copy engine (cp.async.bulk into one of two shared-memory
-// stages, completion on an mbarrier), issued one tile ahead, so tile t+1 is on its way while
-// tile t is being thresholded and ranked; the registers are filled from shared memory.  Needs
-// the vector-load conditions (16-byte aligned rows, slice length a multiple of the vector).
-// Without TMA the tile is loaded straight into registers.
+// TMA: the tiles arrive through the copy engine (cp.async.bulk into a ring of `nstages`
+// shared-memory stages, completion on one mbarrier per stage), requested nstages - 1 tiles ahead:
+// while the first tile is thresholded and ranked — the one long serial step of a row, and one that
+// every CTA of a launch reaches at the same moment — the following tiles are already on their way,
+// so HBM does not go idle.  The registers are filled from shared memory.  Needs the vector-load
+// conditions (16-byte aligned rows, slice length a multiple of the vector).  Without TMA the tile
+// is loaded straight into registers.
 template <typename T, int MIN_BLOCKS, bool TMA>
 __global__ void __launch_bounds__(kTopkThreads, MIN_BLOCKS)
 topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int slices, int K,
                   int32_t* __restrict__ out_ids_base, T* __restrict__ out_vals_base, int out_lists,
-                  int32_t index_offset, int vec_loads, unsigned* __restrict__ status,
+                  int32_t index_offset, int vec_loads, int nstages, unsigned* __restrict__ status,
                   const float* __restrict__ uniform, float temperature, int32_t* __restrict__ sampled_ids) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int kVecs = kElemsPerThread / E;
-    extern __shared__ __align__(128) unsigned char stage_raw[];  // TMA: [2][kTileElems * sizeof(T)]
-    __shared__ __align__(8) uint64_t full[2];
+    extern __shared__ __align__(128) unsigned char stage_raw[];  // TMA: [nstages][kTileElems * sizeof(T)]
+    __shared__ __align__(8) uint64_t full[kMaxStages];
     __shared__ unsigned long long cand[2][kCandSlots];  // [cur]: running best then tile survivors
     __shared__ uint32_t warp_thr[kTopkWarps];
     __shared__ int s_count;
@@ -345,19 +348,25 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         const int left = n - tile_begin;
         return static_cast<uint32_t>(left < kTileElems ? left : kTileElems) * static_cast<uint32_t>(sizeof(T));
     };
+    // Tile t lives in stage t % nstages and completes its barrier with parity (t / nstages) & 1.
+    auto issue_tile = [&](int tile, int stage) {  // thread 0 only
+        const int tile_begin = tile * kTileElems;
+        tma::mbar_arrive_expect_tx(&full[stage], tile_bytes(tile_begin));
+        tma::load(stage_raw + static_cast<size_t>(stage) * kStageBytes, src + tile_begin, tile_bytes(tile_begin), &full[stage]);
+    };
+    const int ntiles = (n + kTileElems - 1) / kTileElems;
     if (TMA) {
         if (tid == 0) {
-            tma::mbar_init(&full[0], 1);
-            tma::mbar_init(&full[1], 1);
+            for (int st = 0; st < nstages; ++st) tma::mbar_init(&full[st], 1);
             tma::fence_mbar_init();
             s_timeout = 0;
         }
         __syncthreads();
-        if (tid == 0 && n > 0) {
-            tma::mbar_arrive_expect_tx(&full[0], tile_bytes(0));
-            tma::load(stage_raw, src, tile_bytes(0), &full[0]);
-        }
+        if (tid == 0)
+            for (int tile = 0; tile < nstages - 1 && tile < ntiles; ++tile) issue_tile(tile, tile);
     }
+    int ring_stage = 0;        // stage of the tile worked on
+    uint32_t ring_phase = 0;   // parity its barrier completes with
 
     // `pending` survivors of streamed tiles sit behind the running best, not yet ranked (uniform).
     // Streamed tiles count their survivors in s_push[tile & 3]: the count of tile t is read by
@@ -372,18 +381,15 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     auto timed_out = [&](int tile_no) {
         if (tid == 0) {
             atomicOr(status, ISPORE_DEV_TIMEOUT);
-            tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1);
-            if ((tile_no + 1) * kTileElems < n)  // the next tile was already on its way, too
-                tma::mbar_wait(&full[(tile_no + 1) & 1], ((tile_no + 1) >> 1) & 1);
+            for (int t2 = tile_no; t2 < tile_no + nstages && t2 < ntiles; ++t2)  // this tile and those already requested
+                tma::mbar_wait(&full[t2 % nstages], static_cast<uint32_t>(t2 / nstages) & 1u);
         }
     };
-    auto issue_next = [&](int tile_no, int tile_begin) {
-        if (TMA && tid == 0 && tile_begin + kTileElems < n) {
-            const int next = tile_begin + kTileElems;
-            uint64_t* bar = &full[(tile_no + 1) & 1];
-            tma::mbar_arrive_expect_tx(bar, tile_bytes(next));
-            tma::load(stage_raw + static_cast<size_t>((tile_no + 1) & 1) * kStageBytes, src + next, tile_bytes(next), bar);
-        }
+    // At the top of iteration t the stage of tile t - 1 is free (that iteration ended with a
+    // barrier): tile t + nstages - 1 goes there.
+    auto issue_next = [&](int tile_no) {
+        const int ahead = tile_no + nstages - 1;
+        if (TMA && tid == 0 && ahead < ntiles) issue_tile(ahead, ring_stage == 0 ? nstages - 1 : ring_stage - 1);
     };
     // Ranks the running best together with the first `count` entries behind it; afterwards the
     // (sorted) best is in the other buffer.  Called by every thread; ends with a barrier.
@@ -428,18 +434,22 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     for (int tile_begin = 0; tile_begin < n; tile_begin += kTileElems, ++tile_no) {
         // The stage the next tile goes to was last read during the previous iteration, which ended
         // with a barrier: the copy can start now and fly while this tile is worked on.
-        issue_next(tile_no, tile_begin);
+        issue_next(tile_no);
         if (tid == 0) s_push[(tile_no + 1) & 3] = 0;  // that slot was read for the last time two tiles ago
         if (streamed_prev) settle_previous(tile_no - 1, false);
         streamed_prev = false;
 
         int bits[kElemsPerThread];
         int pmax;
-        const T* stage = reinterpret_cast<const T*>(stage_raw + static_cast<size_t>(tile_no & 1) * kStageBytes);
+        const T* stage = reinterpret_cast<const T*>(stage_raw + static_cast<size_t>(ring_stage) * kStageBytes);
         if (TMA) {
             // A wait that runs out is recorded here and acted on by the whole CTA after the next
             // barrier (whatever was read meanwhile is discarded).
-            if (!tma::mbar_wait(&full[tile_no & 1], (tile_no >> 1) & 1)) s_timeout = 1;
+            if (!tma::mbar_wait(&full[ring_stage], ring_phase)) s_timeout = 1;
+            if (++ring_stage == nstages) {  // (the next iteration's stage; `stage` above keeps this tile's)
+                ring_stage = 0;
+                ring_phase ^= 1u;
+            }
             pmax = INT_MIN;
             const uint4* stage_v = reinterpret_cast<const uint4*>(stage);
 #pragma unroll
@@ -690,16 +700,18 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
     const int vec_loads = (vocab % E == 0) && aligned16(probs);
     const bool use_tma = vec_loads && !(variant & 1);
-    constexpr size_t kTmaSmem = 2 * static_cast<size_t>(kTileElems) * sizeof(T);
+    // The tile ring: 64 KB per CTA (three CTAs per SM) when there are CTAs to spare, 96 KB (two per
+    // SM, more tiles in flight per CTA) when the whole launch fits the GPU at two per SM anyway.
+    constexpr size_t kStage = static_cast<size_t>(kTileElems) * sizeof(T);
+    constexpr size_t kRingMany = 64 * 1024, kRingFew = 96 * 1024;
     auto kernel = use_tma ? topk_slice_kernel<T, 3, true> : topk_slice_kernel<T, 4, false>;
-    const size_t smem = use_tma ? kTmaSmem : 0;
-    if (use_tma && !allow_dynamic_smem(kernel, kTmaSmem))
-        return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", kTmaSmem);
+    if (use_tma && !allow_dynamic_smem(kernel, kRingFew))
+        return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", kRingFew);
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "topk: no device status word");
-    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, smem);
+    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, use_tma ? kRingMany : 0);
     int64_t slices;
-    switch (variant >> 1) {
+    switch ((variant & 0xff) >> 1) {
         case 1: slices = ceil_div(vocab, kTileElems); if (ceil_div(resident, rows) > slices) slices = ceil_div(resident, rows); break;
         case 2: slices = 8; break;
         case 3: slices = 2; break;
@@ -713,16 +725,29 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     int64_t slice_len = ceil_div(ceil_div(vocab, slices), E) * E;
     slices = ceil_div(vocab, slice_len);
     if (rows * slices > INT32_MAX) return fail(ISPORE_ELIMIT, "topk: rows*slices too large");
+    int nstages = 0;
+    size_t smem = 0;
+    if (use_tma) {
+        const bool few = rows * slices <= 2 * static_cast<int64_t>(sm_count());
+        int64_t st_n = static_cast<int64_t>((few ? kRingFew : kRingMany) / kStage);
+        const int64_t tiles = ceil_div(slice_len, kTileElems);
+        if (st_n > tiles) st_n = tiles;  // a short slice needs no more stages than it has tiles
+        if (st_n > kMaxStages) st_n = kMaxStages;
+        if (st_n < 2) st_n = 2;
+        if (variant >> 8) st_n = variant >> 8;  // tuning builds: stages from the variant's high byte
+        nstages = static_cast<int>(st_n);
+        smem = static_cast<size_t>(nstages) * kStage;
+    }
 
     if (slices == 1) {
         // The slice kernel's sorted list is already the answer.
         launch_chained(kernel, static_cast<int>(rows), kTopkThreads, smem, st, probs, vocab, static_cast<int>(slice_len), 1, K,
-                       final_ids, final_vals, 1, index_offset, vec_loads, status, uniform, temperature, sampled_ids);
+                       final_ids, final_vals, 1, index_offset, vec_loads, nstages, status, uniform, temperature, sampled_ids);
         return check_launch("topk_slice_kernel");
     }
     launch_chained(kernel, static_cast<int>(rows * slices), kTopkThreads, smem, st, probs, vocab,
                    static_cast<int>(slice_len), static_cast<int>(slices), K, scratch_ids, scratch_vals, scratch_slices,
-                   index_offset, vec_loads, status, nullptr, 1.0f, nullptr);
+                   index_offset, vec_loads, nstages, status, nullptr, 1.0f, nullptr);
     if (int rc = check_launch("topk_slice_kernel")) return rc;
     const int64_t row_stride = static_cast<int64_t>(scratch_slices) * K;
     return merge_dispatch<T>(scratch_ids, scratch_vals, rows, static_cast<int32_t>(slices), K, K, row_stride, K,

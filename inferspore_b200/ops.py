@@ -19,6 +19,7 @@ m0dulo/InferSpore); TensorWrapper shapes become tensor shapes.
 """
 from __future__ import annotations
 
+import threading
 from typing import Optional, Sequence
 
 import torch
@@ -99,10 +100,49 @@ def _stream(t: torch.Tensor) -> int:
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+_recording = threading.local()
+
+
 def _call(name: str, ref: torch.Tensor, *args) -> None:
     lib = capi.load()
+    record = getattr(_recording, "calls", None)
+    if record is not None:  # inside prepare(): validated, not launched
+        record.append(PreparedLaunch(getattr(lib, name), args, ref.device))
+        return
     with torch.cuda.device(ref.device):
         capi.check(getattr(lib, name)(*args, _stream(ref)))
+
+
+class PreparedLaunch:
+    """One validated call of the C ABI bound to its buffers: calling it launches on torch's current
+    stream of the tensors' device and does nothing else (no re-validation, no device switch — the
+    tensors' device must be the current one).  The tensors it was prepared with must stay alive and
+    in place, as for a captured CUDA graph."""
+
+    __slots__ = ("fn", "args", "device")
+
+    def __init__(self, fn, args, device):
+        self.fn, self.args, self.device = fn, args, device
+
+    def __call__(self) -> None:
+        rc = self.fn(*self.args, torch.cuda.current_stream(self.device).cuda_stream)
+        if rc != capi.ISPORE_OK:
+            capi.check(rc)
+
+
+def prepare(launcher, *args, **kwargs) -> PreparedLaunch:
+    """Validates launcher(*args, **kwargs) once, without launching, and returns the bound call:
+    for loops over fixed buffers, where per-call argument checks would cost more host time than a
+    short kernel takes on the device."""
+    _recording.calls = []
+    try:
+        launcher(*args, **kwargs)
+        calls = _recording.calls
+    finally:
+        _recording.calls = None
+    if len(calls) != 1:
+        raise RuntimeError("prepare() takes a launcher that makes exactly one C ABI call")
+    return calls[0]
 
 
 def set_programmatic_launch(enable: bool) -> None:

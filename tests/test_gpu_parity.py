@@ -102,6 +102,19 @@ def test_rmsnorm_empty(ops, cuda):
     ops.launchFusedAddBiasResidualRMSNorm(torch.empty_like(x), x, None, torch.ones(128, device=cuda), 1e-6)
 
 
+def test_prepared_launch_is_the_same_call_without_the_checks(ops, rng):
+    x = rng.standard_normal((33, 1024), dtype=np.float32)
+    g = rng.uniform(0.5, 1.5, 1024).astype(np.float32)
+    a, b, dg = dev(x), dev(x), dev(g)
+    ops.launchRMSNorm(a, None, dg, 1e-6)
+    launch = ops.prepare(ops.launchRMSNorm, b, None, dg, 1e-6)
+    assert np.array_equal(host(b), x)  # preparing validates and binds, it does not launch
+    launch()
+    assert np.array_equal(host(a), host(b))
+    with pytest.raises(ValueError):  # the checks run at prepare time
+        ops.prepare(ops.launchRMSNorm, b, None, dev(g[:100]), 1e-6)
+
+
 # ---- embedding -----------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("dtype", [np.float32, np.float16])
