@@ -15,8 +15,8 @@ scaling is strong: total work is fixed as N grows.
 
 Rank 0 prints ONE JSON line.  `value` is rows (tokens) per second of the whole
 job through the chain with inputs resident in HBM (the steps replayed from a
-CUDA graph with programmatic dependent launch; `--no-graph` / `--no-pdl` switch
-either off); `eager` is the same K steps launched one by one with CUDA events
+CUDA graph; `--no-graph` launches them one by one, `--pdl` adds programmatic
+dependent launch); `eager` is the same K steps launched one by one with CUDA events
 around every kernel, which gives `kernels` (rows/s and algorithmic GB/s per
 kernel) and `roofline` (SiLU*up, the kernel that moves the most bytes); `e2e`
 is the chain driven from pinned host buffers with the host<->device copies
@@ -609,7 +609,7 @@ class StatedConfigs:
 
         sweep()
         eager_us = timed_ms(t, sweep, 5) / sets * 1e3
-        graph = capture_graph(t, o, dev, sweep, True)
+        graph = capture_graph(t, o, dev, sweep, False)
         graph.replay()
         graph_us = timed_ms(t, graph.replay, 5) / sets * 1e3
         nbytes = 4 * rows * HIDDEN * 4 + HIDDEN * 4
@@ -649,7 +649,7 @@ class StatedConfigs:
 
         all_layers()
         eager_us = timed_ms(t, all_layers, 5) / layers * 1e3
-        graph = capture_graph(t, o, dev, all_layers, True)
+        graph = capture_graph(t, o, dev, all_layers, False)
         graph.replay()
         graph_us = timed_ms(t, graph.replay, 5) / layers * 1e3
         concat_bytes = 2 * 2 * bs * KV_HEADS * HEAD_SIZE * 2 + 2 * bs * 4
@@ -831,7 +831,7 @@ def run_ours(args) -> dict:
         total_tokens, total_topk_rows = TOTAL_TOKENS, TOPK_ROWS
         _, tok = shard_sequences(total_tokens // SEQ, SEQ, world, rank)
         tokens, topk_rows = tok.size, shard_range(total_topk_rows, world, rank).size
-    use_graph, use_pdl = not args.no_graph, not args.no_pdl
+    use_graph, use_pdl = not args.no_graph, args.pdl
     K, W = args.steps, max(3, args.warmup)
 
     chain = GpuChain(tokens, device, seed=1000 + rank, topk_rows=topk_rows)
@@ -1061,7 +1061,7 @@ def vocab_sharded_leg(torch, dist, ops, device, rank, world, barrier, max_over_r
     # that has nothing to replay.
     graph, graph_ms = None, None
     try:
-        graph = capture_graph(torch, ops, device, whole, True)
+        graph = capture_graph(torch, ops, device, whole, False)
     except Exception as exc:
         print(f"bench: capture of the sharded top-K failed on rank {rank} ({exc})", file=sys.stderr)
     captured = torch.tensor([0 if graph is None else 1], dtype=torch.int32, device=device)
@@ -1148,7 +1148,8 @@ def main() -> int:
                     help="tokens per GPU per step of the host-driven leg (default: this GPU's share of the batch, "
                          "halved until two pinned buffer sets fit the host)")
     ap.add_argument("--no-graph", action="store_true", help="launch the timed steps one by one instead of from a CUDA graph")
-    ap.add_argument("--no-pdl", action="store_true", help="no programmatic dependent launch in the timed steps")
+    ap.add_argument("--pdl", action="store_true",
+                    help="programmatic dependent launch in the timed steps (measured neutral inside a graph; off by default)")
     ap.add_argument("--no-weak", action="store_true", help="N > 1: skip the extra 65,536-tokens-per-GPU (weak scaling) leg")
     ap.add_argument("--e2e-steps", type=int, default=20)
     ap.add_argument("--cpu-tokens", type=int, default=4096, help="tokens per step of the CPU chain sample")

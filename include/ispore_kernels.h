@@ -68,14 +68,15 @@ ISPORE_API ispore_stream_t ispore_get_stream(void);
 /* Programmatic dependent launch, per calling thread (default: off).
  * ref: none — the reference launches every kernel with plain stream order.
  * When on, the library's main kernels are launched with
- * cudaLaunchAttributeProgrammaticStreamSerialization: a kernel may be scheduled
- * while its predecessor on the same stream is still finishing its last CTAs, and
+ * cudaLaunchAttributeProgrammaticStreamSerialization: a kernel's launch may be
+ * processed before its predecessor on the same stream has retired, and the kernel
  * waits on the device (griddepcontrol.wait) until that predecessor has completed
  * and its memory is visible before it touches global memory.  Results are
- * identical; what changes is that launch latency and CTA ramp-up of one kernel
- * overlap the tail of the one before, which matters for chains of short kernels
- * (decode steps, small token shards).  Works for plain launches and inside stream
- * capture.  Only back-to-back kernels of this library overlap; anything else on
+ * identical; what changes is that part of the launch latency of one kernel
+ * overlaps the tail of the one before, which matters for chains of short kernels
+ * launched one by one (decode steps, small token shards: 5 % on an eight-kernel
+ * chain of 20-90 us kernels); inside a CUDA graph it is neutral.  Works for plain
+ * launches and inside stream capture.  Only back-to-back kernels of this library overlap; anything else on
  * the stream (copies, events, other libraries' kernels) orders as usual. */
 ISPORE_API void ispore_set_programmatic_launch(int enable);
 ISPORE_API int ispore_get_programmatic_launch(void);

@@ -32,19 +32,24 @@ inline bool allow_dynamic_smem(Kernel kernel, size_t bytes) {
 }
 
 // ---- programmatic dependent launch ---------------------------------------------
-// A kernel launched through launch_chained() may be scheduled while its predecessor on the
-// stream is still draining its last CTAs (the launch carries
-// cudaLaunchAttributeProgrammaticStreamSerialization when the calling thread has switched that
-// on with ispore_set_programmatic_launch).  Every kernel launched this way starts with
-// chain_begin(): it lets ITS successor be scheduled early in turn and then waits until the
-// predecessor grid has completed and its memory is visible, before the first global access.
-// Launched without the attribute both instructions are no-ops, so the same kernel serves both
-// modes.  The wait is unconditional and precedes every early return, so a grid can only complete
-// after its predecessor has: ordering stays transitive along the stream.
+// A kernel launched through launch_chained() may be scheduled before its predecessor on the
+// stream has fully retired (the launch carries cudaLaunchAttributeProgrammaticStreamSerialization
+// when the calling thread has switched that on with ispore_set_programmatic_launch).  Every kernel
+// launched this way starts with chain_begin(): it waits until the predecessor grid has completed
+// and its memory is visible, before the first global access.  Launched without the attribute the
+// instruction is a no-op, so the same kernel serves both modes.  The wait is unconditional and
+// precedes every early return, so a grid can only complete after its predecessor has: ordering
+// stays transitive along the stream.
+// The successor is released when this grid's CTAs exit (no explicit early trigger).  Measured on
+// B200 over the eight-kernel chain, CUDA-graph replay: an early trigger at the top of every kernel
+// (griddepcontrol.launch_dependents, so that the successor's CTAs take their places during this
+// kernel's last wave and wait there) made the chain 11-12 % SLOWER at 8,192 and at 65,536 tokens
+// (390 -> 437 us, 2.91 -> 3.22 ms); without it the attribute is neutral inside a graph (390 us)
+// and saves 5 % on launches issued one by one at the small size (411 -> 391 us).
 bool programmatic_launch_enabled();  // thread-local, c_api.cu
 
 #ifndef ISPORE_CHAIN_MODE
-#define ISPORE_CHAIN_MODE 0  // experiments: 1 = wait only (the successor is released when this grid's CTAs exit)
+#define ISPORE_CHAIN_MODE 1  // experiments: 0 = also trigger the successor at the top of the kernel
 #endif
 __device__ __forceinline__ void chain_begin() {
     if (ISPORE_CHAIN_MODE == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

@@ -18,9 +18,10 @@
 // the running top-K already sorted without a sorting network.  Every later tile
 // only has to beat the running K-th best: while that is a positive value the
 // test is one integer compare of the thread's maximum (nearly every thread of
-// every later tile holds no survivor and is done after it), survivors are
-// parked behind the running best, and the ranking runs once every few tiles
-// rather than once per tile — a later tile costs one block barrier.
+// every later tile holds no survivor and is done after it); the few survivors
+// are parked behind the running best and ranked before the next tile is
+// touched, so the bar rises as early as possible.  A later tile costs one block
+// barrier, plus one for its ranking when it had survivors.
 // Adversarial tiles (e.g. constant data, where the threshold keeps everything)
 // fall back to an exact radix select over the tile, ties resolved by an
 // index-ordered block scan.  Round 2 (one CTA per row) merges the slices' sorted
@@ -46,8 +47,8 @@ __device__ int g_topk_debug = 0;  // ablation switches, tuning builds only
 
 constexpr int kTopkThreads = 256;  // measured: 512 threads x 16 keys is 1.5x slower (barriers over 16 warps)
 constexpr int kTopkWarps = kTopkThreads / 32;
-constexpr int kElemsPerThread = 16;                          // keys a thread holds per tile
-constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 4096
+constexpr int kElemsPerThread = 32;                          // keys a thread holds per tile
+constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
 constexpr int kMaxStages = 8;                                // tiles of the shared-memory ring
 constexpr int kTileCap = 256;                                // survivors a tile may add on the fast path
 constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + tile survivors
@@ -302,12 +303,10 @@ __device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, in
 }
 
 // TMA: the tiles arrive through the copy engine (cp.async.bulk into a ring of `nstages`
-// shared-memory stages, completion on one mbarrier per stage), requested nstages - 1 tiles ahead:
-// while the first tile is thresholded and ranked — the one long serial step of a row, and one that
-// every CTA of a launch reaches at the same moment — the following tiles are already on their way,
-// so HBM does not go idle.  The registers are filled from shared memory.  Needs the vector-load
-// conditions (16-byte aligned rows, slice length a multiple of the vector).  Without TMA the tile
-// is loaded straight into registers.
+// shared-memory stages, completion on one mbarrier per stage), requested nstages - 1 tiles ahead,
+// so the following tiles are on their way while one is thresholded and ranked.  The registers are
+// filled from shared memory.  Needs the vector-load conditions (16-byte aligned rows, slice length
+// a multiple of the vector).  Without TMA the tile is loaded straight into registers.
 template <typename T, int MIN_BLOCKS, bool TMA>
 __global__ void __launch_bounds__(kTopkThreads, MIN_BLOCKS)
 topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int slices, int K,
@@ -368,13 +367,11 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     int ring_stage = 0;        // stage of the tile worked on
     uint32_t ring_phase = 0;   // parity its barrier completes with
 
-    // `pending` survivors of streamed tiles sit behind the running best, not yet ranked (uniform).
     // Streamed tiles count their survivors in s_push[tile & 3]: the count of tile t is read by
     // everyone after the barrier of tile t+1 while tile t+1 already counts in the next slot, and
     // the slot is cleared again two tiles later, so no thread reads a counter that another is
     // still adding to.
-    int pending = 0;
-    bool streamed_prev = false;  // the previous tile's survivors are parked and not yet counted into `pending`
+    bool streamed_prev = false;  // the previous tile's survivors are parked behind the running best, not yet ranked
     uint32_t thr = 0;
     // A bounded wait on a tile ran out somewhere in the CTA: record it, wait once more for the copy
     // in flight (shared memory must not be released under it) and leave; every thread comes here.
@@ -398,7 +395,6 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         rank_into(cand[cur], nbest, total, K, cand[cur ^ 1]);
         cur ^= 1;
         nbest = total < K ? total : K;
-        pending = 0;
         __syncthreads();
         if (nbest == K) {
             const uint32_t kth = static_cast<uint32_t>(cand[cur][K - 1] >> 32);
@@ -415,18 +411,18 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         rank_pending(K);
     };
 
-    // Counts the survivors the previous (streamed) tile parked behind the running best; ranks when
-    // the next tile's survivors (about K; room for twice that is kept) might no longer fit, and
-    // falls back to the exact selection when the previous tile alone overflowed its room.  Runs at
-    // the top of an iteration, after the barrier that ended the previous one, while no tile is
-    // held in registers.
-    auto settle_previous = [&](int prev_tile_no, bool last) {
+    // Takes in the survivors the previous (streamed) tile parked behind the running best and ranks
+    // them at once: the sooner the K-th best rises, the fewer elements of the following tiles
+    // survive, and the ranking costs (K + survivors) x survivors comparisons — putting it off over
+    // several tiles was measured 5x more expensive than a small ranking per tile.  Falls back to the
+    // exact selection when the tile alone overflowed its room.  Runs at the top of an iteration,
+    // after the barrier that ended the previous one, while no tile is held in registers.
+    auto settle_previous = [&](int prev_tile_no) {
         const int added = s_push[prev_tile_no & 3];
-        if (pending + added > kTileCap) {
-            overflow_tile(prev_tile_no * kTileElems, pending);
-        } else {
-            pending += added;
-            if (pending > 0 && (last || pending + 2 * K > kTileCap)) rank_pending(pending);
+        if (added > kTileCap) {
+            overflow_tile(prev_tile_no * kTileElems, 0);
+        } else if (added > 0) {
+            rank_pending(added);
         }
     };
 
@@ -436,7 +432,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         // with a barrier: the copy can start now and fly while this tile is worked on.
         issue_next(tile_no);
         if (tid == 0) s_push[(tile_no + 1) & 3] = 0;  // that slot was read for the last time two tiles ago
-        if (streamed_prev) settle_previous(tile_no - 1, false);
+        if (streamed_prev) settle_previous(tile_no - 1);
         streamed_prev = false;
 
         int bits[kElemsPerThread];
@@ -452,16 +448,29 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             }
             pmax = INT_MIN;
             const uint4* stage_v = reinterpret_cast<const uint4*>(stage);
+            if (tile_begin + kTileElems <= n) {  // a whole tile (uniform): no per-vector guards
 #pragma unroll
-            for (int k = 0; k < kVecs; ++k) {
-                const int v = tid + k * kTopkThreads;
-                const bool ok = tile_begin + v * E < n;
-                Unpacked<T> x;
-                if (ok) unpack(stage_v[v], x);
+                for (int k = 0; k < kVecs; ++k) {
+                    Unpacked<T> x;
+                    unpack(stage_v[tid + k * kTopkThreads], x);
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    bits[k * E + e] = ok ? __float_as_int(x.v[e]) : INT_MIN;
-                    pmax = max(pmax, bits[k * E + e]);
+                    for (int e = 0; e < E; ++e) {
+                        bits[k * E + e] = __float_as_int(x.v[e]);
+                        pmax = max(pmax, bits[k * E + e]);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int k = 0; k < kVecs; ++k) {
+                    const int v = tid + k * kTopkThreads;
+                    const bool ok = tile_begin + v * E < n;
+                    Unpacked<T> x;
+                    if (ok) unpack(stage_v[v], x);
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        bits[k * E + e] = ok ? __float_as_int(x.v[e]) : INT_MIN;
+                        pmax = max(pmax, bits[k * E + e]);
+                    }
                 }
             }
         } else {
@@ -531,13 +540,13 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
 
         // Streamed tile: K entries are held, an element only matters if it beats the current K-th
         // best outright (on a tie the earlier index, already held, wins).  Survivors are parked
-        // behind the running best and ranked every few tiles, not per tile.
-        push_survivors(thr, pending, &s_push[tile_no & 3]);
+        // behind the running best and ranked at the top of the next iteration.
+        push_survivors(thr, 0, &s_push[tile_no & 3]);
         streamed_prev = true;
         __syncthreads();  // the tile has been read and its survivors counted by every thread
         if (TMA && s_timeout) return timed_out(tile_no);
     }
-    if (streamed_prev) settle_previous(tile_no - 1, true);
+    if (streamed_prev) settle_previous(tile_no - 1);
 
     int32_t* out_ids = out_ids_base + (row * out_lists + slice) * K;
     T* out_vals = out_vals_base + (row * out_lists + slice) * K;
@@ -700,10 +709,10 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
     const int vec_loads = (vocab % E == 0) && aligned16(probs);
     const bool use_tma = vec_loads && !(variant & 1);
-    // The tile ring: 64 KB per CTA (three CTAs per SM) when there are CTAs to spare, 96 KB (two per
-    // SM, more tiles in flight per CTA) when the whole launch fits the GPU at two per SM anyway.
+    // The tile ring: 64 KB per CTA, three CTAs per SM.  (Measured: deeper rings at fewer CTAs per SM
+    // are slower at every row count — the kernel is bound by the work per tile, not by waiting for tiles.)
     constexpr size_t kStage = static_cast<size_t>(kTileElems) * sizeof(T);
-    constexpr size_t kRingMany = 64 * 1024, kRingFew = 96 * 1024;
+    constexpr size_t kRingMany = 64 * 1024, kRingFew = 64 * 1024;
     auto kernel = use_tma ? topk_slice_kernel<T, 3, true> : topk_slice_kernel<T, 4, false>;
     if (use_tma && !allow_dynamic_smem(kernel, kRingFew))
         return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", kRingFew);
