@@ -53,7 +53,7 @@ bool programmatic_launch_enabled();  // thread-local, c_api.cu
 #endif
 __device__ __forceinline__ void chain_begin() {
     if (ISPORE_CHAIN_MODE == 0) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
-    asm volatile("griddepcontrol.wait;" ::: "memory");
+    if (ISPORE_CHAIN_MODE != 2) asm volatile("griddepcontrol.wait;" ::: "memory");  // 2: nothing (measurement only)
 }
 
 // cluster_x > 1 launches the grid as thread-block clusters of that many CTAs along x (gridDim.x must

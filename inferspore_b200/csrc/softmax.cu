@@ -14,7 +14,6 @@
 // rows one after the other.  A row lives in registers between the max, the sum
 // and the store, so qk is read once and the score written once; the index
 // arithmetic (one 32-bit division) is paid per group, not per row.
-#include <cooperative_groups.h>
 #include <float.h>
 
 #include "common.cuh"
@@ -346,129 +345,6 @@ softmax_row_scalar_kernel(T* __restrict__ score, const T* __restrict__ qk, const
     }
 }
 
-// Few, very long rows (8 K elements and more): one CTA per row holds so much of the row per
-// thread that only one or two CTAs fit an SM, and their load / reduce / store phases no longer
-// overlap.  Here a row is split over a thread-block cluster of CL CTAs of 128 threads, each
-// keeping a segment of VPT*128 vectors in registers — the shape that runs at the copy rate on
-// rows of 4096 — and the row's maximum and sum are exchanged through distributed shared
-// memory: every CTA stores its partial result into each peer's shared memory (remote stores),
-// one cluster barrier makes them visible, and each CTA combines the CL partials locally in the
-// same order.  Two cluster barriers per row; after the second nobody touches remote memory, so a
-// CTA may exit at once.
-template <typename T, int VPT, int THREADS, int CL, bool CAUSAL>
-__global__ void __launch_bounds__(THREADS)
-softmax_row_over_cluster_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
-                                const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
-                                uint32_t total_rows, int q_len, int row_vecs, InvariantDivisor by_q_len,
-                                InvariantDivisor by_heads, float scale) {
-    namespace cg = cooperative_groups;
-    constexpr int E = VecTraits<T>::kElems;
-    constexpr int kWarps = THREADS / 32;
-    using Exp = ExpPolicy<T>;
-    __shared__ float warp_red[2][kWarps];
-    __shared__ float peer_max[CL], peer_sum[CL];  // written by the CTAs of the cluster, one slot each
-    chain_begin();
-    cg::cluster_group cluster = cg::this_cluster();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const unsigned seg = cluster.block_rank();
-    const uint32_t r = blockIdx.x / CL;  // grid = rows * CL exactly
-    const uint32_t bh = by_q_len.divide(r);
-    const int qi = static_cast<int>(r - bh * static_cast<uint32_t>(q_len));
-    const int b = static_cast<int>(by_heads.divide(bh));
-    const float a = scale * Exp::kPrescale;
-    const float neg = -10000.0f * Exp::kPrescale;
-    const int seg_vecs = VPT * THREADS;
-    const int v0 = static_cast<int>(seg) * seg_vecs;  // first vector of this CTA's segment
-    const uint4* qrow = reinterpret_cast<const uint4*>(qk) + static_cast<int64_t>(r) * row_vecs + v0;
-    uint4* orow = reinterpret_cast<uint4*>(score) + static_cast<int64_t>(r) * row_vecs + v0;
-    const uint4* mrow = reinterpret_cast<const uint4*>(mask) + (static_cast<int64_t>(b) * q_len + qi) * row_vecs + v0;
-    const int left = row_vecs - v0;  // vectors of the row from v0 on (may be <= 0 for a trailing CTA)
-
-    uint4 q_raw[VPT], m_raw[VPT];
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        if (v < left) {
-            q_raw[i] = ld_stream(qrow + v);
-            if (!CAUSAL) m_raw[i] = ld_keep(mrow + v);
-        }
-    }
-    int lo = 0, hi = -1;
-    if (CAUSAL) {
-        const int qlen = __ldg(q_lens + b), klen = __ldg(k_lens + b);
-        lo = klen - qlen;
-        hi = qi < qlen ? min(klen - 1, qi + lo) : -1;
-    }
-    Unpacked<T> z[VPT];
-    float mx = FLT_MIN * Exp::kPrescale;
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        if (v < left) {
-            unpack(q_raw[i], z[i]);
-            if (CAUSAL) {
-                const int k0 = (v0 + v) * E;
-#pragma unroll
-                for (int e = 0; e < E; ++e) z[i].v[e] = fmaf(a, z[i].v[e], (k0 + e >= lo && k0 + e <= hi) ? 0.0f : neg);
-            } else {
-                Unpacked<T> m;
-                unpack(m_raw[i], m);
-#pragma unroll
-                for (int e = 0; e < E; ++e) z[i].v[e] = fmaf(a, z[i].v[e], fmaf(m.v[e], -neg, neg));
-            }
-#pragma unroll
-            for (int e = 0; e < E; ++e) mx = fmaxf(mx, z[i].v[e]);
-        }
-    }
-    mx = warp_max(mx);
-    if (lane == 0) warp_red[0][warp] = mx;
-    __syncthreads();
-    if (tid < CL) {  // thread p hands this CTA's maximum to CTA p
-        float m = warp_red[0][0];
-#pragma unroll
-        for (int w = 1; w < kWarps; ++w) m = fmaxf(m, warp_red[0][w]);
-        *cluster.map_shared_rank(&peer_max[seg], tid) = m;
-    }
-    cluster.sync();
-    mx = peer_max[0];
-#pragma unroll
-    for (int p = 1; p < CL; ++p) mx = fmaxf(mx, peer_max[p]);
-    float sum = 0.f;
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        if (tid + i * THREADS < left) {
-#pragma unroll
-            for (int e = 0; e < E; ++e) {
-                z[i].v[e] = Exp::exp_diff(z[i].v[e], mx);
-                sum += z[i].v[e];
-            }
-        }
-    }
-    sum = warp_sum(sum);
-    if (lane == 0) warp_red[1][warp] = sum;
-    __syncthreads();
-    if (tid < CL) {
-        float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) t += warp_red[1][w];
-        *cluster.map_shared_rank(&peer_sum[seg], tid) = t;
-    }
-    cluster.sync();
-    sum = 0.f;
-#pragma unroll
-    for (int p = 0; p < CL; ++p) sum += peer_sum[p];  // the same order in every CTA of the cluster
-    const float inv = 1.0f / (sum + 1e-6f);
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        if (v < left) {
-#pragma unroll
-            for (int e = 0; e < E; ++e) z[i].v[e] *= inv;
-            st_stream(orow + v, pack(z[i]));
-        }
-    }
-}
-
 // Where the 0/1 mask comes from: a [batch, q_len, k_len] tensor (the reference's interface) or
 // the two length arrays it would have been built from.
 template <typename T>
@@ -779,30 +655,6 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
         prefer_rows = CAUSAL ? (k_len > 512 && k_len != 4096) : (k_len > 512 && !(pow2 && k_len >= 4096));
     else
         prefer_rows = CAUSAL ? k_len >= 288 : (k_len > 256 && !pow2 && !(k_len >= 1000 && k_len <= 2048));
-    // Rows of 1024 vectors and more (8 K halves, 4 K floats): split over a cluster, 512 vectors per CTA.
-    if (vec_ok && vecs >= 1024 && vecs <= 4096 && total_rows < (1ll << 28) && tune(kTuneSoftmax, 0) != 7) {
-        constexpr int VPT = 4, THREADS = 128;
-        const int cl = static_cast<int>(ceil_div(vecs, VPT * THREADS));  // 2 .. 8
-#define ISPORE_SOFTMAX_CLUSTER(CL)                                                                                        \
-    do {                                                                                                                  \
-        launch_chained_cluster(softmax_row_over_cluster_kernel<T, VPT, THREADS, CL, CAUSAL>,                              \
-                               static_cast<unsigned>(total_rows * CL), THREADS, 0, st, CL, score, qk, ms.mask, ms.q_lens, \
-                               ms.k_lens, static_cast<uint32_t>(total_rows), static_cast<int>(q_len),                     \
-                               static_cast<int>(vecs), InvariantDivisor(static_cast<uint32_t>(q_len)),                    \
-                               InvariantDivisor(static_cast<uint32_t>(heads)), scale);                                    \
-        return check_launch("softmax_row_over_cluster_kernel");                                                           \
-    } while (0)
-        switch (cl) {
-            case 2: ISPORE_SOFTMAX_CLUSTER(2);
-            case 3: ISPORE_SOFTMAX_CLUSTER(3);
-            case 4: ISPORE_SOFTMAX_CLUSTER(4);
-            case 5: ISPORE_SOFTMAX_CLUSTER(5);
-            case 6: ISPORE_SOFTMAX_CLUSTER(6);
-            case 7: ISPORE_SOFTMAX_CLUSTER(7);
-            default: ISPORE_SOFTMAX_CLUSTER(8);
-        }
-#undef ISPORE_SOFTMAX_CLUSTER
-    }
     if (vec_ok && !(rows_ok && prefer_rows)) {
         const int rv = static_cast<int>(vecs);
 #define ISPORE_SOFTMAX(VPT, GROUP, THREADS, HG, MINB) \

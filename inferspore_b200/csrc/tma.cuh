@@ -35,8 +35,27 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t by
                  : "memory");
 }
 
+// One try: true when the phase with the given parity has completed.  A thread that finds it
+// incomplete is parked by the hardware until the phase completes or, at the latest, until the
+// suspend-time hint (nanoseconds) has passed — without the hint the parking time is a short
+// system default and a CTA of waiting threads keeps re-issuing the instruction, which takes issue
+// slots from the warps of other CTAs on the SM that have work to do.
+#ifndef ISPORE_MBAR_HINT_NS
+#define ISPORE_MBAR_HINT_NS 1000000  // 1 ms per try; 0 = no hint
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t done;
+#if ISPORE_MBAR_HINT_NS > 0
+    asm volatile(
+        "{\n"
+        "  .reg .pred p;\n"
+        "  mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+        "  selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_addr(bar)), "r"(parity), "r"(static_cast<uint32_t>(ISPORE_MBAR_HINT_NS))
+        : "memory");
+#else
     asm volatile(
         "{\n"
         "  .reg .pred p;\n"
@@ -46,13 +65,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(done)
         : "r"(smem_addr(bar)), "r"(parity)
         : "memory");
+#endif
     return done != 0;
 }
 
-// Bounded wait for the phase with the given parity.  try_wait itself suspends the thread for a
-// hardware-defined slice, so kMaxTries of them is on the order of a second, far beyond any
-// legitimate DRAM latency.
+// Bounded wait for the phase with the given parity: kMaxTries parked tries add up to about a
+// second (with the 1 ms hint; the un-hinted default parks for far shorter, hence the larger
+// count), far beyond any legitimate DRAM latency.
+#if ISPORE_MBAR_HINT_NS > 0
+constexpr uint32_t kMaxTries = 1024;
+#else
 constexpr uint32_t kMaxTries = 1u << 20;
+#endif
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
     for (uint32_t i = 0; i < kMaxTries; ++i)
         if (mbar_try_wait(bar, parity)) return true;

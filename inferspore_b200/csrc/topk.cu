@@ -125,17 +125,18 @@ __device__ __forceinline__ void rank_into(const unsigned long long* in, int nsor
     }
 }
 
-// A tile lives in registers as the raw fp32 bit patterns of its 32 elements per thread, viewed
-// as signed ints; element e of vector k of thread t is slice element
-// (tile_begin + (t + k*256)*E + e).  Slots beyond the slice hold INT_MIN.
-// For non-negative floats (NaNs included) signed-int order of the bits IS the output order, so
-// as long as the threshold is a positive float the per-element test is one integer compare on
-// the raw bits and nothing is converted.  `pmax` is the signed-int maximum of the thread's slots:
-// a real element of the thread (the true maximum whenever the thread holds a non-negative
-// value), which is all the threshold derivation needs.
+// A thread looks at 32 elements of a tile, as kElemsPerThread / E groups of E consecutive ones
+// (one 128-bit vector each): group k of thread t is vector (t + k*256) of the tile.  It keeps
+// only the maximum of every group, as raw fp32 bit patterns viewed as signed ints, and their
+// maximum pmax; a slot beyond the slice counts as INT_MIN.  For non-negative floats (NaNs
+// included) signed-int order of the bits IS the output order, so as long as the threshold is a
+// positive float "does this group hold a survivor" is one integer compare, and only the (rare)
+// groups that do are read again — from the shared-memory stage or the cache — to be pushed.
+// pmax is a real element of the thread (the true maximum whenever the thread holds a
+// non-negative value), which is all the threshold derivation of the first tile needs.
 template <typename T>
-__device__ __forceinline__ void load_tile_bits(const T* src, int n, int tile_begin, bool vec_loads,
-                                               int (&bits)[kElemsPerThread], int& pmax) {
+__device__ __forceinline__ void group_maxima_from_global(const T* src, int n, int tile_begin, bool vec_loads,
+                                                         int (&gmax)[kElemsPerThread / VecTraits<T>::kElems], int& pmax) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int kVecs = kElemsPerThread / E;
     pmax = INT_MIN;
@@ -151,25 +152,26 @@ __device__ __forceinline__ void load_tile_bits(const T* src, int n, int tile_beg
 #pragma unroll
         for (int k = 0; k < kVecs; ++k) {
             const int v = threadIdx.x + k * kTopkThreads;
-            const bool ok = tile_begin + v * E < n;
-            Unpacked<T> x;
-            if (ok) unpack(raw[k], x);
+            gmax[k] = INT_MIN;
+            if (tile_begin + v * E < n) {
+                Unpacked<T> x;
+                unpack(raw[k], x);
 #pragma unroll
-            for (int e = 0; e < E; ++e) {
-                bits[k * E + e] = ok ? __float_as_int(x.v[e]) : INT_MIN;
-                pmax = max(pmax, bits[k * E + e]);
+                for (int e = 0; e < E; ++e) gmax[k] = max(gmax[k], __float_as_int(x.v[e]));
             }
+            pmax = max(pmax, gmax[k]);
         }
     } else {
 #pragma unroll
         for (int k = 0; k < kVecs; ++k) {
             const int v = threadIdx.x + k * kTopkThreads;
+            gmax[k] = INT_MIN;
 #pragma unroll
             for (int e = 0; e < E; ++e) {
                 const int i = tile_begin + v * E + e;
-                bits[k * E + e] = i < n ? __float_as_int(to_float<T>(src[i])) : INT_MIN;
-                pmax = max(pmax, bits[k * E + e]);
+                if (i < n) gmax[k] = max(gmax[k], __float_as_int(to_float<T>(src[i])));
             }
+            pmax = max(pmax, gmax[k]);
         }
     }
 }
@@ -254,46 +256,33 @@ __device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int
     }
 }
 
-// exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.  One warp.  The sums
-// are the sequential fp32 sums of the definition (p_0 + p_1 + ... in index order): every lane
-// carries the same running sum, fed one term at a time by a shuffle from the lane that holds
-// the term, so there is no dependent chain of shared-memory loads; lane i % 32 keeps the running
-// sum after term i.  The pick is the smallest valid i whose running sum reaches u * total.
+// exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.  One warp; `cum` is K
+// floats of shared memory.  The lanes evaluate the exponentials, lane 0 turns them into running
+// sums one after the other — the sequential fp32 sums of the definition, p_0 + p_1 + ... in index
+// order (an empty slot contributes an exact zero) — and the lanes then look for the smallest valid
+// index whose running sum reaches u * total.
 template <typename T>
 __device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, int K, float u,
-                                           float temperature, int32_t* out) {
-    constexpr int kSlots = ISPORE_TOPK_MAX_K / 32;
+                                           float temperature, float* cum, int32_t* out) {
     const int lane = threadIdx.x & 31;
     const float v0 = to_float<T>(vals[0]);
-    float p[kSlots], cum[kSlots];
-    int32_t id[kSlots];
-#pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-        const int i = s * 32 + lane;
-        id[s] = i < K ? ids[i] : -1;
-        p[s] = id[s] < 0 ? 0.f : expf((to_float<T>(vals[i < K ? i : 0]) - v0) / temperature);
-        cum[s] = 0.f;
-    }
-    float run = 0.f;
-#pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-        if (s * 32 < K) {  // uniform
-            const unsigned valid = __ballot_sync(0xffffffffu, id[s] >= 0);
-            for (int l = 0; l < 32 && s * 32 + l < K; ++l) {
-                const float term = __shfl_sync(0xffffffffu, p[s], l);
-                if ((valid >> l) & 1u) run += term;  // empty slots are skipped, not added as zeros
-                if (l == lane) cum[s] = run;
-            }
+    for (int i = lane; i < K; i += 32)
+        cum[i] = ids[i] < 0 ? 0.f : expf((to_float<T>(vals[i]) - v0) / temperature);
+    __syncwarp();
+    if (lane == 0) {
+        float run = 0.f;
+        for (int i = 0; i < K; ++i) {
+            run += cum[i];
+            cum[i] = run;
         }
     }
-    const float target = u * run;
+    __syncwarp();
+    const float target = u * cum[K - 1];
     int pick = INT_MAX, last = -1;
-#pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-        const int i = s * 32 + lane;
-        if (i < K && id[s] >= 0) {
+    for (int i = lane; i < K; i += 32) {
+        if (ids[i] >= 0) {
             last = i;
-            if (cum[s] >= target && i < pick) pick = i;
+            if (cum[i] >= target && i < pick) pick = i;
         }
     }
     pick = __reduce_min_sync(0xffffffffu, pick);
@@ -341,6 +330,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     int cur = 0;    // which cand[] buffer holds the running best
     int nbest = 0;  // entries of the running best (sorted, best first)
     const int q = (K + kTopkWarps - 1) / kTopkWarps;
+    const int ntiles = (n + kTileElems - 1) / kTileElems;
 
     constexpr uint32_t kStageBytes = kTileElems * sizeof(T);
     auto tile_bytes = [&](int tile_begin) {
@@ -353,7 +343,6 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         tma::mbar_arrive_expect_tx(&full[stage], tile_bytes(tile_begin));
         tma::load(stage_raw + static_cast<size_t>(stage) * kStageBytes, src + tile_begin, tile_bytes(tile_begin), &full[stage]);
     };
-    const int ntiles = (n + kTileElems - 1) / kTileElems;
     if (TMA) {
         if (tid == 0) {
             for (int st = 0; st < nstages; ++st) tma::mbar_init(&full[st], 1);
@@ -413,10 +402,12 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
 
     // Takes in the survivors the previous (streamed) tile parked behind the running best and ranks
     // them at once: the sooner the K-th best rises, the fewer elements of the following tiles
-    // survive, and the ranking costs (K + survivors) x survivors comparisons — putting it off over
-    // several tiles was measured 5x more expensive than a small ranking per tile.  Falls back to the
-    // exact selection when the tile alone overflowed its room.  Runs at the top of an iteration,
-    // after the barrier that ended the previous one, while no tile is held in registers.
+    // survive, and a ranking costs (K + survivors) x survivors comparisons.  Measured and not kept:
+    // parking the survivors of several tiles and ranking them together (5x the comparisons), and
+    // taking a fixed threshold from the first tile with ONE ranking at the end of the row (a row
+    // whose first tile misleads needs a second pass, and with hundreds of rows per launch some row
+    // always does).  A tile that overflowed its room is selected exactly.  Runs at the top of an
+    // iteration, after the barrier that ended the previous one, while no tile is held in registers.
     auto settle_previous = [&](int prev_tile_no) {
         const int added = s_push[prev_tile_no & 3];
         if (added > kTileCap) {
@@ -435,9 +426,10 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         if (streamed_prev) settle_previous(tile_no - 1);
         streamed_prev = false;
 
-        int bits[kElemsPerThread];
+        int gmax[kVecs];
         int pmax;
         const T* stage = reinterpret_cast<const T*>(stage_raw + static_cast<size_t>(ring_stage) * kStageBytes);
+        const uint4* stage_v = reinterpret_cast<const uint4*>(stage);
         if (TMA) {
             // A wait that runs out is recorded here and acted on by the whole CTA after the next
             // barrier (whatever was read meanwhile is discarded).
@@ -447,69 +439,81 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
                 ring_phase ^= 1u;
             }
             pmax = INT_MIN;
-            const uint4* stage_v = reinterpret_cast<const uint4*>(stage);
-            if (tile_begin + kTileElems <= n) {  // a whole tile (uniform): no per-vector guards
+            const bool whole_tile = tile_begin + kTileElems <= n;  // uniform: no per-vector guards then
 #pragma unroll
-                for (int k = 0; k < kVecs; ++k) {
+            for (int k = 0; k < kVecs; ++k) {
+                const int v = tid + k * kTopkThreads;
+                gmax[k] = INT_MIN;
+                if (whole_tile || tile_begin + v * E < n) {
                     Unpacked<T> x;
-                    unpack(stage_v[tid + k * kTopkThreads], x);
+                    unpack(stage_v[v], x);
 #pragma unroll
-                    for (int e = 0; e < E; ++e) {
-                        bits[k * E + e] = __float_as_int(x.v[e]);
-                        pmax = max(pmax, bits[k * E + e]);
-                    }
+                    for (int e = 0; e < E; ++e) gmax[k] = max(gmax[k], __float_as_int(x.v[e]));
                 }
-            } else {
-#pragma unroll
-                for (int k = 0; k < kVecs; ++k) {
-                    const int v = tid + k * kTopkThreads;
-                    const bool ok = tile_begin + v * E < n;
-                    Unpacked<T> x;
-                    if (ok) unpack(stage_v[v], x);
-#pragma unroll
-                    for (int e = 0; e < E; ++e) {
-                        bits[k * E + e] = ok ? __float_as_int(x.v[e]) : INT_MIN;
-                        pmax = max(pmax, bits[k * E + e]);
-                    }
-                }
+                pmax = max(pmax, gmax[k]);
             }
         } else {
-            load_tile_bits<T>(src, n, tile_begin, vec_loads != 0, bits, pmax);
+            group_maxima_from_global<T>(src, n, tile_begin, vec_loads != 0, gmax, pmax);
         }
-        // Slot i of this thread is slice element elem_of(i); a slot is live iff that is < n.
-        auto elem_of = [&](int i) { return tile_begin + (tid + (i / E) * kTopkThreads) * E + (i % E); };
-        // Survivors of this thread: the slots whose key reaches `limit`, pushed behind the running
+        // Survivors of this thread: the elements whose key reaches `limit`, pushed behind the running
         // best from position base + (this thread's share of `counter`), dropped beyond kTileCap
         // (the counter still counts them, which is how the overflow is noticed).
         auto push_survivors = [&](uint32_t limit, int base, int* counter) {
-            uint32_t mask = 0;
-            if (limit > 0x80000000u) {
-                // limit is the key of a positive float: survivors are exactly the slots whose raw
-                // bits, as signed ints, reach its bits (empty slots hold INT_MIN and never do).
-                // pmax is the largest of them, so one compare clears a thread without survivors —
-                // nearly every thread of every tile after the first.
-                const int limit_bits = static_cast<int>(limit & 0x7fffffffu);
-                if (pmax >= limit_bits) {
+            // A positive limit: survivors are exactly the elements whose raw bits, as signed ints,
+            // reach its bits, so pmax clears a thread without survivors in one compare — nearly every
+            // thread of every tile after the first — and the group maxima say which vectors to read
+            // again.  Otherwise every group is read again and compared through the order key.
+            const bool positive = limit > 0x80000000u;
+            const int limit_bits = static_cast<int>(limit & 0x7fffffffu);
+            uint32_t groups = 0;
+            if (!positive) {
+                groups = (1u << kVecs) - 1u;
+            } else if (pmax >= limit_bits) {
 #pragma unroll
-                    for (int i = 0; i < kElemsPerThread; ++i) mask |= (bits[i] >= limit_bits ? 1u : 0u) << i;
-                }
-            } else {
-#pragma unroll
-                for (int i = 0; i < kElemsPerThread; ++i)
-                    mask |= (elem_of(i) < n && order_key(__int_as_float(bits[i])) >= limit ? 1u : 0u) << i;
+                for (int k = 0; k < kVecs; ++k) groups |= (gmax[k] >= limit_bits ? 1u : 0u) << k;
             }
-            if (TOPK_DEBUG(16)) mask = 0;
-            if (mask != 0) {
-                int pos = base + atomicAdd(counter, __popc(mask));
-                unsigned long long* mine = cand[cur] + nbest;
-                while (mask != 0 && pos < kTileCap) {
-                    const int i = __ffs(mask) - 1;
-                    mask &= mask - 1;
-                    const int el = elem_of(i);
-                    // The slot's value is re-read (cache hit) rather than picked out of the register
-                    // array with a run-time index.
-                    const T value = TMA ? stage[el - tile_begin] : src[el];
-                    mine[pos++] = composite(order_key(to_float<T>(value)), static_cast<uint32_t>(begin + el));
+            if (TOPK_DEBUG(16)) groups = 0;
+            unsigned long long* mine = cand[cur] + nbest;
+            while (groups != 0) {
+                const int k = __ffs(groups) - 1;
+                groups &= groups - 1;
+                const int v = tid + k * kTopkThreads;
+                const int el0 = tile_begin + v * E;
+                if (el0 >= n) continue;
+                float val[E];
+                uint32_t live = 0;  // which of the group's elements exist
+                if (TMA || vec_loads) {  // whole vectors only on these paths (n % E == 0)
+                    Unpacked<T> x;
+                    unpack(TMA ? stage_v[v] : ld_keep(reinterpret_cast<const uint4*>(src + tile_begin) + v), x);
+#pragma unroll
+                    for (int e = 0; e < E; ++e) val[e] = x.v[e];
+                    live = (1u << E) - 1u;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        val[e] = 0.f;
+                        if (el0 + e < n) {
+                            val[e] = to_float<T>(src[el0 + e]);
+                            live |= 1u << e;
+                        }
+                    }
+                }
+                uint32_t m = 0;
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    const bool in = positive ? __float_as_int(val[e]) >= limit_bits : order_key(val[e]) >= limit;
+                    m |= (in ? 1u : 0u) << e;
+                }
+                m &= live;
+                if (m != 0) {
+                    int pos = base + atomicAdd(counter, __popc(m));
+#pragma unroll
+                    for (int e = 0; e < E; ++e) {
+                        if ((m >> e) & 1u) {
+                            if (pos < kTileCap) mine[pos] = composite(order_key(val[e]), static_cast<uint32_t>(begin + el0 + e));
+                            ++pos;
+                        }
+                    }
                 }
             }
         };
@@ -518,7 +522,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             // Fewer than K entries are held (the first tile; later ones only in tiny tiles): the
             // threshold is the q-th largest thread representative of every warp, minimum over warps,
             // so that at least K tile elements have key >= threshold; the survivors are ranked at once.
-            const bool any_live = elem_of(0) < n;
+            const bool any_live = tile_begin + tid * E < n;  // the thread's first group exists
             const uint32_t wq = warp_qth_largest(any_live ? order_key(__int_as_float(pmax)) : 0u, q);
             if ((tid & 31) == 0) warp_thr[tid >> 5] = wq;
             if (tid == 0) s_count = 0;
@@ -547,7 +551,6 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         if (TMA && s_timeout) return timed_out(tile_no);
     }
     if (streamed_prev) settle_previous(tile_no - 1);
-
     int32_t* out_ids = out_ids_base + (row * out_lists + slice) * K;
     T* out_vals = out_vals_base + (row * out_lists + slice) * K;
     for (int s = tid; s < K; s += kTopkThreads) {
@@ -565,7 +568,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     if (uniform != nullptr) {
         __syncthreads();  // the list written above is visible to warp 0
         if (tid < 32)
-            sample_row<T>(out_ids, out_vals, K, uniform[row], temperature, sampled_ids + row);
+            sample_row<T>(out_ids, out_vals, K, uniform[row], temperature, reinterpret_cast<float*>(hist), sampled_ids + row);
     }
 }
 
@@ -579,6 +582,7 @@ topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ ca
     unsigned long long* comp = reinterpret_cast<unsigned long long*>(smem_raw);  // [lists*K]
     __shared__ int32_t fin_ids[ISPORE_TOPK_MAX_K];
     __shared__ T fin_vals[ISPORE_TOPK_MAX_K];
+    __shared__ float p_smem[ISPORE_TOPK_MAX_K];
     chain_begin();
 
     const int tid = threadIdx.x;
@@ -631,7 +635,7 @@ topk_merge_kernel(const int32_t* __restrict__ cand_ids, const T* __restrict__ ca
         final_vals[row * K + s] = fin_vals[s];
     }
     if (uniform != nullptr && tid < 32)
-        sample_row<T>(fin_ids, fin_vals, K, uniform[row], temperature, sampled_ids + row);
+        sample_row<T>(fin_ids, fin_vals, K, uniform[row], temperature, p_smem, sampled_ids + row);
 }
 
 template <typename T>
@@ -639,11 +643,12 @@ __global__ void __launch_bounds__(kTopkThreads)
 sampling_kernel(const int32_t* __restrict__ topk_ids, const T* __restrict__ topk_vals,
                 const float* __restrict__ uniform, int32_t* __restrict__ output_ids, int64_t rows,
                 int K, float temperature) {
+    __shared__ float p_smem[kTopkWarps][ISPORE_TOPK_MAX_K];
     chain_begin();
     const int warp = threadIdx.x >> 5;
     const int64_t row = static_cast<int64_t>(blockIdx.x) * kTopkWarps + warp;
     if (row >= rows) return;  // whole warps leave; no block barrier follows
-    sample_row<T>(topk_ids + row * K, topk_vals + row * K, K, uniform[row], temperature, output_ids + row);
+    sample_row<T>(topk_ids + row * K, topk_vals + row * K, K, uniform[row], temperature, p_smem[warp], output_ids + row);
 }
 
 int check_k(const char* who, int32_t K) {

@@ -542,6 +542,27 @@ def test_topk_one_cta_walks_a_long_row(ops, orc, rng, dtype, shape, vocab, K):
     assert np.array_equal(got_v.view(bits), want_v.view(bits))
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+def test_topk_outliers_in_the_first_tile(ops, orc, rng, dtype):
+    """Rows of several tiles first take a threshold from the first tile alone and rank once at the
+    end.  Here the first tile holds 16 huge values, two under each warp (thread t of a CTA looks at
+    the 128-bit vectors t, t + 256, ... of a tile), so that threshold is huge and only those 16
+    elements of the whole row reach it — fewer than K: the row must still come out exact."""
+    rows, vocab, K = 3, 32000, 50
+    x = rng.standard_normal((rows, vocab)).astype(np.float32)
+    E = 4 if dtype == np.float32 else 8
+    for w in range(8):
+        for t in (32 * w, 32 * w + 1):
+            x[:, t * E] = 1000.0 + t  # first element of vector t of the first tile
+    probs = x.astype(dtype)
+    for slices in (1, 8):
+        got_i, got_v, _ = _topk_run(ops, probs, K, slices=slices)
+        want_i, want_v = orc.topk(probs, K)
+        bits = np.uint32 if dtype == np.float32 else np.uint16
+        assert np.array_equal(got_i, want_i)
+        assert np.array_equal(got_v.view(bits), want_v.view(bits))
+
+
 def test_topk_without_scratch(ops, orc, rng):
     probs = (rng.standard_normal((4, 20000), dtype=np.float32))
     f_i = torch.empty((4, 10), dtype=torch.int32, device="cuda:0")
