@@ -56,39 +56,22 @@ __device__ __forceinline__ void chain_begin() {
     if (ISPORE_CHAIN_MODE != 2) asm volatile("griddepcontrol.wait;" ::: "memory");  // 2: nothing (measurement only)
 }
 
-// cluster_x > 1 launches the grid as thread-block clusters of that many CTAs along x (gridDim.x must
-// be a multiple of it); the CTAs of a cluster are co-scheduled and may read each other's shared memory.
 template <typename... KArgs, typename... Args>
-inline void launch_chained_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t dynamic_smem,
-                                   cudaStream_t st, unsigned cluster_x, Args&&... args) {
+inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t dynamic_smem, cudaStream_t st,
+                           Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
     cfg.dynamicSmemBytes = dynamic_smem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[2];
-    unsigned n = 0;
+    cudaLaunchAttribute attr[1];
     if (programmatic_launch_enabled()) {
-        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[n].val.programmaticStreamSerializationAllowed = 1;
-        ++n;
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
     }
-    if (cluster_x > 1) {
-        attr[n].id = cudaLaunchAttributeClusterDimension;
-        attr[n].val.clusterDim.x = cluster_x;
-        attr[n].val.clusterDim.y = 1;
-        attr[n].val.clusterDim.z = 1;
-        ++n;
-    }
-    cfg.attrs = n ? attr : nullptr;
-    cfg.numAttrs = n;
     (void)cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);  // the caller reads the status with check_launch()
-}
-
-template <typename... KArgs, typename... Args>
-inline void launch_chained(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t dynamic_smem, cudaStream_t st,
-                           Args&&... args) {
-    launch_chained_cluster(kernel, grid, block, dynamic_smem, st, 1u, static_cast<Args&&>(args)...);
 }
 
 // Launch-shape experiments: a build with -DISPORE_TUNING exports ispore_tune(key, value)

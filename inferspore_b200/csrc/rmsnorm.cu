@@ -8,7 +8,11 @@
 // r each cross HBM once in and once out.  One row per CTA and as many CTAs as
 // rows (measured faster on B200 than a persistent grid-stride loop); gamma is
 // 8 KB shared by every row and is re-read through L1 for the scaled store.
-#include <cooperative_groups.h>
+// Measured and not kept for few rows (8-64 rows of 4096, fewer CTAs than SMs):
+// a row split over a four-CTA thread-block cluster with the partial sums of
+// squares exchanged through distributed shared memory — 2.5-4.2 us per launch
+// against 2.0-3.1 us for one CTA per row (CUDA-graph replay over inputs larger
+// than L2); the two cluster barriers cost more than the shorter per-CTA copy saves.
 #include <stdint.h>
 
 #include "common.cuh"
@@ -122,126 +126,6 @@ rmsnorm_row_in_regs_kernel(T* __restrict__ x, T* __restrict__ r, const T* __rest
             }
         }
     }
-}
-
-// Few rows (fewer than there are SMs — a decode step, the reference's 64-token unit test): one CTA
-// per row would leave most of the GPU idle and make each busy SM pull a whole row through its own
-// memory pipe.  Here a row is split over a thread-block cluster of CL CTAs: each keeps 1/CL of the
-// row in registers, the CL partial sums of squares are exchanged through distributed shared memory
-// (every CTA reads its peers' partial sums with plain loads after one cluster barrier), and each
-// CTA scales and stores its own part.  A second cluster barrier keeps a CTA's shared memory alive
-// until every peer has read it.
-template <typename T, int VPT, int THREADS, int MODE, int CL>
-__global__ void __launch_bounds__(THREADS)
-rmsnorm_row_over_cluster_kernel(T* __restrict__ x, T* __restrict__ r, const T* __restrict__ bias,
-                                const T* __restrict__ gamma, float eps, int64_t num_tokens, int hidden_vecs,
-                                int hidden) {
-    namespace cg = cooperative_groups;
-    chain_begin();
-    constexpr int kWarps = THREADS / 32;
-    constexpr int E = VecTraits<T>::kElems;
-    constexpr ResidualMode mode = static_cast<ResidualMode>(MODE);
-    __shared__ float warp_part[kWarps];
-    __shared__ float cta_part;
-    cg::cluster_group cluster = cg::this_cluster();
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int part = static_cast<int>(cluster.block_rank());
-    const int64_t row = blockIdx.x / CL;  // grid = rows * CL exactly: every CTA of a cluster has a row
-    const int part_vecs = hidden_vecs / CL;
-    const int v0 = part * part_vecs;
-    uint4* xrow = reinterpret_cast<uint4*>(x) + row * hidden_vecs + v0;
-    uint4* rrow = reinterpret_cast<uint4*>(r) + row * hidden_vecs + v0;
-    const uint4* gamma_v = reinterpret_cast<const uint4*>(gamma) + v0;
-    const uint4* bias_v = reinterpret_cast<const uint4*>(bias) + v0;
-
-    uint4 s_raw[VPT], r_raw[VPT];
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        if (v < part_vecs) {
-            s_raw[i] = ld_stream(xrow + v);
-            if (mode == ResidualMode::kAdd) r_raw[i] = ld_stream(rrow + v);
-        }
-    }
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        if (v < part_vecs) {
-            Unpacked<T> s;
-            unpack(s_raw[i], s);
-            if (mode == ResidualMode::kAdd) {
-                Unpacked<T> rr;
-                unpack(r_raw[i], rr);
-#pragma unroll
-                for (int e = 0; e < E; ++e) s.v[e] += rr.v[e];
-                s_raw[i] = pack(s);  // rounds to the storage type: the new residual
-                st_stream(rrow + v, s_raw[i]);
-                unpack(s_raw[i], s);
-            } else if (mode == ResidualMode::kCopyOut) {
-                st_stream(rrow + v, s_raw[i]);
-            }
-            if (bias != nullptr) {
-                Unpacked<T> bb;
-                unpack(ld_keep(bias_v + v), bb);
-#pragma unroll
-                for (int e = 0; e < E; ++e) s.v[e] += bb.v[e];
-                s_raw[i] = pack(s);
-                unpack(s_raw[i], s);
-            }
-#pragma unroll
-            for (int e = 0; e < E; ++e) acc = fmaf(s.v[e], s.v[e], acc);
-        }
-    }
-    acc = warp_sum(acc);
-    if (lane == 0) warp_part[warp] = acc;
-    __syncthreads();
-    if (tid == 0) {
-        float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) t += warp_part[w];
-        cta_part = t;
-    }
-    cluster.sync();  // every CTA's partial sum is written and visible cluster-wide
-    float total = 0.f;
-#pragma unroll
-    for (int p = 0; p < CL; ++p) total += *cluster.map_shared_rank(&cta_part, p);  // same order in every CTA
-    cluster.sync();  // nobody leaves (and gives up its shared memory) before its peers have read it
-    const float inv = rsqrtf(total / static_cast<float>(hidden) + eps);
-#pragma unroll
-    for (int i = 0; i < VPT; ++i) {
-        const int v = tid + i * THREADS;
-        if (v < part_vecs) {
-            Unpacked<T> s, g;
-            unpack(s_raw[i], s);
-            unpack(ld_keep(gamma_v + v), g);
-#pragma unroll
-            for (int e = 0; e < E; ++e) s.v[e] = (g.v[e] * s.v[e]) * inv;
-            st_stream(xrow + v, pack(s));
-        }
-    }
-}
-
-template <typename T, int VPT, int CL>
-int launch_cluster(T* x, T* r, const T* bias, const T* gamma, float eps, int64_t tokens, int64_t hidden,
-                   ResidualMode mode, cudaStream_t st) {
-    constexpr int THREADS = 128;
-    const int hidden_vecs = static_cast<int>(hidden / VecTraits<T>::kElems);
-    const dim3 grid(static_cast<unsigned>(tokens * CL));
-    switch (mode) {
-        case ResidualMode::kAdd:
-            launch_chained_cluster(rmsnorm_row_over_cluster_kernel<T, VPT, THREADS, 1, CL>, grid, THREADS, 0, st, CL, x, r, bias,
-                                   gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden));
-            break;
-        case ResidualMode::kCopyOut:
-            launch_chained_cluster(rmsnorm_row_over_cluster_kernel<T, VPT, THREADS, 2, CL>, grid, THREADS, 0, st, CL, x, r, bias,
-                                   gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden));
-            break;
-        default:
-            launch_chained_cluster(rmsnorm_row_over_cluster_kernel<T, VPT, THREADS, 0, CL>, grid, THREADS, 0, st, CL, x, r, bias,
-                                   gamma, eps, tokens, hidden_vecs, static_cast<int>(hidden));
-    }
-    return check_launch("rmsnorm_row_over_cluster_kernel");
 }
 
 // Any hidden size / any alignment: scalar accesses, the row is re-read from
@@ -363,17 +247,6 @@ int rmsnorm_dispatch(T* x, T* r, const T* bias, const T* gamma, float eps, int64
     // speed; with two input streams (x and the residual) 256-thread CTAs with 2 vectors
     // per thread, 4 CTAs per SM, do.  Wider rows scale the CTA, not the per-thread count.
     const bool one_stream = mode == ResidualMode::kNone;
-    // Fewer rows than half the SMs and rows of at least 8 KB: each row is split over a cluster of
-    // four CTAs.  The sum of squares is then taken in another order than in the one-CTA kernel, so
-    // the two agree to rounding (1e-7 relative), not bit for bit.
-    const bool clusters = tune(kTuneRmsnorm, 100) >= 100;  // tuning builds: any value below 100 switches them off
-    if (vec_ok && clusters && tokens * 2 <= sm_count() && vecs % 4 == 0 && vecs * 16 >= 8192 && vecs / 4 <= 1024) {
-        const int64_t per_cta = vecs / 4;
-        if (per_cta <= 128) return launch_cluster<T, 1, 4>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-        if (per_cta <= 256) return launch_cluster<T, 2, 4>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-        if (per_cta <= 512) return launch_cluster<T, 4, 4>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-        return launch_cluster<T, 8, 4>(x, r, bias, gamma, eps, tokens, hidden, mode, st);
-    }
 #define ISPORE_NORM(VPT, THREADS, BLOCKS) \
     return launch_regs<T, VPT, THREADS, BLOCKS>(x, r, bias, gamma, eps, tokens, hidden, mode, st)
     // Rows that match none of the fixed shapes below exactly (5120, 2560, 6144, 7168, 4104 ... at
