@@ -40,9 +40,12 @@ namespace {
 
 #ifdef ISPORE_TUNING
 __device__ int g_topk_debug = 0;  // ablation switches, tuning builds only
+__device__ long long g_topk_ts[64];  // clock64() of CTA 0 at marked points, tuning builds only
 #define TOPK_DEBUG(bit) (g_topk_debug & (bit))
+#define TOPK_MARK(i) do { if (blockIdx.x == 0 && threadIdx.x == 0 && (i) < 64) g_topk_ts[i] = clock64(); } while (0)
 #else
 #define TOPK_DEBUG(bit) false
+#define TOPK_MARK(i) do { } while (0)
 #endif
 
 constexpr int kTopkThreads = 256;  // measured: 512 threads x 16 keys is 1.5x slower (barriers over 16 warps)
@@ -75,16 +78,19 @@ __device__ __forceinline__ __half neg_inf<__half>() {
     return __ushort_as_half(0xFC00u);
 }
 
-// q-th largest (1-based, q <= 32) of the 32 lane values: q rounds of a hardware
-// max-reduction, retiring one holder of the maximum per round.
-__device__ __forceinline__ uint32_t warp_qth_largest(uint32_t v, int q) {
+// The q largest (q <= 32) of the 32 lane values, best first, to out[0..q): q rounds of a hardware
+// max-reduction, retiring one holder of the maximum per round; 0 where fewer than q lanes are
+// non-empty.  Returns the q-th largest.
+__device__ __forceinline__ uint32_t warp_top_q(uint32_t v, int q, uint32_t* out) {
     const int lane = threadIdx.x & 31;
     uint32_t m = 0;
     for (int i = 0; i < q; ++i) {
         m = __reduce_max_sync(0xffffffffu, v);
-        if (m == 0) break;  // fewer than q non-empty lanes: the threshold keeps everything
-        const uint32_t holders = __ballot_sync(0xffffffffu, v == m);
-        if (lane == __ffs(holders) - 1) v = 0;
+        if (lane == 0) out[i] = m;
+        if (m != 0) {  // uniform
+            const uint32_t holders = __ballot_sync(0xffffffffu, v == m);
+            if (lane == __ffs(holders) - 1) v = 0;
+        }
     }
     return m;
 }
@@ -107,11 +113,14 @@ __device__ __forceinline__ int count_greater(const unsigned long long* list, int
 // (P a power of two) so that short lists still use the whole CTA.
 __device__ __forceinline__ void rank_into(const unsigned long long* in, int nsorted, int total, int K,
                                           unsigned long long* out) {
-    int P = 1;
-    while (P < 32 && total * (P * 2) <= kTopkThreads) P *= 2;
+    int P = 1, shift = 0;
+    while (P < 32 && total * (P * 2) <= kTopkThreads) {
+        P *= 2;
+        ++shift;
+    }
     const int part = threadIdx.x & (P - 1);
-    for (int c0 = 0; c0 < total; c0 += kTopkThreads / P) {
-        const int c = c0 + threadIdx.x / P;
+    for (int c0 = 0; c0 < total; c0 += kTopkThreads >> shift) {
+        const int c = c0 + (threadIdx.x >> shift);
         const bool live = c < total;
         const unsigned long long mine = live ? in[c] : 0ull;
         int rank = 0;
@@ -315,6 +324,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     __shared__ int s_digit, s_need;
     __shared__ int warp_cnt[kTopkWarps];
     chain_begin();
+    TOPK_MARK(0);
 
     const int tid = threadIdx.x;
     const int64_t row = blockIdx.x / slices;
@@ -324,6 +334,8 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     if (n64 > slice_len) n64 = slice_len;
     const int n = n64 > 0 ? static_cast<int>(n64) : 0;
     const T* src = probs + row * vocab + begin;
+    // (requested now, needed at the very end: its DRAM latency would otherwise sit on the row's critical path)
+    const float u_row = (uniform != nullptr && tid < 32) ? __ldg(uniform + row) : 0.f;
 
     if (tid < 4) s_push[tid] = 0;  // visible before its first use: every tile kind has a barrier before the next tile
 
@@ -345,13 +357,14 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     };
     if (TMA) {
         if (tid == 0) {
+            // The first copies leave before the other threads have even arrived: the wait for the
+            // first tile is the longest stall of a row.
             for (int st = 0; st < nstages; ++st) tma::mbar_init(&full[st], 1);
             tma::fence_mbar_init();
             s_timeout = 0;
-        }
-        __syncthreads();
-        if (tid == 0)
             for (int tile = 0; tile < nstages - 1 && tile < ntiles; ++tile) issue_tile(tile, tile);
+        }
+        __syncthreads();  // the barriers' initialisation is visible to every thread that will wait on them
     }
     int ring_stage = 0;        // stage of the tile worked on
     uint32_t ring_phase = 0;   // parity its barrier completes with
@@ -421,10 +434,12 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     for (int tile_begin = 0; tile_begin < n; tile_begin += kTileElems, ++tile_no) {
         // The stage the next tile goes to was last read during the previous iteration, which ended
         // with a barrier: the copy can start now and fly while this tile is worked on.
+        TOPK_MARK(1 + tile_no * 6);  // top of the iteration
         issue_next(tile_no);
         if (tid == 0) s_push[(tile_no + 1) & 3] = 0;  // that slot was read for the last time two tiles ago
         if (streamed_prev) settle_previous(tile_no - 1);
         streamed_prev = false;
+        TOPK_MARK(2 + tile_no * 6);  // previous tile settled
 
         int gmax[kVecs];
         int pmax;
@@ -455,6 +470,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         } else {
             group_maxima_from_global<T>(src, n, tile_begin, vec_loads != 0, gmax, pmax);
         }
+        TOPK_MARK(3 + tile_no * 6);  // tile landed and read
         // Survivors of this thread: the elements whose key reaches `limit`, pushed behind the running
         // best from position base + (this thread's share of `counter`), dropped beyond kTileCap
         // (the counter still counts them, which is how the overflow is noticed).
@@ -519,26 +535,49 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         };
 
         if (nbest < K) {
-            // Fewer than K entries are held (the first tile; later ones only in tiny tiles): the
-            // threshold is the q-th largest thread representative of every warp, minimum over warps,
-            // so that at least K tile elements have key >= threshold; the survivors are ranked at once.
+            // Fewer than K entries are held (the first tile; later ones only in tiny tiles).  Every warp
+            // contributes its q = ceil(K / 8) largest thread representatives: 8q distinct elements of
+            // the tile, of which the K-th largest is the threshold — at least K tile elements have a
+            // key >= it, and it sits far higher than the smallest of the 8q (the q-th best of the
+            // weakest warp): 65 instead of 97 survivors on average for K = 50, and the ranking that
+            // follows costs survivors squared.  The survivors are ranked at once.
             const bool any_live = tile_begin + tid * E < n;  // the thread's first group exists
-            const uint32_t wq = warp_qth_largest(any_live ? order_key(__int_as_float(pmax)) : 0u, q);
+            uint32_t* reps = reinterpret_cast<uint32_t*>(hist);  // [8][q] best first per warp
+            const uint32_t wq = warp_top_q(any_live ? order_key(__int_as_float(pmax)) : 0u, q, reps + (tid >> 5) * q);
             if ((tid & 31) == 0) warp_thr[tid >> 5] = wq;
             if (tid == 0) s_count = 0;
             __syncthreads();
             if (TMA && s_timeout) return timed_out(tile_no);
+            const int nreps = kTopkWarps * q;
+            if (nreps > K) {  // uniform: thread t ranks representative t among all of them (ties by position)
+                if (tid < nreps) {
+                    const uint32_t mine = reps[tid];
+                    int rank = 0;
+#pragma unroll 8
+                    for (int j = 0; j < nreps; ++j) {
+                        const uint32_t other = reps[j];
+                        rank += (other > mine || (other == mine && j < tid)) ? 1 : 0;
+                    }
+                    if (rank == K - 1) warp_thr[0] = mine;
+                }
+                __syncthreads();
+            }
             uint32_t first_thr = warp_thr[0];
+            if (nreps <= K) {  // every representative is needed: the smallest one
 #pragma unroll
-            for (int w = 1; w < kTopkWarps; ++w) first_thr = min(first_thr, warp_thr[w]);
+                for (int w = 1; w < kTopkWarps; ++w) first_thr = min(first_thr, warp_thr[w]);
+            }
+            TOPK_MARK(4 + tile_no * 6);  // threshold known
             push_survivors(first_thr, 0, &s_count);
             __syncthreads();
+            TOPK_MARK(5 + tile_no * 6);  // survivors pushed
             const int count = s_count;
             if (count > kTileCap) {
                 overflow_tile(tile_begin, 0);
             } else {
                 rank_pending(count);
             }
+            TOPK_MARK(6 + tile_no * 6);  // first tile ranked
             continue;
         }
 
@@ -548,28 +587,88 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         push_survivors(thr, 0, &s_push[tile_no & 3]);
         streamed_prev = true;
         __syncthreads();  // the tile has been read and its survivors counted by every thread
+        TOPK_MARK(5 + tile_no * 6);  // survivors pushed
         if (TMA && s_timeout) return timed_out(tile_no);
     }
+    TOPK_MARK(40);
     if (streamed_prev) settle_previous(tile_no - 1);
+    TOPK_MARK(41);
+    // The lists come straight from the sorted composites in shared memory: the id is the low word,
+    // the value's bits follow from the order key (exactly, except that both zeros share a key — a
+    // zero is read again from the row so that -0.0 keeps its sign).
     int32_t* out_ids = out_ids_base + (row * out_lists + slice) * K;
     T* out_vals = out_vals_base + (row * out_lists + slice) * K;
+    const unsigned long long* best = cand[cur];
+    auto value_of = [&](unsigned long long c) {  // the float whose order key is the composite's high word
+        const uint32_t key = static_cast<uint32_t>(c >> 32);
+        return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
+    };
     for (int s = tid; s < K; s += kTopkThreads) {
         if (s < nbest) {
-            const uint32_t idx = ~static_cast<uint32_t>(cand[cur][s]);
+            const uint32_t idx = ~static_cast<uint32_t>(best[s]);
             out_ids[s] = static_cast<int32_t>(idx) + index_offset;
-            out_vals[s] = src[static_cast<int64_t>(idx) - begin];  // original bits (keeps -0.0)
+            const float v = value_of(best[s]);
+            out_vals[s] = v == 0.0f ? src[static_cast<int64_t>(idx) - begin] : from_float<T>(v);
         } else {
             out_ids[s] = -1;
             out_vals[s] = neg_inf<T>();
         }
     }
-    // With one slice per row the list just written is the final one: sample from it here
-    // instead of in a launch of its own (uniform is NULL whenever there are several slices).
-    if (uniform != nullptr) {
-        __syncthreads();  // the list written above is visible to warp 0
-        if (tid < 32)
-            sample_row<T>(out_ids, out_vals, K, uniform[row], temperature, reinterpret_cast<float*>(hist), sampled_ids + row);
+    TOPK_MARK(42);  // lists written
+    // With one slice per row the list just written is the final one: sample from it here instead
+    // of in a launch of its own (uniform is NULL whenever there are several slices).  Same
+    // arithmetic as sample_row, on the values recovered from the keys.
+    if (uniform != nullptr && tid < 32) {
+        const int lane = tid;
+        const int valid = nbest;  // slots nbest..K-1 are empty
+        const float v0 = valid > 0 ? value_of(best[0]) : 0.f;
+        int pick = INT_MAX;
+        if (valid <= 64) {
+            // Two terms per lane in registers; the running sum is carried by every lane and fed one
+            // term at a time by a shuffle from the lane that holds it (the sequential fp32 sums of the
+            // definition, without a chain of dependent shared-memory accesses); lane i % 32 keeps the
+            // sum after term i.
+            const float p0 = lane < valid ? expf((value_of(best[lane]) - v0) / temperature) : 0.f;
+            const float p1 = lane + 32 < valid ? expf((value_of(best[lane + 32]) - v0) / temperature) : 0.f;
+            float c0 = 0.f, c1 = 0.f, run = 0.f;
+#pragma unroll 8
+            for (int i = 0; i < 32; ++i) {
+                run += __shfl_sync(0xffffffffu, p0, i);
+                if (lane == i) c0 = run;
+            }
+            if (valid > 32) {
+#pragma unroll 8
+                for (int i = 0; i < 32; ++i) {
+                    run += __shfl_sync(0xffffffffu, p1, i);
+                    if (lane == i) c1 = run;
+                }
+            }
+            const float target = u_row * run;  // slots past `valid` added exact zeros: run is the total
+            if (lane < valid && c0 >= target) pick = lane;
+            else if (lane + 32 < valid && c1 >= target) pick = lane + 32;
+        } else {
+            float* cum = reinterpret_cast<float*>(hist);
+            for (int i = lane; i < valid; i += 32) cum[i] = expf((value_of(best[i]) - v0) / temperature);
+            __syncwarp();
+            if (lane == 0) {
+                float run = 0.f;
+#pragma unroll 8
+                for (int i = 0; i < valid; ++i) {
+                    run += cum[i];
+                    cum[i] = run;
+                }
+            }
+            __syncwarp();
+            const float target = u_row * cum[valid - 1];
+            for (int i = lane; i < valid; i += 32)
+                if (cum[i] >= target && i < pick) pick = i;
+        }
+        pick = __reduce_min_sync(0xffffffffu, pick);
+        if (pick == INT_MAX) pick = valid - 1;  // nothing reached the target (rounding): the last valid slot
+        if (lane == 0)
+            sampled_ids[row] = pick >= 0 ? static_cast<int32_t>(~static_cast<uint32_t>(best[pick])) + index_offset : -1;
     }
+    TOPK_MARK(43);  // sampled
 }
 
 template <typename T>
@@ -815,6 +914,9 @@ int static_scratch(unsigned char** out) {
 }  // namespace ispore
 
 #ifdef ISPORE_TUNING
+extern "C" __attribute__((visibility("default"))) void ispore_topk_ts(long long* out) {
+    cudaMemcpyFromSymbol(out, ispore::g_topk_ts, sizeof(long long) * 64);
+}
 extern "C" __attribute__((visibility("default"))) void ispore_topk_debug(int v) {
     cudaMemcpyToSymbol(ispore::g_topk_debug, &v, sizeof(int));
 }
