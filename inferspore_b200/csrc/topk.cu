@@ -9,19 +9,19 @@
 // (value descending, index ascending), -0.0 == +0.0.
 //
 // Round 1 (one CTA per row slice) streams its slice from HBM once, a tile of
-// 8192 elements at a time (TMA bulk copies into a two-stage shared-memory ring,
-// the next tile requested before the current one is touched), into registers
-// as raw bit patterns, 32 per thread.  First tile: a threshold that is
-// guaranteed to keep at least K elements comes from one representative per
-// thread with warp-level max-reductions only; the few survivors are compacted
-// into shared memory and ranked by counting against each other, which yields
-// the running top-K already sorted without a sorting network.  Every later tile
-// only has to beat the running K-th best: while that is a positive value the
-// test is one integer compare of the thread's maximum (nearly every thread of
-// every later tile holds no survivor and is done after it); the few survivors
-// are parked behind the running best and ranked before the next tile is
-// touched, so the bar rises as early as possible.  A later tile costs one block
-// barrier, plus one for its ranking when it had survivors.
+// 8192 elements at a time (TMA bulk copies into a shared-memory ring, the next
+// tile requested before the current one is touched), 32 elements per thread.
+// First tile: a threshold that is guaranteed to keep at least K elements comes
+// from one representative per thread: every warp sorts its 32 with a shuffle
+// network and contributes its best few, and the K-th largest contribution is
+// the threshold.  The few survivors are compacted into shared memory, a warp
+// at a time, and ranked by counting against each other, which yields the
+// running top-K already sorted.  Every later tile only has to beat the running
+// K-th best: while that is a positive value the test is one integer compare of
+// the thread's maximum and one vote per warp; the few survivors are parked
+// behind the running best and ranked before the next tile is touched, so the
+// bar rises as early as possible.  A later tile costs one block barrier, plus
+// one for its ranking when it had survivors.
 // Adversarial tiles (e.g. constant data, where the threshold keeps everything)
 // fall back to an exact radix select over the tile, ties resolved by an
 // index-ordered block scan.  Round 2 (one CTA per row) merges the slices' sorted
@@ -55,6 +55,7 @@ constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
 constexpr int kMaxStages = 8;                                // tiles of the shared-memory ring
 constexpr int kTileCap = 256;                                // survivors a tile may add on the fast path
 constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + tile survivors
+constexpr int kWarpVecCap = 64;                              // vectors with survivors a warp lists per tile
 constexpr int kMergeCap = 4096;                              // lists*K candidates the merge kernel holds
 
 __device__ __forceinline__ uint32_t order_key(float f) {
@@ -78,21 +79,53 @@ __device__ __forceinline__ __half neg_inf<__half>() {
     return __ushort_as_half(0xFC00u);
 }
 
-// The q largest (q <= 32) of the 32 lane values, best first, to out[0..q): q rounds of a hardware
-// max-reduction, retiring one holder of the maximum per round; 0 where fewer than q lanes are
-// non-empty.  Returns the q-th largest.
-__device__ __forceinline__ uint32_t warp_top_q(uint32_t v, int q, uint32_t* out) {
+// Bitonic networks over one warp.  Element i of a sequence of 32 R values sits in register i / 32
+// of lane i % 32; exchanges across a distance below 32 are shuffles, the others stay inside a lane.
+// Every loop unrolls, so the network is straight-line code.
+// (Measured and not kept: ranking the candidates of a tile — 64-bit composites, up to 128 — with
+// these networks in a single warp instead of the counting rank of the whole CTA below.  It
+// executes a fifth fewer instructions over the kernel and is slower at every row count, 8 to 25 %:
+// two dozen dependent exchanges in one warp against independent counting loops in eight.)
+template <typename V, int R>
+__device__ __forceinline__ void bitonic_phase(V (&a)[R], int k) {  // merges runs of k / 2 into runs of k
     const int lane = threadIdx.x & 31;
-    uint32_t m = 0;
-    for (int i = 0; i < q; ++i) {
-        m = __reduce_max_sync(0xffffffffu, v);
-        if (lane == 0) out[i] = m;
-        if (m != 0) {  // uniform
-            const uint32_t holders = __ballot_sync(0xffffffffu, v == m);
-            if (lane == __ffs(holders) - 1) v = 0;
+#pragma unroll
+    for (int j = 16 * R; j > 0; j >>= 1) {
+        if (j >= k) continue;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            const bool desc = ((r * 32 + lane) & k) == 0;  // the last phase (k = 32 R) is descending everywhere
+            if (j >= 32) {
+                const int rp = r ^ (j >> 5);
+                if (rp > r && ((a[r] < a[rp]) == desc)) {
+                    const V t = a[r];
+                    a[r] = a[rp];
+                    a[rp] = t;
+                }
+            } else {
+                const V p = __shfl_xor_sync(0xffffffffu, a[r], j);
+                const bool take_max = ((lane & j) == 0) == desc;
+                a[r] = ((a[r] > p) == take_max) ? a[r] : p;
+            }
         }
     }
-    return m;
+}
+// Sorts the 32 R values best (largest) first.
+template <typename V, int R>
+__device__ __forceinline__ void warp_sort_desc(V (&a)[R]) {
+#pragma unroll
+    for (int k = 2; k <= 32 * R; k <<= 1) bitonic_phase<V, R>(a, k);
+}
+
+// The q largest (q <= 32) of the 32 lane values, best first, to out[0..q) (0 where fewer than q
+// lanes are non-empty): one 32-value sorting network, 15 exchanges whatever q.  Returns the q-th
+// largest to every lane.
+__device__ __forceinline__ uint32_t warp_top_q(uint32_t v, int q, uint32_t* out) {
+    const int lane = threadIdx.x & 31;
+    uint32_t a[1] = {v};
+    warp_sort_desc<uint32_t, 1>(a);
+    if (lane < q) out[lane] = a[0];
+    return __shfl_sync(0xffffffffu, a[0], q - 1);
 }
 
 // Number of entries of a descending-sorted composite list that are greater than x.
@@ -302,8 +335,9 @@ __device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, in
 
 // TMA: the tiles arrive through the copy engine (cp.async.bulk into a ring of `nstages`
 // shared-memory stages, completion on one mbarrier per stage), requested nstages - 1 tiles ahead,
-// so the following tiles are on their way while one is thresholded and ranked.  The registers are
-// filled from shared memory.  Needs the vector-load conditions (16-byte aligned rows, slice length
+// so the following tiles are on their way while one is thresholded and ranked (a one-stage ring
+// requests the next tile once the current one has been read, and only the ranking hides part of
+// its way).  The registers are filled from shared memory.  Needs the vector-load conditions (16-byte aligned rows, slice length
 // a multiple of the vector).  Without TMA the tile is loaded straight into registers.
 template <typename T, int MIN_BLOCKS, bool TMA>
 __global__ void __launch_bounds__(kTopkThreads, MIN_BLOCKS)
@@ -355,6 +389,9 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         tma::mbar_arrive_expect_tx(&full[stage], tile_bytes(tile_begin));
         tma::load(stage_raw + static_cast<size_t>(stage) * kStageBytes, src + tile_begin, tile_bytes(tile_begin), &full[stage]);
     };
+    // Tiles requested before the loop: all stages but one, and the only one of a one-stage ring
+    // (whose next tile can only follow once the current one has been read).
+    const int first_wave = nstages > 1 ? nstages - 1 : 1;
     if (TMA) {
         if (tid == 0) {
             // The first copies leave before the other threads have even arrived: the wait for the
@@ -362,7 +399,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             for (int st = 0; st < nstages; ++st) tma::mbar_init(&full[st], 1);
             tma::fence_mbar_init();
             s_timeout = 0;
-            for (int tile = 0; tile < nstages - 1 && tile < ntiles; ++tile) issue_tile(tile, tile);
+            for (int tile = 0; tile < first_wave && tile < ntiles; ++tile) issue_tile(tile, tile);
         }
         __syncthreads();  // the barriers' initialisation is visible to every thread that will wait on them
     }
@@ -388,7 +425,8 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     // barrier): tile t + nstages - 1 goes there.
     auto issue_next = [&](int tile_no) {
         const int ahead = tile_no + nstages - 1;
-        if (TMA && tid == 0 && ahead < ntiles) issue_tile(ahead, ring_stage == 0 ? nstages - 1 : ring_stage - 1);
+        if (TMA && tid == 0 && ahead >= first_wave && ahead < ntiles)
+            issue_tile(ahead, ring_stage == 0 ? nstages - 1 : ring_stage - 1);
     };
     // Ranks the running best together with the first `count` entries behind it; afterwards the
     // (sorted) best is in the other buffer.  Called by every thread; ends with a barrier.
@@ -471,28 +509,68 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             group_maxima_from_global<T>(src, n, tile_begin, vec_loads != 0, gmax, pmax);
         }
         TOPK_MARK(3 + tile_no * 6);  // tile landed and read
-        // Survivors of this thread: the elements whose key reaches `limit`, pushed behind the running
-        // best from position base + (this thread's share of `counter`), dropped beyond kTileCap
-        // (the counter still counts them, which is how the overflow is noticed).
+        // Survivors: the elements whose key reaches `limit`, pushed behind the running best from
+        // position base + (their share of `counter`), dropped beyond kTileCap (the counter still
+        // counts them, which is how the overflow is noticed).
         auto push_survivors = [&](uint32_t limit, int base, int* counter) {
-            // A positive limit: survivors are exactly the elements whose raw bits, as signed ints,
-            // reach its bits, so pmax clears a thread without survivors in one compare — nearly every
-            // thread of every tile after the first — and the group maxima say which vectors to read
-            // again.  Otherwise every group is read again and compared through the order key.
-            const bool positive = limit > 0x80000000u;
-            const int limit_bits = static_cast<int>(limit & 0x7fffffffu);
-            uint32_t groups = 0;
-            if (!positive) {
-                groups = (1u << kVecs) - 1u;
-            } else if (pmax >= limit_bits) {
-#pragma unroll
-                for (int k = 0; k < kVecs; ++k) groups |= (gmax[k] >= limit_bits ? 1u : 0u) << k;
-            }
-            if (TOPK_DEBUG(16)) groups = 0;
             unsigned long long* mine = cand[cur] + nbest;
-            while (groups != 0) {
-                const int k = __ffs(groups) - 1;
-                groups &= groups - 1;
+            if (TOPK_DEBUG(16)) return;
+            if (limit > 0x80000000u) {
+                // A positive limit: survivors are exactly the elements whose raw bits, as signed ints,
+                // reach its bits.  pmax and one vote clear a warp without survivors.  Otherwise the
+                // warp works as one: the lanes note which of their vectors hold a survivor in a
+                // short per-warp list (positions from votes, no atomics), then lane l looks at
+                // element l % E of listed vector l / E — 32 elements per trip, read again from the
+                // stage — and the survivors among them take consecutive slots behind the running
+                // best through one shared-memory atomic per trip.  (A thread walking its own groups
+                // instead costs the warp the union of all its lanes' walks, with an atomic in each;
+                // a warp walking its holder threads one by one, 32 elements each, was measured 25 %
+                // slower over the whole kernel: a dozen dependent trips instead of one or two.)
+                const int limit_bits = static_cast<int>(limit & 0x7fffffffu);
+                if (__ballot_sync(0xffffffffu, pmax >= limit_bits) == 0) return;
+                const int lane = tid & 31;
+                const uint32_t below = (1u << lane) - 1u;
+                uint16_t* wlist = reinterpret_cast<uint16_t*>(hist) + (tid >> 5) * kWarpVecCap;
+                int nv = 0;
+#pragma unroll
+                for (int k = 0; k < kVecs; ++k) {
+                    const bool holds = gmax[k] >= limit_bits;  // a group beyond the slice is INT_MIN
+                    const uint32_t votes = __ballot_sync(0xffffffffu, holds);
+                    const int at = nv + __popc(votes & below);
+                    if (holds && at < kWarpVecCap) wlist[at] = static_cast<uint16_t>(tid + k * kTopkThreads);
+                    nv += __popc(votes);
+                }
+                if (nv > kWarpVecCap) {  // more than the list holds: the tile is selected exactly
+                    if (lane == 0) atomicAdd(counter, kTileCap + 1);
+                    return;
+                }
+                __syncwarp();
+                const int sub = lane / E, e = lane % E;
+                for (int j0 = 0; j0 < nv; j0 += 32 / E) {
+                    const int j = j0 + sub;
+                    int bits = INT_MIN, el = 0;
+                    if (j < nv) {
+                        el = static_cast<int>(wlist[j]) * E + e;  // within the tile
+                        if (TMA) bits = __float_as_int(to_float<T>(stage[el]));
+                        else if (tile_begin + el < n) bits = __float_as_int(to_float<T>(__ldg(src + tile_begin + el)));
+                    }
+                    const bool in = bits >= limit_bits;
+                    const uint32_t votes = __ballot_sync(0xffffffffu, in);
+                    if (votes == 0) continue;
+                    int first = 0;
+                    if (lane == 0) first = atomicAdd(counter, __popc(votes));
+                    first = __shfl_sync(0xffffffffu, first, 0);
+                    const int pos = base + first + __popc(votes & below);
+                    if (in && pos < kTileCap)
+                        mine[pos] = composite(static_cast<uint32_t>(bits) | 0x80000000u,
+                                              static_cast<uint32_t>(begin + tile_begin + el));
+                }
+                return;
+            }
+            // Zero or negative limit (fewer than K positive values so far): every group is read
+            // again by its own thread and compared through the order key.
+#pragma unroll 1
+            for (int k = 0; k < kVecs; ++k) {
                 const int v = tid + k * kTopkThreads;
                 const int el0 = tile_begin + v * E;
                 if (el0 >= n) continue;
@@ -516,10 +594,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
                 }
                 uint32_t m = 0;
 #pragma unroll
-                for (int e = 0; e < E; ++e) {
-                    const bool in = positive ? __float_as_int(val[e]) >= limit_bits : order_key(val[e]) >= limit;
-                    m |= (in ? 1u : 0u) << e;
-                }
+                for (int e = 0; e < E; ++e) m |= (order_key(val[e]) >= limit ? 1u : 0u) << e;
                 m &= live;
                 if (m != 0) {
                     int pos = base + atomicAdd(counter, __popc(m));
@@ -549,17 +624,27 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             __syncthreads();
             if (TMA && s_timeout) return timed_out(tile_no);
             const int nreps = kTopkWarps * q;
-            if (nreps > K) {  // uniform: thread t ranks representative t among all of them (ties by position)
-                if (tid < nreps) {
-                    const uint32_t mine = reps[tid];
-                    int rank = 0;
-#pragma unroll 8
-                    for (int j = 0; j < nreps; ++j) {
-                        const uint32_t other = reps[j];
-                        rank += (other > mine || (other == mine && j < tid)) ? 1 : 0;
-                    }
-                    if (rank == K - 1) warp_thr[0] = mine;
+            if (nreps > K) {
+                // (uniform) The K-th largest representative, ties by position: every representative
+                // is ranked by as many threads as the CTA affords, each counting a share of the others.
+                int P = 1, shift = 0;
+                while (P < 32 && nreps * (P * 2) <= kTopkThreads) {
+                    P *= 2;
+                    ++shift;
                 }
+                const int r = tid >> shift, part = tid & (P - 1);
+                const bool live = r < nreps;  // nreps <= 256: one trip
+                const uint32_t mine = live ? reps[r] : 0u;
+                int rank = 0;
+                if (live) {
+#pragma unroll 4
+                    for (int j = part; j < nreps; j += P) {
+                        const uint32_t other = reps[j];
+                        rank += (other > mine || (other == mine && j < r)) ? 1 : 0;
+                    }
+                }
+                for (int o = 1; o < P; o <<= 1) rank += __shfl_xor_sync(0xffffffffu, rank, o);
+                if (live && part == 0 && rank == K - 1) warp_thr[0] = mine;
                 __syncthreads();
             }
             uint32_t first_thr = warp_thr[0];
@@ -813,16 +898,26 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
     const int vec_loads = (vocab % E == 0) && aligned16(probs);
     const bool use_tma = vec_loads && !(variant & 1);
-    // The tile ring: 64 KB per CTA, three CTAs per SM.  (Measured: deeper rings at fewer CTAs per SM
-    // are slower at every row count — the kernel is bound by the work per tile, not by waiting for tiles.)
+    // The tile ring.  A row is a chain of dependent steps (tile, threshold, survivors, rank, next
+    // tile ...) and what a launch with more rows than the GPU holds at once needs is rows in
+    // flight: then 32 KB of ring per CTA and a register cap of 64, four CTAs per SM (measured at
+    // 4096 rows x 32000: 125 us against 137 us, in both types).  A launch that fits in one wave
+    // keeps 64 KB and three CTAs per SM (one stage is 20 % slower there: nothing else hides the
+    // wait for the next tile).  Measured and not kept: deeper rings at fewer CTAs per SM, slower
+    // at every row count.
     constexpr size_t kStage = static_cast<size_t>(kTileElems) * sizeof(T);
-    constexpr size_t kRingMany = 64 * 1024, kRingFew = 64 * 1024;
-    auto kernel = use_tma ? topk_slice_kernel<T, 3, true> : topk_slice_kernel<T, 4, false>;
-    if (use_tma && !allow_dynamic_smem(kernel, kRingFew))
-        return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", kRingFew);
+    constexpr size_t kRingMany = 32 * 1024, kRingFew = 64 * 1024;
+    const int64_t one_wave = 3 * static_cast<int64_t>(sm_count());
+    bool many = use_tma && rows > one_wave;  // (a launch of that many rows runs one slice per row)
+    if (variant & 0x40) many = use_tma;
+    if (variant & 0x80) many = false;
+    auto kernel = use_tma ? (many ? topk_slice_kernel<T, 4, true> : topk_slice_kernel<T, 3, true>) : topk_slice_kernel<T, 4, false>;
+    const size_t ring_bytes = many ? kRingMany : kRingFew;
+    if (use_tma && !allow_dynamic_smem(kernel, ring_bytes))
+        return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", ring_bytes);
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "topk: no device status word");
-    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, use_tma ? kRingMany : 0);
+    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, use_tma ? ring_bytes : 0);
     int64_t slices;
     switch ((variant & 0xff) >> 1) {
         case 1: slices = ceil_div(vocab, kTileElems); if (ceil_div(resident, rows) > slices) slices = ceil_div(resident, rows); break;
@@ -841,12 +936,11 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     int nstages = 0;
     size_t smem = 0;
     if (use_tma) {
-        const bool few = rows * slices <= 2 * static_cast<int64_t>(sm_count());
-        int64_t st_n = static_cast<int64_t>((few ? kRingFew : kRingMany) / kStage);
+        int64_t st_n = static_cast<int64_t>(ring_bytes / kStage);
         const int64_t tiles = ceil_div(slice_len, kTileElems);
         if (st_n > tiles) st_n = tiles;  // a short slice needs no more stages than it has tiles
         if (st_n > kMaxStages) st_n = kMaxStages;
-        if (st_n < 2) st_n = 2;
+        if (st_n < 1) st_n = 1;
         if (variant >> 8) st_n = variant >> 8;  // tuning builds: stages from the variant's high byte
         nstages = static_cast<int>(st_n);
         smem = static_cast<size_t>(nstages) * kStage;

@@ -563,6 +563,38 @@ def test_topk_outliers_in_the_first_tile(ops, orc, rng, dtype):
         assert np.array_equal(got_v.view(bits), want_v.view(bits))
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("shape", ["noise", "rising", "steps", "flat", "negative"])
+@pytest.mark.parametrize("vocab,K", [(20000, 50), (8192, 64), (17001, 5)])
+def test_topk_more_rows_than_one_wave(ops, orc, rng, dtype, shape, vocab, K):
+    """More rows than three CTAs per SM hold at once: the launch switches to a smaller tile ring
+    (one fp32 stage, two fp16 stages) and four CTAs per SM, one slice per row.  `flat` rows hold one
+    value only (every vector of a tile survives the threshold: the per-warp lists overflow and the
+    tile is selected exactly), `rising` and `steps` overflow the parked survivors of later tiles,
+    `negative` keeps the threshold below zero, 17001 is not a whole number of 128-bit vectors."""
+    rows = 600
+    x = rng.standard_normal((rows, vocab)).astype(np.float32)
+    t = np.arange(vocab, dtype=np.float32) / vocab
+    if shape == "rising":
+        x += 8 * t
+    elif shape == "steps":
+        x += 3.0 * ((np.arange(vocab) // 8192) % 2 == 1)
+    elif shape == "flat":
+        x[:] = 0.75
+        x[::7, 100] = 2.0
+    elif shape == "negative":
+        x = -np.abs(x) - 1.0
+    probs = x.astype(dtype)
+    u = rng.random(rows, dtype=np.float32)
+    got_i, got_v, picked = _topk_run(ops, probs, K, uniform=u)
+    want_i, want_v = orc.topk(probs, K)
+    bits = np.uint32 if dtype == np.float32 else np.uint16
+    assert np.array_equal(got_i, want_i)
+    assert np.array_equal(got_v.view(bits), want_v.view(bits))
+    want_pick, margin = orc.sampling(want_i, want_v, u, 1.0)
+    assert np.all(margin[picked != want_pick] < 1e-6)
+
+
 def test_topk_without_scratch(ops, orc, rng):
     probs = (rng.standard_normal((4, 20000), dtype=np.float32))
     f_i = torch.empty((4, 10), dtype=torch.int32, device="cuda:0")
