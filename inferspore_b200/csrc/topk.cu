@@ -53,9 +53,10 @@ constexpr int kTopkWarps = kTopkThreads / 32;
 constexpr int kElemsPerThread = 32;                          // keys a thread holds per tile
 constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
 constexpr int kMaxStages = 8;                                // tiles of the shared-memory ring
-constexpr int kTileCap = 256;                                // survivors a tile may add on the fast path
+constexpr int kRoundTiles = 2;                               // tiles a CTA thresholds, compacts and ranks together
+constexpr int kTileCap = 256;                                // survivors a round may add on the fast path
 constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + tile survivors
-constexpr int kWarpVecCap = 64;                              // vectors with survivors a warp lists per tile
+constexpr int kWarpVecCap = 64;                              // vectors with survivors a warp lists per round
 constexpr int kMergeCap = 4096;                              // lists*K candidates the merge kernel holds
 
 __device__ __forceinline__ uint32_t order_key(float f) {
@@ -220,8 +221,8 @@ __device__ __forceinline__ void group_maxima_from_global(const T* src, int n, in
 
 // Exact selection of a tile's K largest keys, for tiles the threshold cannot thin out
 // (constant data, K close to the tile size): radix select, 8 bits per pass, then an
-// index-ordered block scan that hands the tied key to the lowest indices.  Writes exactly K
-// composites to `mine`.  Kept out of line, and re-reading the tile from global memory (it is
+// index-ordered block scan that hands the tied key to the lowest indices.  Writes the tile's
+// min(K, elements) best composites to `mine` and returns how many.  Kept out of line, and re-reading the tile from global memory (it is
 // cache-resident) instead of taking the caller's registers, so that it costs the fast path
 // neither registers nor stack traffic.
 struct SelectScratch {
@@ -232,8 +233,8 @@ struct SelectScratch {
     int* s_need;
 };
 template <typename T>
-__device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int n, long long begin, int K,
-                                               unsigned long long* mine, SelectScratch sm) {
+__device__ __noinline__ int exact_select_tile(const T* src, int tile_begin, int n, long long begin, int K,
+                                              unsigned long long* mine, SelectScratch sm) {
     const int tid = threadIdx.x;
     int* hist = sm.hist;
     int* warp_cnt = sm.warp_cnt;
@@ -245,7 +246,8 @@ __device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int
     auto key_at = [&](int el) { return order_key(to_float<T>(src[el])); };
 
     uint32_t prefix = 0, prefix_mask = 0;
-    int need = K;  // the caller saw more than kTileCap >= K survivors, so the tile holds at least K elements
+    const int wanted = tile_end - tile_begin < K ? tile_end - tile_begin : K;
+    int need = wanted;
     for (int shift = 24; shift >= 0; shift -= 8) {
         if (tid < 256) hist[tid] = 0;
         __syncthreads();
@@ -296,6 +298,7 @@ __device__ __noinline__ void exact_select_tile(const T* src, int tile_begin, int
         taken += total;
         __syncthreads();
     }
+    return wanted;
 }
 
 // exp((v - v0)/T) in index order, inverse CDF on a caller-drawn uniform.  One warp; `cum` is K
@@ -377,6 +380,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     int nbest = 0;  // entries of the running best (sorted, best first)
     const int q = (K + kTopkWarps - 1) / kTopkWarps;
     const int ntiles = (n + kTileElems - 1) / kTileElems;
+    const int nrounds = (ntiles + kRoundTiles - 1) / kRoundTiles;
 
     constexpr uint32_t kStageBytes = kTileElems * sizeof(T);
     auto tile_bytes = [&](int tile_begin) {
@@ -384,49 +388,52 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         return static_cast<uint32_t>(left < kTileElems ? left : kTileElems) * static_cast<uint32_t>(sizeof(T));
     };
     // Tile t lives in stage t % nstages and completes its barrier with parity (t / nstages) & 1.
-    auto issue_tile = [&](int tile, int stage) {  // thread 0 only
+    auto stage_of = [&](int tile) {
+        return reinterpret_cast<const T*>(stage_raw + static_cast<size_t>(tile % nstages) * kStageBytes);
+    };
+    auto issue_tile = [&](int tile) {  // thread 0 only
+        const int stage = tile % nstages;
         const int tile_begin = tile * kTileElems;
         tma::mbar_arrive_expect_tx(&full[stage], tile_bytes(tile_begin));
         tma::load(stage_raw + static_cast<size_t>(stage) * kStageBytes, src + tile_begin, tile_bytes(tile_begin), &full[stage]);
     };
-    // Tiles requested before the loop: all stages but one, and the only one of a one-stage ring
-    // (whose next tile can only follow once the current one has been read).
-    const int first_wave = nstages > 1 ? nstages - 1 : 1;
     if (TMA) {
         if (tid == 0) {
-            // The first copies leave before the other threads have even arrived: the wait for the
-            // first tile is the longest stall of a row.
+            // The whole ring is requested before the other threads have even arrived: the wait for
+            // the first tiles is the longest stall of a row.
             for (int st = 0; st < nstages; ++st) tma::mbar_init(&full[st], 1);
             tma::fence_mbar_init();
             s_timeout = 0;
-            for (int tile = 0; tile < first_wave && tile < ntiles; ++tile) issue_tile(tile, tile);
+            for (int tile = 0; tile < nstages && tile < ntiles; ++tile) issue_tile(tile);
         }
         __syncthreads();  // the barriers' initialisation is visible to every thread that will wait on them
     }
-    int ring_stage = 0;        // stage of the tile worked on
-    uint32_t ring_phase = 0;   // parity its barrier completes with
 
-    // Streamed tiles count their survivors in s_push[tile & 3]: the count of tile t is read by
-    // everyone after the barrier of tile t+1 while tile t+1 already counts in the next slot, and
-    // the slot is cleared again two tiles later, so no thread reads a counter that another is
+    // A round takes kRoundTiles tiles at once — 64 elements per thread — through threshold,
+    // compaction and ranking: those steps depend on each other and on two block barriers, and a row
+    // is a chain of them, so half as many rounds is what shortens a row (measured at 256 and 4096
+    // rows x 32000 against one tile per round: see the dispatcher).
+    // Streamed rounds count their survivors in s_push[round & 3]: the count of round r is read by
+    // everyone after the barrier of round r+1 while round r+1 already counts in the next slot, and
+    // the slot is cleared again two rounds later, so no thread reads a counter that another is
     // still adding to.
-    bool streamed_prev = false;  // the previous tile's survivors are parked behind the running best, not yet ranked
+    bool streamed_prev = false;  // the previous round's survivors are parked behind the running best, not yet ranked
     uint32_t thr = 0;
-    // A bounded wait on a tile ran out somewhere in the CTA: record it, wait once more for the copy
-    // in flight (shared memory must not be released under it) and leave; every thread comes here.
-    auto timed_out = [&](int tile_no) {
+    // A bounded wait on a tile ran out somewhere in the CTA: record it, wait once more for the copies
+    // in flight (shared memory must not be released under them) and leave; every thread comes here.
+    auto timed_out = [&](int first_tile) {
         if (tid == 0) {
             atomicOr(status, ISPORE_DEV_TIMEOUT);
-            for (int t2 = tile_no; t2 < tile_no + nstages && t2 < ntiles; ++t2)  // this tile and those already requested
+            for (int t2 = first_tile; t2 < first_tile + nstages && t2 < ntiles; ++t2)  // the round's tiles and those already requested
                 tma::mbar_wait(&full[t2 % nstages], static_cast<uint32_t>(t2 / nstages) & 1u);
         }
     };
-    // At the top of iteration t the stage of tile t - 1 is free (that iteration ended with a
-    // barrier): tile t + nstages - 1 goes there.
-    auto issue_next = [&](int tile_no) {
-        const int ahead = tile_no + nstages - 1;
-        if (TMA && tid == 0 && ahead >= first_wave && ahead < ntiles)
-            issue_tile(ahead, ring_stage == 0 ? nstages - 1 : ring_stage - 1);
+    // Every thread has read the tiles of the round that starts at `first_tile` (a barrier has
+    // passed): their stages take the tiles one ring further on.
+    auto refill = [&](int first_tile) {
+        if (TMA && tid == 0) {
+            for (int t2 = first_tile + nstages; t2 < first_tile + kRoundTiles + nstages && t2 < ntiles; ++t2) issue_tile(t2);
+        }
     };
     // Ranks the running best together with the first `count` entries behind it; afterwards the
     // (sorted) best is in the other buffer.  Called by every thread; ends with a barrier.
@@ -441,74 +448,84 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             thr = kth == 0xffffffffu ? kth : kth + 1u;  // a later element must beat the K-th best outright
         }
     };
-    // The survivors of tile `tile_begin` did not fit behind the `kept` earlier ones: rank those,
-    // then select the tile's K largest exactly and rank again.
-    auto overflow_tile = [&](int tile_begin, int kept) {
-        if (kept > 0) rank_pending(kept);
-        exact_select_tile<T>(src, tile_begin, n, begin, K, cand[cur] + nbest,
-                             SelectScratch{hist, warp_cnt, &s_count, &s_digit, &s_need});
-        __syncthreads();
-        rank_pending(K);
+    // The survivors of the round that starts at `first_tile` did not fit behind the running best:
+    // each of its tiles is selected exactly (from global memory: the stages may be refilled by now)
+    // and ranked.
+    auto overflow_round = [&](int first_tile) {
+        for (int t2 = first_tile; t2 < first_tile + kRoundTiles && t2 < ntiles; ++t2) {
+            const int got = exact_select_tile<T>(src, t2 * kTileElems, n, begin, K, cand[cur] + nbest,
+                                                 SelectScratch{hist, warp_cnt, &s_count, &s_digit, &s_need});
+            __syncthreads();
+            rank_pending(got);
+        }
     };
 
-    // Takes in the survivors the previous (streamed) tile parked behind the running best and ranks
-    // them at once: the sooner the K-th best rises, the fewer elements of the following tiles
+    // Takes in the survivors the previous (streamed) round parked behind the running best and ranks
+    // them at once: the sooner the K-th best rises, the fewer elements of the following rounds
     // survive, and a ranking costs (K + survivors) x survivors comparisons.  Measured and not kept:
-    // parking the survivors of several tiles and ranking them together (5x the comparisons), and
+    // parking the survivors of several rounds and ranking them together (5x the comparisons), and
     // taking a fixed threshold from the first tile with ONE ranking at the end of the row (a row
     // whose first tile misleads needs a second pass, and with hundreds of rows per launch some row
-    // always does).  A tile that overflowed its room is selected exactly.  Runs at the top of an
+    // always does).  A round that overflowed its room is selected exactly.  Runs at the top of an
     // iteration, after the barrier that ended the previous one, while no tile is held in registers.
-    auto settle_previous = [&](int prev_tile_no) {
-        const int added = s_push[prev_tile_no & 3];
+    auto settle_previous = [&](int prev_round) {
+        const int added = s_push[prev_round & 3];
         if (added > kTileCap) {
-            overflow_tile(prev_tile_no * kTileElems, 0);
+            overflow_round(prev_round * kRoundTiles);
         } else if (added > 0) {
             rank_pending(added);
         }
     };
 
-    int tile_no = 0;
-    for (int tile_begin = 0; tile_begin < n; tile_begin += kTileElems, ++tile_no) {
-        // The stage the next tile goes to was last read during the previous iteration, which ended
-        // with a barrier: the copy can start now and fly while this tile is worked on.
-        TOPK_MARK(1 + tile_no * 6);  // top of the iteration
-        issue_next(tile_no);
-        if (tid == 0) s_push[(tile_no + 1) & 3] = 0;  // that slot was read for the last time two tiles ago
-        if (streamed_prev) settle_previous(tile_no - 1);
+    for (int round = 0; round < nrounds; ++round) {
+        const int t0 = round * kRoundTiles;
+        TOPK_MARK(1 + round * 6);  // top of the iteration
+        if (tid == 0) s_push[(round + 1) & 3] = 0;  // that slot was read for the last time two rounds ago
+        if (streamed_prev) settle_previous(round - 1);
         streamed_prev = false;
-        TOPK_MARK(2 + tile_no * 6);  // previous tile settled
+        TOPK_MARK(2 + round * 6);  // previous round settled
 
-        int gmax[kVecs];
-        int pmax;
-        const T* stage = reinterpret_cast<const T*>(stage_raw + static_cast<size_t>(ring_stage) * kStageBytes);
-        const uint4* stage_v = reinterpret_cast<const uint4*>(stage);
-        if (TMA) {
-            // A wait that runs out is recorded here and acted on by the whole CTA after the next
-            // barrier (whatever was read meanwhile is discarded).
-            if (!tma::mbar_wait(&full[ring_stage], ring_phase)) s_timeout = 1;
-            if (++ring_stage == nstages) {  // (the next iteration's stage; `stage` above keeps this tile's)
-                ring_stage = 0;
-                ring_phase ^= 1u;
+        // Group maxima: gmax[h * kVecs + k] covers vector tid + k * 256 of tile t0 + h.
+        int gmax[kRoundTiles * kVecs];
+        int pmax = INT_MIN;
+#pragma unroll
+        for (int h = 0; h < kRoundTiles; ++h) {
+            const int tile = t0 + h;
+            const int tile_begin = tile * kTileElems;
+            if (tile >= ntiles) {  // uniform: the slice ends with half a round
+#pragma unroll
+                for (int k = 0; k < kVecs; ++k) gmax[h * kVecs + k] = INT_MIN;
+                continue;
             }
-            pmax = INT_MIN;
-            const bool whole_tile = tile_begin + kTileElems <= n;  // uniform: no per-vector guards then
+            if (TMA) {
+                // A wait that runs out is recorded here and acted on by the whole CTA after the next
+                // barrier (whatever was read meanwhile is discarded).
+                if (!tma::mbar_wait(&full[tile % nstages], static_cast<uint32_t>(tile / nstages) & 1u)) s_timeout = 1;
+                const uint4* stage_v = reinterpret_cast<const uint4*>(stage_of(tile));
+                const bool whole_tile = tile_begin + kTileElems <= n;  // uniform: no per-vector guards then
 #pragma unroll
-            for (int k = 0; k < kVecs; ++k) {
-                const int v = tid + k * kTopkThreads;
-                gmax[k] = INT_MIN;
-                if (whole_tile || tile_begin + v * E < n) {
-                    Unpacked<T> x;
-                    unpack(stage_v[v], x);
+                for (int k = 0; k < kVecs; ++k) {
+                    const int v = tid + k * kTopkThreads;
+                    int g = INT_MIN;
+                    if (whole_tile || tile_begin + v * E < n) {
+                        Unpacked<T> x;
+                        unpack(stage_v[v], x);
 #pragma unroll
-                    for (int e = 0; e < E; ++e) gmax[k] = max(gmax[k], __float_as_int(x.v[e]));
+                        for (int e = 0; e < E; ++e) g = max(g, __float_as_int(x.v[e]));
+                    }
+                    gmax[h * kVecs + k] = g;
+                    pmax = max(pmax, g);
                 }
-                pmax = max(pmax, gmax[k]);
+            } else {
+                int part[kVecs];
+                int part_max;
+                group_maxima_from_global<T>(src, n, tile_begin, vec_loads != 0, part, part_max);
+#pragma unroll
+                for (int k = 0; k < kVecs; ++k) gmax[h * kVecs + k] = part[k];
+                pmax = max(pmax, part_max);
             }
-        } else {
-            group_maxima_from_global<T>(src, n, tile_begin, vec_loads != 0, gmax, pmax);
         }
-        TOPK_MARK(3 + tile_no * 6);  // tile landed and read
+        TOPK_MARK(3 + round * 6);  // tiles landed and read
         // Survivors: the elements whose key reaches `limit`, pushed behind the running best from
         // position base + (their share of `counter`), dropped beyond kTileCap (the counter still
         // counts them, which is how the overflow is noticed).
@@ -533,14 +550,16 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
                 uint16_t* wlist = reinterpret_cast<uint16_t*>(hist) + (tid >> 5) * kWarpVecCap;
                 int nv = 0;
 #pragma unroll
-                for (int k = 0; k < kVecs; ++k) {
-                    const bool holds = gmax[k] >= limit_bits;  // a group beyond the slice is INT_MIN
+                for (int g = 0; g < kRoundTiles * kVecs; ++g) {
+                    const bool holds = gmax[g] >= limit_bits;  // a group beyond the slice is INT_MIN
                     const uint32_t votes = __ballot_sync(0xffffffffu, holds);
                     const int at = nv + __popc(votes & below);
-                    if (holds && at < kWarpVecCap) wlist[at] = static_cast<uint16_t>(tid + k * kTopkThreads);
+                    // (which tile of the round) << 11 | vector within the tile
+                    if (holds && at < kWarpVecCap)
+                        wlist[at] = static_cast<uint16_t>(((g / kVecs) << 11) | (tid + (g % kVecs) * kTopkThreads));
                     nv += __popc(votes);
                 }
-                if (nv > kWarpVecCap) {  // more than the list holds: the tile is selected exactly
+                if (nv > kWarpVecCap) {  // more than the list holds: the round is selected exactly
                     if (lane == 0) atomicAdd(counter, kTileCap + 1);
                     return;
                 }
@@ -550,9 +569,11 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
                     const int j = j0 + sub;
                     int bits = INT_MIN, el = 0;
                     if (j < nv) {
-                        el = static_cast<int>(wlist[j]) * E + e;  // within the tile
-                        if (TMA) bits = __float_as_int(to_float<T>(stage[el]));
-                        else if (tile_begin + el < n) bits = __float_as_int(to_float<T>(__ldg(src + tile_begin + el)));
+                        const int entry = wlist[j];
+                        const int tile = t0 + (entry >> 11);
+                        el = tile * kTileElems + (entry & 2047) * E + e;  // within the slice
+                        if (TMA) bits = __float_as_int(to_float<T>(stage_of(tile)[el - tile * kTileElems]));
+                        else if (el < n) bits = __float_as_int(to_float<T>(__ldg(src + el)));
                     }
                     const bool in = bits >= limit_bits;
                     const uint32_t votes = __ballot_sync(0xffffffffu, in);
@@ -562,23 +583,23 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
                     first = __shfl_sync(0xffffffffu, first, 0);
                     const int pos = base + first + __popc(votes & below);
                     if (in && pos < kTileCap)
-                        mine[pos] = composite(static_cast<uint32_t>(bits) | 0x80000000u,
-                                              static_cast<uint32_t>(begin + tile_begin + el));
+                        mine[pos] = composite(static_cast<uint32_t>(bits) | 0x80000000u, static_cast<uint32_t>(begin + el));
                 }
                 return;
             }
             // Zero or negative limit (fewer than K positive values so far): every group is read
             // again by its own thread and compared through the order key.
 #pragma unroll 1
-            for (int k = 0; k < kVecs; ++k) {
-                const int v = tid + k * kTopkThreads;
-                const int el0 = tile_begin + v * E;
+            for (int g = 0; g < kRoundTiles * kVecs; ++g) {
+                const int tile = t0 + g / kVecs;
+                const int v = tid + (g % kVecs) * kTopkThreads;
+                const int el0 = tile * kTileElems + v * E;
                 if (el0 >= n) continue;
                 float val[E];
                 uint32_t live = 0;  // which of the group's elements exist
                 if (TMA || vec_loads) {  // whole vectors only on these paths (n % E == 0)
                     Unpacked<T> x;
-                    unpack(TMA ? stage_v[v] : ld_keep(reinterpret_cast<const uint4*>(src + tile_begin) + v), x);
+                    unpack(TMA ? reinterpret_cast<const uint4*>(stage_of(tile))[v] : ld_keep(reinterpret_cast<const uint4*>(src + el0)), x);
 #pragma unroll
                     for (int e = 0; e < E; ++e) val[e] = x.v[e];
                     live = (1u << E) - 1u;
@@ -610,19 +631,19 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         };
 
         if (nbest < K) {
-            // Fewer than K entries are held (the first tile; later ones only in tiny tiles).  Every warp
-            // contributes its q = ceil(K / 8) largest thread representatives: 8q distinct elements of
-            // the tile, of which the K-th largest is the threshold — at least K tile elements have a
+            // Fewer than K entries are held (the first round; later ones only in tiny slices).  Every
+            // warp contributes its q = ceil(K / 8) largest thread representatives: 8q distinct elements
+            // of the round, of which the K-th largest is the threshold — at least K elements have a
             // key >= it, and it sits far higher than the smallest of the 8q (the q-th best of the
-            // weakest warp): 65 instead of 97 survivors on average for K = 50, and the ranking that
-            // follows costs survivors squared.  The survivors are ranked at once.
-            const bool any_live = tile_begin + tid * E < n;  // the thread's first group exists
+            // weakest warp), and the ranking that follows costs survivors squared.  The survivors
+            // are ranked at once.
+            const bool any_live = t0 * kTileElems + tid * E < n;  // the thread's first group exists
             uint32_t* reps = reinterpret_cast<uint32_t*>(hist);  // [8][q] best first per warp
             const uint32_t wq = warp_top_q(any_live ? order_key(__int_as_float(pmax)) : 0u, q, reps + (tid >> 5) * q);
             if ((tid & 31) == 0) warp_thr[tid >> 5] = wq;
             if (tid == 0) s_count = 0;
             __syncthreads();
-            if (TMA && s_timeout) return timed_out(tile_no);
+            if (TMA && s_timeout) return timed_out(t0);
             const int nreps = kTopkWarps * q;
             if (nreps > K) {
                 // (uniform) The K-th largest representative, ties by position: every representative
@@ -652,29 +673,32 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
 #pragma unroll
                 for (int w = 1; w < kTopkWarps; ++w) first_thr = min(first_thr, warp_thr[w]);
             }
-            TOPK_MARK(4 + tile_no * 6);  // threshold known
+            TOPK_MARK(4 + round * 6);  // threshold known
             push_survivors(first_thr, 0, &s_count);
             __syncthreads();
-            TOPK_MARK(5 + tile_no * 6);  // survivors pushed
+            TOPK_MARK(5 + round * 6);  // survivors pushed
+            refill(t0);
             const int count = s_count;
             if (count > kTileCap) {
-                overflow_tile(tile_begin, 0);
+                overflow_round(t0);
             } else {
                 rank_pending(count);
             }
-            TOPK_MARK(6 + tile_no * 6);  // first tile ranked
+            TOPK_MARK(6 + round * 6);  // first round ranked
             continue;
         }
 
-        // Streamed tile: K entries are held, an element only matters if it beats the current K-th
+        // Streamed round: K entries are held, an element only matters if it beats the current K-th
         // best outright (on a tie the earlier index, already held, wins).  Survivors are parked
         // behind the running best and ranked at the top of the next iteration.
-        push_survivors(thr, 0, &s_push[tile_no & 3]);
+        push_survivors(thr, 0, &s_push[round & 3]);
         streamed_prev = true;
-        __syncthreads();  // the tile has been read and its survivors counted by every thread
-        TOPK_MARK(5 + tile_no * 6);  // survivors pushed
-        if (TMA && s_timeout) return timed_out(tile_no);
+        __syncthreads();  // the tiles have been read and their survivors counted by every thread
+        TOPK_MARK(5 + round * 6);  // survivors pushed
+        if (TMA && s_timeout) return timed_out(t0);
+        refill(t0);
     }
+    const int tile_no = nrounds;
     TOPK_MARK(40);
     if (streamed_prev) settle_previous(tile_no - 1);
     TOPK_MARK(41);
@@ -688,7 +712,8 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         const uint32_t key = static_cast<uint32_t>(c >> 32);
         return __uint_as_float((key & 0x80000000u) ? (key & 0x7fffffffu) : ~key);
     };
-    for (int s = tid; s < K; s += kTopkThreads) {
+    // (Written by the last warps first: the first warp goes straight on to the sampling.)
+    for (int s = kTopkThreads - 1 - tid; s < K; s += kTopkThreads) {
         if (s < nbest) {
             const uint32_t idx = ~static_cast<uint32_t>(best[s]);
             out_ids[s] = static_cast<int32_t>(idx) + index_offset;
@@ -716,19 +741,18 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
             const float p0 = lane < valid ? expf((value_of(best[lane]) - v0) / temperature) : 0.f;
             const float p1 = lane + 32 < valid ? expf((value_of(best[lane + 32]) - v0) / temperature) : 0.f;
             float c0 = 0.f, c1 = 0.f, run = 0.f;
+            const int first = valid < 32 ? valid : 32;
 #pragma unroll 8
-            for (int i = 0; i < 32; ++i) {
+            for (int i = 0; i < first; ++i) {
                 run += __shfl_sync(0xffffffffu, p0, i);
                 if (lane == i) c0 = run;
             }
-            if (valid > 32) {
 #pragma unroll 8
-                for (int i = 0; i < 32; ++i) {
-                    run += __shfl_sync(0xffffffffu, p1, i);
-                    if (lane == i) c1 = run;
-                }
+            for (int i = 0; i < valid - 32; ++i) {
+                run += __shfl_sync(0xffffffffu, p1, i);
+                if (lane == i) c1 = run;
             }
-            const float target = u_row * run;  // slots past `valid` added exact zeros: run is the total
+            const float target = u_row * run;  // every valid term has been added: run is the total
             if (lane < valid && c0 >= target) pick = lane;
             else if (lane + 32 < valid && c1 >= target) pick = lane + 32;
         } else {
@@ -898,21 +922,21 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
     const int vec_loads = (vocab % E == 0) && aligned16(probs);
     const bool use_tma = vec_loads && !(variant & 1);
-    // The tile ring.  A row is a chain of dependent steps (tile, threshold, survivors, rank, next
-    // tile ...) and what a launch with more rows than the GPU holds at once needs is rows in
-    // flight: then 32 KB of ring per CTA and a register cap of 64, four CTAs per SM (measured at
-    // 4096 rows x 32000: 125 us against 137 us, in both types).  A launch that fits in one wave
-    // keeps 64 KB and three CTAs per SM (one stage is 20 % slower there: nothing else hides the
-    // wait for the next tile).  Measured and not kept: deeper rings at fewer CTAs per SM, slower
-    // at every row count.
+    // The tile ring.  A row is a chain of dependent steps (tiles, threshold, survivors, rank, next
+    // tiles ...), so what a launch with more rows than the GPU holds at once needs is rows in
+    // flight, and what any launch needs is a ring that holds a whole round: 64 KB and three CTAs per
+    // SM — one round of fp32, two of fp16 — or, for fp16 launches of more than one wave, 32 KB and
+    // four CTAs per SM under a register cap of 64.  Measured and not kept: deeper rings at fewer
+    // CTAs per SM, slower at every row count.
     constexpr size_t kStage = static_cast<size_t>(kTileElems) * sizeof(T);
-    constexpr size_t kRingMany = 32 * 1024, kRingFew = 64 * 1024;
+    constexpr size_t kRingFew = 64 * 1024;
+    constexpr size_t kRingMany = kRoundTiles * kStage < kRingFew ? kRoundTiles * kStage : kRingFew;
     const int64_t one_wave = 3 * static_cast<int64_t>(sm_count());
-    bool many = use_tma && rows > one_wave;  // (a launch of that many rows runs one slice per row)
+    bool many = use_tma && kRingMany < kRingFew && rows > one_wave;  // (a launch of that many rows runs one slice per row)
     if (variant & 0x40) many = use_tma;
     if (variant & 0x80) many = false;
     auto kernel = use_tma ? (many ? topk_slice_kernel<T, 4, true> : topk_slice_kernel<T, 3, true>) : topk_slice_kernel<T, 4, false>;
-    const size_t ring_bytes = many ? kRingMany : kRingFew;
+    const size_t ring_bytes = (variant >> 8) ? static_cast<size_t>(variant >> 8) * kStage : (many ? kRingMany : kRingFew);  // (tuning builds: stages from the variant's high byte)
     if (use_tma && !allow_dynamic_smem(kernel, ring_bytes))
         return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", ring_bytes);
     unsigned* status = device_status_ptr();
@@ -941,7 +965,6 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
         if (st_n > tiles) st_n = tiles;  // a short slice needs no more stages than it has tiles
         if (st_n > kMaxStages) st_n = kMaxStages;
         if (st_n < 1) st_n = 1;
-        if (variant >> 8) st_n = variant >> 8;  // tuning builds: stages from the variant's high byte
         nstages = static_cast<int>(st_n);
         smem = static_cast<size_t>(nstages) * kStage;
     }
