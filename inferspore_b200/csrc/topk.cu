@@ -337,11 +337,12 @@ __device__ __forceinline__ void sample_row(const int32_t* ids, const T* vals, in
 }
 
 // TMA: the tiles arrive through the copy engine (cp.async.bulk into a ring of `nstages`
-// shared-memory stages, completion on one mbarrier per stage), requested nstages - 1 tiles ahead,
-// so the following tiles are on their way while one is thresholded and ranked (a one-stage ring
-// requests the next tile once the current one has been read, and only the ranking hides part of
-// its way).  The registers are filled from shared memory.  Needs the vector-load conditions (16-byte aligned rows, slice length
-// a multiple of the vector).  Without TMA the tile is loaded straight into registers.
+// shared-memory stages, completion on one mbarrier per stage).  The whole ring is requested at
+// the start, and once every thread has read the tiles of a round their stages are refilled, so
+// the next tiles are on their way while this round is ranked.  The registers are filled from
+// shared memory.  Needs the vector-load conditions (16-byte aligned rows, slice length a multiple
+// of the vector) and a ring that holds a round.  Without TMA the tiles are loaded straight into
+// registers.
 template <typename T, int MIN_BLOCKS, bool TMA>
 __global__ void __launch_bounds__(kTopkThreads, MIN_BLOCKS)
 topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int slices, int K,
@@ -927,7 +928,10 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     // flight, and what any launch needs is a ring that holds a whole round: 64 KB and three CTAs per
     // SM — one round of fp32, two of fp16 — or, for fp16 launches of more than one wave, 32 KB and
     // four CTAs per SM under a register cap of 64.  Measured and not kept: deeper rings at fewer
-    // CTAs per SM, slower at every row count.
+    // CTAs per SM, slower at every row count; and one CTA per resident slot walking the rows
+    // b, b + grid, ... with the next row's first tiles requested during the current row's last
+    // ranking (4096 rows: 124 us against 115 us — the rows a static stride hands the slowest CTA
+    // set the time, and with three rows per SM in flight the wait it hides was not exposed).
     constexpr size_t kStage = static_cast<size_t>(kTileElems) * sizeof(T);
     constexpr size_t kRingFew = 64 * 1024;
     constexpr size_t kRingMany = kRoundTiles * kStage < kRingFew ? kRoundTiles * kStage : kRingFew;
