@@ -17,6 +17,7 @@
 #include <float.h>
 
 #include "common.cuh"
+#include "tma.cuh"
 
 namespace ispore {
 namespace {
@@ -632,6 +633,202 @@ softmax_offset_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const
     }
 }
 
+// Long rows of whole vectors (up to 64 values per thread of a 256-thread CTA: 16384 elements).
+// The register kernels above keep a row's loads in flight in registers, which bounds the bytes an
+// SM has under way by its register file: measured 0.59 of the copy rate on 16384-long fp16 rows,
+// 0.75 with the launch shape that has the most of them.  Here the rows travel through the copy
+// engine instead: a CTA walks the rows b, b + grid, ... with a ring of shared-memory row buffers,
+// the next two rows requested (cp.async.bulk, one mbarrier per buffer) while one is worked on;
+// the normalised row is written back into its buffer and leaves as one bulk store.  A thread
+// holds the same vectors of every row (v = tid, tid + 256, ...), so nothing but the two
+// reductions crosses threads.  Same arithmetic as the head-group kernel.
+constexpr int kStagedMaxBuf = 4;
+
+template <typename T, int VPT, int kStagedThreads, bool CAUSAL>
+__global__ void __launch_bounds__(kStagedThreads, (kStagedThreads > 256 ? 1 : 2))
+softmax_staged_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
+                          const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
+                          uint32_t total_rows, uint32_t heads, uint32_t q_len, int row_vecs, float scale,
+                          int nbuf, unsigned* __restrict__ status) {
+    constexpr int E = VecTraits<T>::kElems;
+    constexpr int kWarps = kStagedThreads / 32;
+    using Exp = ExpPolicy<T>;
+    extern __shared__ __align__(128) unsigned char rows_raw[];  // [nbuf][row_vecs * 16]
+    __shared__ __align__(8) uint64_t full[kStagedMaxBuf];
+    __shared__ float red[2][kWarps];
+    __shared__ int s_timeout;
+    chain_begin();
+
+    const int tid = threadIdx.x;
+    const int lane = tid & 31, warp = tid >> 5;
+    const uint32_t row_bytes = static_cast<uint32_t>(row_vecs) * 16u;
+    const float a = scale * Exp::kPrescale;
+    const float neg = -10000.0f * Exp::kPrescale;
+    const float floor_m = FLT_MIN * Exp::kPrescale;
+    const uint32_t rows_per_batch = heads * q_len;
+
+    // Trip i of this CTA works on row blockIdx.x + i * gridDim.x, in buffer i % nbuf.
+    auto row_of = [&](uint32_t i) { return static_cast<uint64_t>(blockIdx.x) + static_cast<uint64_t>(i) * gridDim.x; };
+    auto request_row = [&](uint32_t i) {  // thread 0 only
+        const uint64_t r = row_of(i);
+        if (r >= total_rows) return;
+        const uint32_t b = i % static_cast<uint32_t>(nbuf);
+        tma::mbar_arrive_expect_tx(&full[b], row_bytes);
+        tma::load(rows_raw + static_cast<size_t>(b) * row_bytes, qk + r * static_cast<uint64_t>(row_vecs) * E, row_bytes, &full[b]);
+    };
+    if (tid == 0) {
+        for (int b = 0; b < nbuf; ++b) tma::mbar_init(&full[b], 1);
+        tma::fence_mbar_init();
+        s_timeout = 0;
+        for (int i = 0; i < nbuf - 1; ++i) request_row(static_cast<uint32_t>(i));
+    }
+    __syncthreads();
+
+    // The mask slice of a row comes from L2 and is needed as soon as the row's buffer has landed,
+    // which, thanks to the ring, is at once: it is requested a trip ahead, right after the previous
+    // row has consumed its own (the registers are free from there on), and is there in time.
+    uint4 m_raw[VPT];
+    auto request_mask = [&](uint32_t i) {
+        const uint64_t r = row_of(i);
+        if (CAUSAL || r >= total_rows) return;
+        const uint32_t b = static_cast<uint32_t>(r / rows_per_batch);
+        const uint32_t qi = static_cast<uint32_t>(r - static_cast<uint64_t>(b) * rows_per_batch) % q_len;
+        const uint4* mrow = reinterpret_cast<const uint4*>(mask) + (static_cast<int64_t>(b) * q_len + qi) * row_vecs;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = tid + j * kStagedThreads;
+            if (v < row_vecs) m_raw[j] = ld_keep(mrow + v);
+        }
+    };
+    request_mask(0);
+
+    for (uint32_t i = 0;; ++i) {
+        const uint64_t r = row_of(i);
+        if (r >= total_rows) break;  // uniform
+        const uint32_t buf = i % static_cast<uint32_t>(nbuf);
+        const uint32_t parity = (i / static_cast<uint32_t>(nbuf)) & 1u;
+        const uint32_t b = static_cast<uint32_t>(r / rows_per_batch);
+        const uint32_t qi = static_cast<uint32_t>(r - static_cast<uint64_t>(b) * rows_per_batch) % q_len;
+
+        int lo = 0, hi = -1;  // CAUSAL: the ones of the mask row span k in [lo, hi]
+        if (CAUSAL) {
+            const int qlen = __ldg(q_lens + b), klen = __ldg(k_lens + b);
+            lo = klen - qlen;
+            hi = static_cast<int>(qi) < qlen ? min(klen - 1, static_cast<int>(qi) + lo) : -1;
+        }
+        // A wait that runs out is recorded here and acted on by the whole CTA after the next barrier.
+        if (!tma::mbar_wait(&full[buf], parity)) s_timeout = 1;
+        uint4* srow = reinterpret_cast<uint4*>(rows_raw + static_cast<size_t>(buf) * row_bytes);
+
+        Unpacked<T> z[VPT];
+        float mx = floor_m;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = tid + j * kStagedThreads;
+            if (v < row_vecs) {
+                Unpacked<T> term;
+                if (CAUSAL) {
+                    const int k0 = v * E, k1 = k0 + (E - 1);
+                    const bool all_in = k0 >= lo && k1 <= hi;
+                    const bool all_out = k0 > hi || k1 < lo;
+                    const float fill = all_in ? 0.0f : neg;
+#pragma unroll
+                    for (int e = 0; e < E; ++e) term.v[e] = fill;
+                    if (!all_in && !all_out) {
+#pragma unroll
+                        for (int e = 0; e < E; ++e) term.v[e] = (k0 + e >= lo && k0 + e <= hi) ? 0.0f : neg;
+                    }
+                } else {
+                    unpack(m_raw[j], term);
+#pragma unroll
+                    for (int e = 0; e < E; ++e) term.v[e] = fmaf(term.v[e], -neg, neg);  // (1 - mask) * neg in one rounding
+                }
+                unpack(srow[v], z[j]);
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    z[j].v[e] = fmaf(a, z[j].v[e], term.v[e]);
+                    mx = fmaxf(mx, z[j].v[e]);
+                }
+            }
+        }
+        request_mask(i + 1);
+        mx = warp_max(mx);
+        if (lane == 0) red[0][warp] = mx;
+        __syncthreads();
+        if (s_timeout) {  // uniform: give up, but not before the copies under way have landed
+            if (tid == 0) {
+                atomicOr(status, ISPORE_DEV_TIMEOUT);
+                for (uint32_t i2 = i; i2 < i + static_cast<uint32_t>(nbuf) - 1u && row_of(i2) < total_rows; ++i2)
+                    tma::mbar_wait(&full[i2 % static_cast<uint32_t>(nbuf)], (i2 / static_cast<uint32_t>(nbuf)) & 1u);
+                tma::wait_group_read<0>();
+            }
+            return;
+        }
+        // The buffer of the previous row is free once its bulk store has read it: row i + nbuf - 1 goes there.
+        if (tid == 0) {
+            tma::wait_group_read<0>();
+            request_row(i + static_cast<uint32_t>(nbuf) - 1u);
+        }
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) mx = fmaxf(mx, red[0][w]);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = tid + j * kStagedThreads;
+            if (v < row_vecs) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) {
+                    z[j].v[e] = Exp::exp_diff(z[j].v[e], mx);
+                    sum += z[j].v[e];
+                }
+            }
+        }
+        sum = warp_sum(sum);
+        if (lane == 0) red[1][warp] = sum;
+        __syncthreads();
+        sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kWarps; ++w) sum += red[1][w];
+        const float inv = 1.0f / (sum + 1e-6f);
+#pragma unroll
+        for (int j = 0; j < VPT; ++j) {
+            const int v = tid + j * kStagedThreads;
+            if (v < row_vecs) {
+#pragma unroll
+                for (int e = 0; e < E; ++e) z[j].v[e] *= inv;
+                srow[v] = pack(z[j]);
+            }
+        }
+        tma::fence_proxy_async();  // the row written above is read by the copy engine
+        __syncthreads();
+        if (tid == 0) {
+            tma::store(score + r * static_cast<uint64_t>(row_vecs) * E, srow, row_bytes);
+            tma::commit_group();
+        }
+    }
+    if (tid == 0) tma::wait_group_read<0>();  // shared memory must outlive the last store's read
+}
+
+template <typename T, bool CAUSAL, int VPT, int kStagedThreads>
+int launch_staged_rows(T* score, const T* qk, const MaskSource<T>& ms, int64_t total_rows, int64_t heads, int64_t q_len,
+                       int row_vecs, float scale, cudaStream_t st) {
+    auto kernel = softmax_staged_row_kernel<T, VPT, kStagedThreads, CAUSAL>;
+    const size_t row_bytes = static_cast<size_t>(row_vecs) * 16;
+    // Two CTAs of 256 threads with three buffers each, or one of 512 with as many as fit (up to four).
+    int nbuf = 3;
+    if (kStagedThreads > 256 && 4 * row_bytes <= 220 * 1024) nbuf = 4;
+    const size_t smem = nbuf * row_bytes;
+    if (!allow_dynamic_smem(kernel, smem)) return fail(ISPORE_ELAUNCH, "softmax: %zu bytes of dynamic shared memory refused", smem);
+    unsigned* status = device_status_ptr();
+    if (status == nullptr) return fail(ISPORE_ELAUNCH, "softmax: no device status word");
+    const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kStagedThreads, smem);
+    const int grid = static_cast<int>(total_rows < resident ? total_rows : resident);
+    launch_chained(kernel, grid, kStagedThreads, smem, st, score, qk, ms.mask, ms.q_lens, ms.k_lens,
+                   static_cast<uint32_t>(total_rows), static_cast<uint32_t>(heads), static_cast<uint32_t>(q_len), row_vecs,
+                   scale, nbuf, status);
+    return check_launch("softmax_staged_row_kernel");
+}
+
 template <typename T, bool CAUSAL>
 int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t batch, int64_t heads, int64_t q_len,
                      int64_t k_len, float scale, cudaStream_t st) {
@@ -661,6 +858,27 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
         prefer_rows = CAUSAL ? (k_len > 512 && k_len != 4096) : (k_len > 512 && !(pow2 && k_len >= 4096));
     else
         prefer_rows = CAUSAL ? k_len >= 288 : (k_len > 256 && !pow2 && !(k_len >= 1000 && k_len <= 2048));
+    // Rows of more than 16 KB (whole vectors, up to 4096 of them) go through the staged kernel:
+    // measured on B200 against the kernels below, with and without a mask tensor, 0.74-0.93 of the
+    // copy rate against 0.51-0.74 (fp32 from 6000 elements, fp16 from 12000; 16384: 0.84-0.92
+    // against 0.55-0.67).  Shorter rows lose there: one CTA per row synchronises too often.
+    if (vec_ok && vecs <= 4096 && (vecs > 1024 || (CAUSAL && sizeof(T) == 2 && vecs == 1024)) &&
+        tune(kTuneSoftmax, 0) != 1) {
+        const int rv = static_cast<int>(vecs);
+        // rows of which only one CTA's ring fits an SM, or with more than 8 vectors per thread, get twice the threads
+        const bool wide = vecs * 16 * 3 * 2 > 220 * 1024 || vecs > 8 * 256;
+        const int64_t per_thread = ceil_div(vecs, static_cast<int64_t>(wide ? 512 : 256));
+#define ISPORE_STAGED(VPT, THREADS) \
+    return launch_staged_rows<T, CAUSAL, VPT, THREADS>(score, qk, ms, total_rows, heads, q_len, rv, scale, st)
+        if (wide) {
+            if (per_thread <= 4) ISPORE_STAGED(4, 512);
+            ISPORE_STAGED(8, 512);
+        } else {
+            if (per_thread <= 4) ISPORE_STAGED(4, 256);
+            ISPORE_STAGED(8, 256);
+        }
+#undef ISPORE_STAGED
+    }
     if (vec_ok && !(rows_ok && prefer_rows)) {
         const int rv = static_cast<int>(vecs);
 #define ISPORE_SOFTMAX(VPT, GROUP, THREADS, HG, MINB) \

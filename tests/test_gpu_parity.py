@@ -1041,6 +1041,37 @@ def test_causal_softmax_any_row_length(ops, orc, rng, case, dtype):
         assert_close_f32(host(d), want, floor=1e-30, what="causal softmax f32, any row length")
 
 
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("case", [(2, 3, 5, 8192), (1, 2, 3, 8200), (2, 2, 7, 12000), (1, 3, 4, 16384), (1, 40, 9, 16384),
+                                  (1, 2, 3, 20000), (1, 1, 2, 32768)])
+def test_softmax_long_rows_through_the_staged_ring(ops, orc, rng, case, causal, dtype):
+    """Rows of whole vectors beyond 16 KB travel through a ring of shared-memory row buffers (bulk
+    copies in, bulk stores out), two CTAs of 256 threads per SM or one of 512 for the longest; a CTA
+    walks rows b, b + grid, ... — (1, 40, 9, 16384) gives every CTA several trips and wraps the
+    ring — and fetches each row's mask slice a trip ahead.  In place, mask tensor and mask-free."""
+    batch, heads, q_len, k_len = case
+    if dtype == np.float32 and k_len > 16384:
+        pytest.skip("fp32 rows beyond 4096 vectors take the generic kernel")
+    qk = (rng.standard_normal((batch, heads, q_len, k_len), dtype=np.float32) * 3).astype(dtype)
+    d = dev(qk)
+    if causal:
+        ql = rng.integers(1, q_len + 1, batch)
+        kl = np.minimum(ql + rng.integers(k_len // 2, k_len + 1, batch), k_len)
+        ops.launchScaleCausalSoftmax(d, _i32(ql), _i32(kl), d, 0.2)
+        mask = orc.build_causal_mask(ql, kl, q_len, k_len, dtype)
+    else:
+        mask = (rng.random((batch, q_len, k_len)) < 0.7).astype(dtype)
+        mask[0, q_len - 1] = 0  # a fully masked row
+        ops.launchScaleMaskAndSoftmax(d, dev(mask), d, 0.2)
+    want, want32 = orc.scale_mask_softmax(qk, mask, np.float32(0.2))
+    if dtype == np.float16:
+        err, over, _ = assert_close_f16(host(d), want32, want, "long-row softmax f16")
+        assert over == 0
+    else:
+        assert_close_f32(host(d), want, floor=1e-30, what="long-row softmax f32")
+
+
 @pytest.mark.parametrize("case", [(3000, 7, 3, 17), (2, 1, 4, 19), (5, 16, 1, 23), (1, 3, 1025, 9), (700, 3, 2, 35)])
 def test_softmax_any_row_length_row_index_recovery(ops, orc, rng, case):
     # many rows, one head, one q row, q_len a power of two and not: (sequence, head, q) are
