@@ -16,6 +16,8 @@
 // kernel argument.
 #include <math.h>
 
+#include <algorithm>
+
 #include "common.cuh"
 #include "tma.cuh"
 
@@ -202,6 +204,7 @@ qkv_rope_transpose_vec_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
 // 25 % slower at every token count, more so with more buffers: what carries this kernel is the
 // number of CTAs an SM overlaps (nine of these), not the depth of any one CTA's queue.
 constexpr int kTmaPiece = 8192;
+constexpr int64_t kSplitTokens = 16384;  // launches up to this many tokens run three CTAs per token
 
 template <typename T, int THREADS, int HEAD_SIZE, bool FULL_ROT, bool HAS_BIAS>
 __global__ void __launch_bounds__(THREADS)
@@ -223,12 +226,20 @@ qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
     const int tid = threadIdx.x;
     const int qkv_heads = head_num + 2 * kv_head_num;
     const int64_t token = blockIdx.x;
-    const uint32_t bytes = static_cast<uint32_t>(qkv_heads) * head_size * sizeof(T);
+    // gridDim.y == 3: the CTA takes the token's q heads, its k heads or its v heads only.
+    int first_head = 0, last_head = qkv_heads;
+    if (gridDim.y == 3) {
+        first_head = blockIdx.y == 0 ? 0 : blockIdx.y == 1 ? head_num : head_num + kv_head_num;
+        last_head = blockIdx.y == 0 ? head_num : blockIdx.y == 1 ? head_num + kv_head_num : qkv_heads;
+    }
+    const uint32_t head_bytes = static_cast<uint32_t>(head_size) * sizeof(T);
+    const uint32_t bytes = static_cast<uint32_t>(last_head - first_head) * head_bytes;
     if (tid == 0) {
         tma::mbar_init(&bar, 1);
         tma::fence_mbar_init();
         tma::mbar_arrive_expect_tx(&bar, bytes);
-        const unsigned char* src = reinterpret_cast<const unsigned char*>(QKV) + token * bytes;
+        const unsigned char* src = reinterpret_cast<const unsigned char*>(QKV) +
+                                   (token * qkv_heads + first_head) * static_cast<int64_t>(head_bytes);
         for (uint32_t off = 0; off < bytes; off += kTmaPiece)
             tma::load(token_raw + off, src + off, min(static_cast<uint32_t>(kTmaPiece), bytes - off), &bar);
     }
@@ -244,11 +255,13 @@ qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
             b = dst_token / seq_len;
             s = dst_token - b * seq_len;
         }
-        const float m = static_cast<float>(__ldg(history_length + b) + static_cast<int>(s));
-        for (int j = tid; j < kRotHalf; j += THREADS) {
-            float sn, cs;
-            sincosf(m / freq.d[j], &sn, &cs);
-            cos_sin[j] = make_float2(cs, sn);
+        if (first_head < head_num + kv_head_num) {  // v heads are not rotated
+            const float m = static_cast<float>(__ldg(history_length + b) + static_cast<int>(s));
+            for (int j = tid; j < kRotHalf; j += THREADS) {
+                float sn, cs;
+                sincosf(m / freq.d[j], &sn, &cs);
+                cos_sin[j] = make_float2(cs, sn);
+            }
         }
     }
     __syncthreads();  // cos/sin written; the barrier's initialisation is visible to every waiter
@@ -267,13 +280,17 @@ qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
     uint4* q_row = reinterpret_cast<uint4*>(q_buf) + (b * head_num * seq_len + s) * kHeadVecs;
     uint4* k_row = reinterpret_cast<uint4*>(k_buf) + (b * kv_head_num * seq_len + s) * kHeadVecs;
     uint4* v_row = reinterpret_cast<uint4*>(v_buf) + (b * kv_head_num * seq_len + s) * kHeadVecs;
-    const int rope_tasks = (head_num + kv_head_num) * kHalfVecs;
-    const int v_tasks = kv_head_num * kHeadVecs;
+    // (tok holds the heads first_head .. last_head - 1 of the token)
+    const int rope_end = min(last_head, head_num + kv_head_num);
+    const int rope_tasks = rope_end > first_head ? (rope_end - first_head) * kHalfVecs : 0;
+    const int v_first = max(first_head, head_num + kv_head_num);  // first v head held, as a qkv head index
+    const int v_tasks = (last_head - v_first) * kHeadVecs;
     for (int task = tid; task < rope_tasks; task += THREADS) {
-        const int hh = task / kHalfVecs, c = task % kHalfVecs;
+        const int hl = task / kHalfVecs, c = task % kHalfVecs;
+        const int hh = first_head + hl;
         Unpacked<T> lo, hi;
-        unpack(tok[hh * kHeadVecs + c], lo);
-        unpack(tok[hh * kHeadVecs + kHalfVecs + c], hi);
+        unpack(tok[hl * kHeadVecs + c], lo);
+        unpack(tok[hl * kHeadVecs + kHalfVecs + c], hi);
         if (HAS_BIAS) {
             Unpacked<T> blo, bhi;
             unpack(ld_keep(bias_v + hh * kHeadVecs + c), blo);
@@ -297,9 +314,9 @@ qkv_rope_transpose_tma_kernel(T* __restrict__ q_buf, T* __restrict__ k_buf, T* _
         st_stream(dst + c, pack(lo));
         st_stream(dst + kHalfVecs + c, pack(hi));
     }
-    const uint4* vtok = tok + (head_num + kv_head_num) * kHeadVecs;
+    const uint4* vtok = tok + (v_first - first_head) * kHeadVecs;
     for (int task = tid; task < v_tasks; task += THREADS) {
-        const int h = task / kHeadVecs, c = task % kHeadVecs;
+        const int h = task / kHeadVecs, c = task % kHeadVecs;  // (every v head of the token is held when any is)
         uint4 raw = vtok[task];
         if (HAS_BIAS) {
             Unpacked<T> x, bb;
@@ -445,12 +462,20 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
         // shapes, run-time head size / partial rotation otherwise.
         const int64_t token_bytes = (head_num + 2 * kv_head_num) * head_size * static_cast<int64_t>(sizeof(T));
         if (token_bytes <= 96 * 1024 && token_num < (1ll << 31) && head_size <= 2 * kMaxRotHalf && tune(kTuneQkv, 0) != 1) {
+            // One CTA per token, or three (its q, k and v heads) while the launch is short: a launch
+            // costs a whole number of waves of resident CTAs plus about one for the ramp, and CTAs
+            // of a third of the bytes make the waves shorter (measured, 32 + 32 + 32 heads of 128:
+            // 4096 tokens 45 -> 40 us, 8192 tokens 76 -> 72 us, 16384 tokens 137 -> 135 us; at
+            // 65536 tokens the single CTA is 2 % faster; 64-thread CTAs for the thirds: no better).
+            const bool split = tune(kTuneQkv, 0) == 3 || (tune(kTuneQkv, 0) != 2 && token_num <= kSplitTokens);
+            const int64_t part_bytes = split ? std::max(head_num, kv_head_num) * head_size * static_cast<int64_t>(sizeof(T)) : token_bytes;
+            const dim3 tma_grid(static_cast<unsigned>(token_num), split ? 3u : 1u);
 #define ISPORE_QKV_TMA(HS, FR, HB)                                                                          \
     do {                                                                                                    \
         constexpr int TH = 128; /* measured: 64 and 256 threads are 3-6 % slower */                         \
         auto kernel = qkv_rope_transpose_tma_kernel<T, TH, HS, FR, HB>;                                     \
-        if (!allow_dynamic_smem(kernel, static_cast<size_t>(token_bytes))) break;                           \
-        launch_chained(kernel, static_cast<unsigned>(token_num), TH, static_cast<size_t>(token_bytes), st,  \
+        if (!allow_dynamic_smem(kernel, static_cast<size_t>(part_bytes))) break;                            \
+        launch_chained(kernel, tma_grid, TH, static_cast<size_t>(part_bytes), st,                           \
             q_buf, k_buf, v_buf, QKV, bias, padding_offset, history_length, batch_size, seq_len,           \
             (int)head_num, (int)kv_head_num, (int)head_size, rot_dim / 2, freq, status);                    \
         return check_launch("qkv_rope_transpose_tma_kernel");                                               \

@@ -330,6 +330,31 @@ def test_concat_kv_overrun_is_flagged_and_clamped(ops, orc, rng):
     assert np.array_equal(host(dk), orc.concat_kv(k_dst, k_src, cur, hist, 0))
 
 
+def test_qkv_rope_beyond_the_three_way_split(ops, orc, rng):
+    """Launches of up to 16384 tokens run three CTAs per token (its q, its k and its v heads); longer
+    ones one CTA per token.  17000 tokens of small grouped heads (8 q, 2 kv, size 64) with a bias and
+    ragged sequences take the latter, against the oracle."""
+    batch, seq, heads, kv_heads, d = 40, 512, 8, 2, 64
+    lens = rng.integers(300, seq + 1, batch)
+    lens[: 17000 // seq + 1] = seq
+    while lens.sum() < 17000:
+        lens[rng.integers(0, batch)] = seq
+    tokens = int(lens.sum())
+    assert tokens > 16384
+    pad = np.concatenate([np.full(n, i * seq - lens[:i].sum(), np.int32) for i, n in enumerate(lens)])
+    hist = rng.integers(0, 100, batch).astype(np.int32)
+    qkv = randn16(rng, (tokens, heads + 2 * kv_heads, d))
+    bias = randn16(rng, ((heads + 2 * kv_heads) * d,), 0.1)
+    q = torch.zeros((batch, heads, seq, d), dtype=torch.float16, device="cuda:0")
+    k = torch.zeros((batch, kv_heads, seq, d), dtype=torch.float16, device="cuda:0")
+    v = torch.zeros_like(k)
+    ops.launchAddFusedQKVBiasTransposeAndRoPE(q, k, v, dev(qkv), dev(bias), dev(pad), dev(hist), _i32(lens), d, 10000.0)
+    wq, wk, wv, q32, k32 = orc.qkv_bias_rope_transpose(qkv, bias, pad, hist, batch, seq, heads, kv_heads, d, 10000.0)
+    assert_close_f16(host(q), q32, wq, "q beyond the split")
+    assert_close_f16(host(k), k32, wk, "k beyond the split")
+    assert np.array_equal(host(v).view(np.uint16), wv.view(np.uint16))
+
+
 # ---- softmax --------------------------------------------------------------------------------------------------------------
 
 SOFTMAX_CASES = [
