@@ -54,11 +54,11 @@ KERNELS = ["input_embedding", "rmsnorm", "qkv_bias_rope_transpose", "concat_kv",
            "add_residual_rmsnorm", "silu_mul", "topk_sampling"]
 TOTAL_TOKENS = 65536
 # DRAM traffic of the roofline kernel (SiLU*up): dram__bytes_read.sum + dram__bytes_write.sum of one
-# launch at 16,384 tokens from an ncu capture of the current kernel (721.4 + 315.1 MB) over that
+# launch at 16,384 tokens from an ncu capture of the current kernel (721.4 + 314.0 MB) over that
 # launch's algorithmic bytes (1,082.1 MB).  The kernel is a flat streaming pass, so traffic grows in
 # proportion to the rows; a full-size launch is scaled by it.  --traffic overrides it with a fresh
 # capture's figure.
-NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1036.5 / 1082.13
+NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1035.4 / 1082.13
 
 
 def launches_per_step(topk_rows: int) -> int:
