@@ -794,6 +794,34 @@ def host_memory_available() -> int:
     return avail
 
 
+def bind_to_gpu_numa_node(device_index: int) -> str:
+    """Pins this process to the CPUs of the NUMA node its GPU hangs off, before any pinned host
+    buffer exists: pinned pages are placed where the allocating thread runs, and copies from the
+    other socket's memory cross the inter-socket link, which all ranks of a node then share.
+    Best effort: returns what was done (the bench line carries it)."""
+    try:
+        import torch
+
+        bus = torch.cuda.get_device_properties(device_index).pci_bus_id
+        dom = torch.cuda.get_device_properties(device_index).pci_domain_id
+        dev = torch.cuda.get_device_properties(device_index).pci_device_id
+        pci = f"{dom:04x}:{bus:02x}:{dev:02x}.0"
+        node = int(Path(f"/sys/bus/pci/devices/{pci}/numa_node").read_text().strip())
+        if node < 0:
+            return f"unchanged (GPU {pci} reports no NUMA node)"
+        cpus = set()
+        for part in Path(f"/sys/devices/system/node/node{node}/cpulist").read_text().strip().split(","):
+            lo, _, hi = part.partition("-")
+            cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & set(os.sched_getaffinity(0))
+        if not allowed:
+            return f"unchanged (no allowed CPU on NUMA node {node} of GPU {pci})"
+        os.sched_setaffinity(0, allowed)
+        return f"NUMA node {node} of GPU {pci} ({len(allowed)} CPUs)"
+    except Exception as exc:  # no sysfs, no such attribute, not permitted ...
+        return f"unchanged ({type(exc).__name__})"
+
+
 def run_ours(args) -> dict:
     import torch
     import torch.distributed as dist
@@ -808,6 +836,8 @@ def run_ours(args) -> dict:
         raise RuntimeError("bench.py needs a CUDA device: the layer kernels have no CPU path")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
+    all_cpus = os.sched_getaffinity(0)
+    host_affinity = bind_to_gpu_numa_node(local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # NCCL prints its version banner on stdout at VERSION/INFO level; stdout carries the one JSON line.
@@ -937,6 +967,7 @@ def run_ours(args) -> dict:
            "h2d_bytes_per_step": hd.h2d, "d2h_bytes_per_step": hd.d2h, "rows_per_step": e2e_tokens,
            "rows_per_step_all_gpus": world * e2e_tokens, "steps": e2e_steps, "ms_per_step": round(e2e_ms_per_step, 3)}
     del e2e_chains, hd
+    os.sched_setaffinity(0, all_cpus)  # the CPU baseline below runs on every core again
     torch.cuda.empty_cache()
 
     sharded_topk = vocab_sharded_leg(torch, dist, ops, device, rank, world, barrier, max_over_ranks) if world > 1 else None
@@ -979,7 +1010,7 @@ def run_ours(args) -> dict:
                    "l2": "inputs larger than L2 (2.4 GB of tensors per step even at 8,192 tokens per GPU; top-K rotates 5 "
                          "logits buffers)",
                    "sharding": f"token axis, whole sequences, {world} shard(s), no collective",
-                   "launch": launch_mode},
+                   "launch": launch_mode, "host_affinity": host_affinity},
         "gbs": round(total_bytes / (ms_per_step * 1e-3) / 1e9, 1),
         "eager": {"ms_per_step": round(eager_ms_per_step, 4), "value": round(total_tokens / (eager_ms_per_step * 1e-3), 1),
                   "note": "the same K steps launched one by one with CUDA events around every kernel; source of `kernels` "
