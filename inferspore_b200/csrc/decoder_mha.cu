@@ -708,7 +708,8 @@ constexpr int kChunkFloatsMax = 40960;       // with the opt-in (160 KB)
 // q heads of one kv head per CTA.  Eight only where both products run on the tensor cores (half
 // rows of 128); with FMA products a group of eight is bound by instruction issue.
 int pick_group(int64_t q_per_kv, bool tensor_cores) {
-    const int cap = tune(kTuneMhaGroup, 8);
+    int cap = tune(kTuneMhaGroup, 8);
+    if (tune(kTuneMhaStaged, 1) == 0 && cap > 4) cap = 4;  // the register-staged comparison variant has no group of eight
     for (int g : {8, 4, 2})
         if (g <= cap && q_per_kv % g == 0 && (g < 8 || tensor_cores)) return g;
     return 1;
