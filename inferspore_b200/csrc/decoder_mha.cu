@@ -30,6 +30,14 @@
 // eight warps.
 // With more than one chunk per (b, head) the CTAs leave (max, sum, unnormalised output) in a
 // workspace and a second kernel combines them.
+// Measured and not kept: chunks longer than the logits buffer, worked through in passes of 512
+// positions inside one CTA with a running maximum (so that a CTA's start and end are paid once
+// per 1024-4096 positions and the number of chunks can be fitted to the rounds of resident CTAs).
+// The accumulators and the tile bookkeeping that then live across the passes took the
+// eight-head variant from 62 to 123 registers; capped at the 85 that three CTAs per SM allow it
+// ran at 0.71 of the copy rate against 0.81 at the same 512-position chunk, and longer chunks
+// (0.74 at 1024, 0.60 at 4096) did not make up for it.  A fourth ring stage instead of the third
+// CTA: 0.66-0.79 against 0.81.
 #include <float.h>
 
 #include <algorithm>
