@@ -8,20 +8,21 @@
 // is a run-time value up to ISPORE_TOPK_MAX_K and the order is total:
 // (value descending, index ascending), -0.0 == +0.0.
 //
-// Round 1 (one CTA per row slice) streams its slice from HBM once, a tile of
-// 8192 elements at a time (TMA bulk copies into a shared-memory ring, the next
-// tile requested before the current one is touched), 32 elements per thread.
-// First tile: a threshold that is guaranteed to keep at least K elements comes
-// from one representative per thread: every warp sorts its 32 with a shuffle
-// network and contributes its best few, and the K-th largest contribution is
-// the threshold.  The few survivors are compacted into shared memory, a warp
-// at a time, and ranked by counting against each other, which yields the
-// running top-K already sorted.  Every later tile only has to beat the running
-// K-th best: while that is a positive value the test is one integer compare of
-// the thread's maximum and one vote per warp; the few survivors are parked
-// behind the running best and ranked before the next tile is touched, so the
-// bar rises as early as possible.  A later tile costs one block barrier, plus
-// one for its ranking when it had survivors.
+// Round 1 (one CTA per row slice) streams its slice from HBM once, in passes of two
+// tiles of 8192 elements — 64 elements per thread (TMA bulk copies into a
+// shared-memory ring that holds a pass, the next tiles requested as soon as
+// every thread has read this pass's).  First pass: a threshold that is
+// guaranteed to keep at least K elements comes from one representative per
+// thread: every warp sorts its 32 with a shuffle network and contributes its
+// best few, and the K-th largest contribution is the threshold.  The few
+// survivors are compacted into shared memory, a warp at a time, and ranked by
+// counting against each other, which yields the running top-K already sorted.
+// Every later pass only has to beat the running K-th best: while that is a
+// positive value the test is one integer compare of the thread's maximum and
+// one vote per warp; the few survivors are parked behind the running best and
+// ranked before the next pass is touched, so the bar rises as early as
+// possible.  A later pass costs one block barrier, plus one for its ranking
+// when it had survivors.  (The code calls a pass a "round".)
 // Adversarial tiles (e.g. constant data, where the threshold keeps everything)
 // fall back to an exact radix select over the tile, ties resolved by an
 // index-ordered block scan.  Round 2 (one CTA per row) merges the slices' sorted
@@ -50,12 +51,12 @@ __device__ long long g_topk_ts[64];  // clock64() of CTA 0 at marked points, tun
 
 constexpr int kTopkThreads = 256;  // measured: 512 threads x 16 keys is 1.5x slower (barriers over 16 warps)
 constexpr int kTopkWarps = kTopkThreads / 32;
-constexpr int kElemsPerThread = 32;                          // keys a thread holds per tile
+constexpr int kElemsPerThread = 32;                          // elements of a tile a thread looks at
 constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
 constexpr int kMaxStages = 8;                                // tiles of the shared-memory ring
 constexpr int kRoundTiles = 2;                               // tiles a CTA thresholds, compacts and ranks together
 constexpr int kTileCap = 256;                                // survivors a round may add on the fast path
-constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + tile survivors
+constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + a round's survivors
 constexpr int kWarpVecCap = 64;                              // vectors with survivors a warp lists per round
 constexpr int kMergeCap = 4096;                              // lists*K candidates the merge kernel holds
 
@@ -353,7 +354,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     constexpr int kVecs = kElemsPerThread / E;
     extern __shared__ __align__(128) unsigned char stage_raw[];  // TMA: [nstages][kTileElems * sizeof(T)]
     __shared__ __align__(8) uint64_t full[kMaxStages];
-    __shared__ unsigned long long cand[2][kCandSlots];  // [cur]: running best then tile survivors
+    __shared__ unsigned long long cand[2][kCandSlots];  // [cur]: running best, then the round's survivors
     __shared__ uint32_t warp_thr[kTopkWarps];
     __shared__ int s_count;
     __shared__ int s_push[4];
@@ -375,7 +376,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
     // (requested now, needed at the very end: its DRAM latency would otherwise sit on the row's critical path)
     const float u_row = (uniform != nullptr && tid < 32) ? __ldg(uniform + row) : 0.f;
 
-    if (tid < 4) s_push[tid] = 0;  // visible before its first use: every tile kind has a barrier before the next tile
+    if (tid < 4) s_push[tid] = 0;  // visible before its first use: every kind of round has a barrier before the next round
 
     int cur = 0;    // which cand[] buffer holds the running best
     int nbest = 0;  // entries of the running best (sorted, best first)
