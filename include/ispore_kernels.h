@@ -269,7 +269,8 @@ ISPORE_API int ispore_scale_causal_softmax_f16(void* attn_score, const void* qk,
  * tensors the reference launcher takes; round 2 merges them.  The scratch only
  * bounds the number of slices: with scratch_slices <= 1 (or NULL scratch) one
  * CTA walks each row and writes the final lists directly, which is correct for
- * any vocab but leaves the GPU idle when there are few rows.  index_offset is
+ * any vocab and is what the library chooses anyway for rows of up to 65536
+ * elements (one launch; longer rows are cut into slices of 32768).  index_offset is
  * added to every emitted id (vocab-sharded callers pass the shard's first
  * column).  When uniform != NULL the merge also draws one id per row exactly
  * as ispore_sampling_* does and writes it to sampled_ids [rows]. */

@@ -917,9 +917,6 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     if (uniform != nullptr && sampled_ids == nullptr) return fail(ISPORE_ENULL, "topk: uniform given without sampled_ids");
 
     constexpr int E = VecTraits<T>::kElems;
-    // Slices per row: enough CTAs to fill the GPU once (a CTA walks a long slice tile by
-    // tile, and later tiles are cheap because they must beat the running K-th best), at
-    // least 1024 elements per slice, never more than the scratch or the merge kernel hold.
     const int variant = tune(kTuneTopk, 0);
     const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
     const int vec_loads = (vocab % E == 0) && aligned16(probs);
@@ -947,14 +944,23 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     unsigned* status = device_status_ptr();
     if (status == nullptr) return fail(ISPORE_ELAUNCH, "topk: no device status word");
     const int64_t resident = resident_ctas(reinterpret_cast<const void*>(kernel), kTopkThreads, use_tma ? ring_bytes : 0);
+    // Slices per row.  A row of up to four rounds is one slice: a CTA walks it in 9-10 us at any
+    // row count that fits the GPU, where cutting it costs the merge launch (measured at 8-128
+    // rows x 32000: 9-10 us against 11-17 us with 2-8 slices).  Longer rows are cut into slices of
+    // two rounds, as far as the resident slots, the scratch and the merge kernel allow.
+    constexpr int64_t kRoundElems = static_cast<int64_t>(kRoundTiles) * kTileElems;
     int64_t slices;
     switch ((variant & 0xff) >> 1) {
-        case 1: slices = ceil_div(vocab, kTileElems); if (ceil_div(resident, rows) > slices) slices = ceil_div(resident, rows); break;
+        case 1: slices = resident / rows; break;  // (tuning builds: as many slices as fill the GPU once)
         case 2: slices = 8; break;
         case 3: slices = 2; break;
         case 4: slices = 3; break;
-        default: slices = resident / rows; if (slices < 1) slices = 1; break;
+        default:
+            slices = vocab <= 4 * kRoundElems ? 1 : ceil_div(vocab, 2 * kRoundElems);
+            if (slices > resident / rows) slices = resident / rows;
+            break;
     }
+    if (slices < 1) slices = 1;
     if (slices > ceil_div(vocab, 1024)) slices = ceil_div(vocab, 1024);
     if (slices * K > kMergeCap) slices = kMergeCap / K;
     if (slices > (have_scratch ? scratch_slices : 1)) slices = have_scratch ? scratch_slices : 1;
