@@ -62,10 +62,10 @@ NCU_TRAFFIC_PER_ALGORITHMIC_BYTE = 1035.4 / 1082.13
 
 
 def launches_per_step(topk_rows: int) -> int:
-    """Kernels of this library per chain step: one per op, and a second one (the merge) for top-K
-    when the rows are too few to fill the GPU with one CTA each, so that each row is cut in slices
-    (3 CTAs per SM x 148 SMs resident: two or more slices per row up to 222 rows)."""
-    return 8 + (1 if 2 * topk_rows <= 3 * 148 else 0)
+    """Kernels of this library per chain step: one per op (top-K runs one slice per row at this
+    vocabulary, so its merge kernel is not launched)."""
+    del topk_rows
+    return 8
 
 
 def algorithmic_bytes(tokens: int, topk_rows: int) -> dict:
