@@ -54,7 +54,12 @@ constexpr int kTopkWarps = kTopkThreads / 32;
 constexpr int kElemsPerThread = 32;                          // elements of a tile a thread looks at
 constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
 constexpr int kMaxStages = 8;                                // tiles of the shared-memory ring
-constexpr int kRoundTiles = 2;                               // tiles a CTA thresholds, compacts and ranks together
+#ifndef ISPORE_TOPK_HALF_ROUND
+#define ISPORE_TOPK_HALF_ROUND 2
+#endif
+// Tiles a CTA thresholds, compacts and ranks together: 64 elements per thread.
+template <typename T>
+constexpr int round_tiles() { return sizeof(T) == 2 ? ISPORE_TOPK_HALF_ROUND : 2; }
 constexpr int kTileCap = 256;                                // survivors a round may add on the fast path
 constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + a round's survivors
 constexpr int kWarpVecCap = 64;                              // vectors with survivors a warp lists per round
@@ -352,6 +357,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
                   const float* __restrict__ uniform, float temperature, int32_t* __restrict__ sampled_ids) {
     constexpr int E = VecTraits<T>::kElems;
     constexpr int kVecs = kElemsPerThread / E;
+    constexpr int kRoundTiles = round_tiles<T>();
     extern __shared__ __align__(128) unsigned char stage_raw[];  // TMA: [nstages][kTileElems * sizeof(T)]
     __shared__ __align__(8) uint64_t full[kMaxStages];
     __shared__ unsigned long long cand[2][kCandSlots];  // [cur]: running best, then the round's survivors
@@ -932,6 +938,7 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     // set the time, and with three rows per SM in flight the wait it hides was not exposed).
     constexpr size_t kStage = static_cast<size_t>(kTileElems) * sizeof(T);
     constexpr size_t kRingFew = 64 * 1024;
+    constexpr int kRoundTiles = round_tiles<T>();
     constexpr size_t kRingMany = kRoundTiles * kStage < kRingFew ? kRoundTiles * kStage : kRingFew;
     const int64_t one_wave = 3 * static_cast<int64_t>(sm_count());
     bool many = use_tma && kRingMany < kRingFew && rows > one_wave;  // (a launch of that many rows runs one slice per row)
