@@ -8,10 +8,10 @@
 // is a run-time value up to ISPORE_TOPK_MAX_K and the order is total:
 // (value descending, index ascending), -0.0 == +0.0.
 //
-// Round 1 (one CTA per row slice) streams its slice from HBM once, in passes of two
-// tiles of 8192 elements — 64 elements per thread (TMA bulk copies into a
-// shared-memory ring that holds a pass, the next tiles requested as soon as
-// every thread has read this pass's).  First pass: a threshold that is
+// Round 1 (one CTA per row slice) streams its slice from HBM once, in passes of 64 KB
+// — two tiles of 8192 fp32 elements or four of fp16, 64 or 128 elements per
+// thread (TMA bulk copies into a shared-memory ring that holds a pass, the next
+// tiles requested as soon as every thread has read this pass's).  First pass: a threshold that is
 // guaranteed to keep at least K elements comes from one representative per
 // thread: every warp sorts its 32 with a shuffle network and contributes its
 // best few, and the K-th largest contribution is the threshold.  The few
@@ -54,12 +54,11 @@ constexpr int kTopkWarps = kTopkThreads / 32;
 constexpr int kElemsPerThread = 32;                          // elements of a tile a thread looks at
 constexpr int kTileElems = kTopkThreads * kElemsPerThread;   // 8192
 constexpr int kMaxStages = 8;                                // tiles of the shared-memory ring
-#ifndef ISPORE_TOPK_HALF_ROUND
-#define ISPORE_TOPK_HALF_ROUND 2
-#endif
-// Tiles a CTA thresholds, compacts and ranks together: 64 elements per thread.
+// Tiles a CTA thresholds, compacts and ranks together: 64 KB of the row, i.e. 64 fp32 or 128 fp16
+// elements per thread (measured for fp16 against two tiles per round: [256, 32000] 12.2 -> 9.5 us,
+// 4096 rows 100 -> 89 us, [256, 128256] 31.7 -> 26.3 us).
 template <typename T>
-constexpr int round_tiles() { return sizeof(T) == 2 ? ISPORE_TOPK_HALF_ROUND : 2; }
+constexpr int round_tiles() { return sizeof(T) == 2 ? 4 : 2; }
 constexpr int kTileCap = 256;                                // survivors a round may add on the fast path
 constexpr int kCandSlots = ISPORE_TOPK_MAX_K + kTileCap;     // running best + a round's survivors
 constexpr int kWarpVecCap = 64;                              // vectors with survivors a warp lists per round
@@ -417,7 +416,7 @@ topk_slice_kernel(const T* __restrict__ probs, int64_t vocab, int slice_len, int
         __syncthreads();  // the barriers' initialisation is visible to every thread that will wait on them
     }
 
-    // A round takes kRoundTiles tiles at once — 64 elements per thread — through threshold,
+    // A round takes kRoundTiles tiles at once — 64 KB of the row — through threshold,
     // compaction and ranking: those steps depend on each other and on two block barriers, and a row
     // is a chain of them, so half as many rounds is what shortens a row (measured at 256 and 4096
     // rows x 32000 against one tile per round: see the dispatcher).
@@ -927,25 +926,21 @@ int topk_dispatch(const T* probs, int64_t rows, int64_t vocab, int32_t K, int32_
     const bool have_scratch = scratch_ids != nullptr && scratch_vals != nullptr && scratch_slices >= 1;
     const int vec_loads = (vocab % E == 0) && aligned16(probs);
     const bool use_tma = vec_loads && !(variant & 1);
-    // The tile ring.  A row is a chain of dependent steps (tiles, threshold, survivors, rank, next
-    // tiles ...), so what a launch with more rows than the GPU holds at once needs is rows in
-    // flight, and what any launch needs is a ring that holds a whole round: 64 KB and three CTAs per
-    // SM — one round of fp32, two of fp16 — or, for fp16 launches of more than one wave, 32 KB and
-    // four CTAs per SM under a register cap of 64.  Measured and not kept: deeper rings at fewer
-    // CTAs per SM, slower at every row count; and one CTA per resident slot walking the rows
+    // The tile ring: 64 KB, one round, three CTAs per SM.  A row is a chain of dependent steps
+    // (tiles, threshold, survivors, rank, next tiles ...): what shortens it is fewer, larger rounds,
+    // and what a launch of more rows than the GPU holds at once needs is rows in flight.  Measured
+    // and not kept: deeper rings at fewer CTAs per SM, slower at every row count; four CTAs per SM
+    // on a 32 KB ring (a gain while a round was one tile, none against 64 KB rounds); and one
+    // CTA per resident slot walking the rows
     // b, b + grid, ... with the next row's first tiles requested during the current row's last
     // ranking (4096 rows: 124 us against 115 us — the rows a static stride hands the slowest CTA
     // set the time, and with three rows per SM in flight the wait it hides was not exposed).
     constexpr size_t kStage = static_cast<size_t>(kTileElems) * sizeof(T);
-    constexpr size_t kRingFew = 64 * 1024;
+    constexpr size_t kRingBytes = 64 * 1024;
     constexpr int kRoundTiles = round_tiles<T>();
-    constexpr size_t kRingMany = kRoundTiles * kStage < kRingFew ? kRoundTiles * kStage : kRingFew;
-    const int64_t one_wave = 3 * static_cast<int64_t>(sm_count());
-    bool many = use_tma && kRingMany < kRingFew && rows > one_wave;  // (a launch of that many rows runs one slice per row)
-    if (variant & 0x40) many = use_tma;
-    if (variant & 0x80) many = false;
-    auto kernel = use_tma ? (many ? topk_slice_kernel<T, 4, true> : topk_slice_kernel<T, 3, true>) : topk_slice_kernel<T, 4, false>;
-    const size_t ring_bytes = (variant >> 8) ? static_cast<size_t>(variant >> 8) * kStage : (many ? kRingMany : kRingFew);  // (tuning builds: stages from the variant's high byte)
+    static_assert(kRoundTiles * kStage == kRingBytes, "the ring holds one round");
+    auto kernel = use_tma ? topk_slice_kernel<T, 3, true> : topk_slice_kernel<T, 4, false>;
+    const size_t ring_bytes = (variant >> 8) ? static_cast<size_t>(variant >> 8) * kStage : kRingBytes;  // (tuning builds: stages from the variant's high byte)
     if (use_tma && !allow_dynamic_smem(kernel, ring_bytes))
         return fail(ISPORE_ELAUNCH, "topk: %zu bytes of dynamic shared memory refused", ring_bytes);
     unsigned* status = device_status_ptr();

@@ -592,8 +592,8 @@ def test_topk_outliers_in_the_first_tile(ops, orc, rng, dtype):
 @pytest.mark.parametrize("shape", ["noise", "rising", "steps", "flat", "negative"])
 @pytest.mark.parametrize("vocab,K", [(20000, 50), (8192, 64), (17001, 5)])
 def test_topk_more_rows_than_one_wave(ops, orc, rng, dtype, shape, vocab, K):
-    """More rows than three CTAs per SM hold at once: the launch switches to a smaller tile ring
-    (one fp32 stage, two fp16 stages) and four CTAs per SM, one slice per row.  `flat` rows hold one
+    """More rows than three CTAs per SM hold at once (CTA slots are reused within the launch), one
+    slice per row, a round of 64 KB (two fp32 tiles, four fp16 tiles).  `flat` rows hold one
     value only (every vector of a tile survives the threshold: the per-warp lists overflow and the
     tile is selected exactly), `rising` and `steps` overflow the parked survivors of later tiles,
     `negative` keeps the threshold below zero, 17001 is not a whole number of 128-bit vectors."""
