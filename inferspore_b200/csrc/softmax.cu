@@ -645,7 +645,7 @@ softmax_offset_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const
 constexpr int kStagedMaxBuf = 4;
 
 template <typename T, int VPT, int kStagedThreads, bool CAUSAL>
-__global__ void __launch_bounds__(kStagedThreads, (kStagedThreads > 256 ? 1 : kStagedThreads > 128 ? 2 : kStagedThreads > 64 ? 4 : 8))
+__global__ void __launch_bounds__(kStagedThreads, (kStagedThreads > 256 ? 1 : kStagedThreads > 128 ? 2 : kStagedThreads > 64 ? 4 : kStagedThreads > 32 ? 8 : 16))
 softmax_staged_row_kernel(T* __restrict__ score, const T* __restrict__ qk, const T* __restrict__ mask,
                           const int32_t* __restrict__ q_lens, const int32_t* __restrict__ k_lens,
                           uint32_t total_rows, uint32_t heads, uint32_t q_len, int row_vecs, float scale,
@@ -867,6 +867,11 @@ int softmax_dispatch(T* score, const T* qk, const MaskSource<T>& ms, int64_t bat
     // the row kernels run at 0.63-0.80), and fp16 rows of 8192 without a mask tensor: the same
     // staged kernel with four warps per row and four CTAs per SM — measured 0.72-0.89 (fp16 5000,
     // 6000; fp32 3000), 0.82 against 0.72 on the 8192-long mask-free fp16 rows.
+    // fp16 rows of 3 to 4 KB (beyond what the warp-per-row kernel holds in registers), one warp per
+    // row and no block barrier at all: 1792 elements 0.68 -> 0.84 with a mask tensor, 0.73 -> 0.82
+    // without; 2048 with a mask tensor 0.73 -> 0.78 (without: the head-group kernel's 0.81 stands).
+    if (vec_ok && sizeof(T) == 2 && vecs > 192 && vecs <= 256 && !(CAUSAL && pow2) && tune(kTuneSoftmax, 0) != 1)
+        return launch_staged_rows<T, CAUSAL, 8, 32>(score, qk, ms, total_rows, heads, q_len, static_cast<int>(vecs), scale, st);
     // Rows of 4 to 8 KB between the powers of two, two warps per row and eight CTAs per SM: fp16
     // 2560 / 3000 / 3584 elements 0.67-0.74 -> 0.73-0.79 with a mask tensor, 0.69-0.80 -> 0.74-0.80
     // without; fp32 1536 with a mask tensor 0.81 -> 0.89 (without: the row kernel's 0.93 stands).

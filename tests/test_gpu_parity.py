@@ -1070,7 +1070,7 @@ def test_causal_softmax_any_row_length(ops, orc, rng, case, dtype):
 @pytest.mark.parametrize("causal", [False, True])
 @pytest.mark.parametrize("case", [(2, 3, 5, 8192), (1, 2, 3, 8200), (2, 2, 7, 12000), (1, 3, 4, 16384), (1, 40, 9, 16384),
                                   (1, 2, 3, 20000), (1, 1, 2, 32768), (2, 3, 5, 5000), (1, 70, 9, 6008), (1, 33, 7, 3000),
-                                  (2, 2, 3, 4104), (2, 5, 3, 1536), (1, 200, 11, 2560)])
+                                  (2, 2, 3, 4104), (2, 5, 3, 1536), (1, 200, 11, 2560), (3, 50, 7, 1792), (1, 9, 40, 2048)])
 def test_softmax_long_rows_through_the_staged_ring(ops, orc, rng, case, causal, dtype):
     """Rows of whole vectors beyond 16 KB — and rows of 8 to 16 KB that are not a power of two long
     (5000, 6008 in fp16; 3000, 4104 in fp32), four warps per row, and of 4 to 8 KB between the powers
