@@ -466,7 +466,8 @@ int qkv_dispatch(T* q_buf, T* k_buf, T* v_buf, const T* QKV, const T* bias,
             // costs a whole number of waves of resident CTAs plus about one for the ramp, and CTAs
             // of a third of the bytes make the waves shorter (measured, 32 + 32 + 32 heads of 128:
             // 4096 tokens 45 -> 40 us, 8192 tokens 76 -> 72 us, 16384 tokens 137 -> 135 us; at
-            // 65536 tokens the single CTA is 2 % faster; 64-thread CTAs for the thirds: no better).
+            // 65536 tokens the single CTA is 2 % faster; 64-thread CTAs for the thirds: no better; four to
+            // twelve equal runs of heads per token instead of three: slower from 4096 tokens up).
             const bool split = tune(kTuneQkv, 0) == 3 || (tune(kTuneQkv, 0) != 2 && token_num <= kSplitTokens);
             const int64_t part_bytes = split ? std::max(head_num, kv_head_num) * head_size * static_cast<int64_t>(sizeof(T)) : token_bytes;
             const dim3 tma_grid(static_cast<unsigned>(token_num), split ? 3u : 1u);
